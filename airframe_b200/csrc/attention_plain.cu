@@ -1,0 +1,240 @@
+// Rotary position encoding with the cache write, and the plain attention
+// kernels (one warp per query row and head, keys in order).  They serve the
+// 32-bit path and stand beside the faster bfloat16 kernels as their twins.
+//
+// Cache of one layer: pages [n_pages][n_kv_heads][AF_PAGE][head_dim] for K and
+// for V.  A sequence's page table maps row / AF_PAGE to a page.  A layer with
+// a window keeps rows modulo `ring_rows` (a multiple of AF_PAGE, >= window).
+#include "common.cuh"
+
+#define AF_MAX_HD 512
+#define AF_HD_SLICES (AF_MAX_HD / 32)
+
+// ---------------------------------------------------------------- rope + cache write
+
+// One block per token.  Rotates the q and k heads of the packed row
+// [q heads | k heads | v heads] in place (32-bit angles and arithmetic) and,
+// when a cache is given, stores the rotated k and the v in the row's page.
+template <typename T>
+__global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
+                                  const int* __restrict__ seq_of_token, const int* __restrict__ slots,
+                                  const int* __restrict__ len_after, const float* __restrict__ inv_freq,
+                                  int nq, int nkv, int hd, int rot_dim, int pairing,
+                                  T* __restrict__ kcache, T* __restrict__ vcache,
+                                  const int* __restrict__ page_table, int max_pages, int ring_rows) {
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  T* row = qkv + (size_t)t * row_stride;
+  const int half = rot_dim / 2;
+  // rotate q and k
+  const int n_rot = (nq + nkv) * half;
+  for (int idx = threadIdx.x; idx < n_rot; idx += blockDim.x) {
+    const int h = idx / half, p = idx - h * half;
+    T* x = row + (size_t)h * hd;
+    const int i0 = pairing == AF_PAIR_HALF ? p : 2 * p;
+    const int i1 = pairing == AF_PAIR_HALF ? p + half : 2 * p + 1;
+    const float ang = (float)pos * inv_freq[p];
+    float s, c;
+    sincosf(ang, &s, &c);
+    const float a = to_f32(x[i0]), b = to_f32(x[i1]);
+    x[i0] = from_f32<T>(a * c - b * s);
+    x[i1] = from_f32<T>(b * c + a * s);
+  }
+  if (kcache == nullptr) return;
+  __syncthreads();
+  const int seq = seq_of_token[t];
+  const int slot = slots[seq];
+  if (slot < 0) return;  // padding row
+  int r = pos;
+  if (ring_rows > 0) {
+    // of the tokens of this step that share a ring row only the last is kept
+    if (pos + ring_rows < len_after[seq]) return;
+    r = pos % ring_rows;
+  }
+  const int page = page_table[(size_t)slot * max_pages + r / AF_PAGE];
+  const int in_page = r % AF_PAGE;
+  const T* k = row + (size_t)nq * hd;
+  const T* v = k + (size_t)nkv * hd;
+  for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
+    const int h = idx / hd, d = idx - h * hd;
+    const size_t dst = (((size_t)page * nkv + h) * AF_PAGE + in_page) * hd + d;
+    kcache[dst] = k[idx];
+    vcache[dst] = v[idx];
+  }
+}
+
+AF_EXPORT int af_rope_cache_write(void* qkv, int dtype, int row_stride, const int* positions,
+                                  const int* seq_of_token, const int* slots, const int* len_after,
+                                  const float* inv_freq, int n_tokens, int nq, int nkv, int hd,
+                                  int rot_dim, int pairing, void* kcache, void* vcache,
+                                  const int* page_table, int max_pages, int ring_rows,
+                                  cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  AF_REQUIRE(n_tokens > 0 && nq > 0 && nkv > 0 && hd > 0, "af_rope_cache_write: bad sizes");
+  AF_REQUIRE(rot_dim >= 0 && rot_dim <= hd && rot_dim % 2 == 0,
+             "af_rope_cache_write: rotary dim %d must be even and <= head_dim %d", rot_dim, hd);
+  AF_REQUIRE(pairing == AF_PAIR_HALF || pairing == AF_PAIR_ADJACENT, "af_rope_cache_write: pairing");
+  AF_REQUIRE(ring_rows % AF_PAGE == 0, "af_rope_cache_write: ring rows %d not whole pages", ring_rows);
+  AF_REQUIRE((kcache == nullptr) == (vcache == nullptr), "af_rope_cache_write: k and v cache");
+  AF_DISPATCH_DTYPE(dtype, T,
+                    rope_cache_kernel<T><<<n_tokens, 256, 0, stream>>>(
+                        (T*)qkv, row_stride, positions, seq_of_token, slots, len_after, inv_freq, nq,
+                        nkv, hd, rot_dim, pairing, (T*)kcache, (T*)vcache, page_table, max_pages,
+                        ring_rows));
+  AF_CHECK_LAUNCH("af_rope_cache_write");
+}
+
+// ---------------------------------------------------------------- plain attention
+
+// Online-softmax state of one (query, head) held by a warp: lane l owns the
+// elements l, l + 32, ... of the head.
+struct WarpAttn {
+  float q[AF_HD_SLICES];
+  float o[AF_HD_SLICES];
+  float m, l;
+};
+
+template <typename T>
+__device__ __forceinline__ void attn_load_q(WarpAttn& st, const T* q, int hd, int lane) {
+#pragma unroll
+  for (int e = 0; e < AF_HD_SLICES; ++e) {
+    const int d = lane + 32 * e;
+    st.q[e] = d < hd ? to_f32(q[d]) : 0.f;
+    st.o[e] = 0.f;
+  }
+  st.m = -INFINITY;
+  st.l = 0.f;
+}
+
+template <typename T>
+__device__ __forceinline__ void attn_key(WarpAttn& st, const T* k, const T* v, int hd, int lane,
+                                         float scale, float cap) {
+  float dot = 0.f;
+#pragma unroll
+  for (int e = 0; e < AF_HD_SLICES; ++e) {
+    const int d = lane + 32 * e;
+    if (d < hd) dot += st.q[e] * to_f32(k[d]);
+  }
+  dot = warp_sum(dot);
+  const float s = softcap_f32(dot * scale, cap);
+  const float m_new = fmaxf(st.m, s);
+  const float corr = expf(st.m - m_new);  // exp(-inf) = 0 on the first key
+  const float p = expf(s - m_new);
+  st.l = st.l * corr + p;
+#pragma unroll
+  for (int e = 0; e < AF_HD_SLICES; ++e) {
+    const int d = lane + 32 * e;
+    if (d < hd) st.o[e] = st.o[e] * corr + p * to_f32(v[d]);
+  }
+  st.m = m_new;
+}
+
+template <typename T>
+__device__ __forceinline__ void attn_store(const WarpAttn& st, T* out, int hd, int lane) {
+  const float inv = st.l > 0.f ? 1.f / st.l : 0.f;
+#pragma unroll
+  for (int e = 0; e < AF_HD_SLICES; ++e) {
+    const int d = lane + 32 * e;
+    if (d < hd) out[d] = from_f32<T>(st.o[e] * inv);
+  }
+}
+
+// Prompts that start at position 0: keys and values are the step's own rows.
+// Warp w of the grid handles (token, head) = (w / nq, w % nq).
+template <typename T>
+__global__ void attn_prefill_plain_kernel(T* __restrict__ out, int out_stride, const T* __restrict__ q,
+                                          int q_stride, const T* __restrict__ k, int k_stride,
+                                          const T* __restrict__ v, int v_stride,
+                                          const int* __restrict__ positions,
+                                          int n_tokens, int nq, int nkv, int hd, float scale, float cap,
+                                          int window) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)n_tokens * nq) return;
+  const int t = (int)(w / nq), h = (int)(w % nq);
+  const int g = h / (nq / nkv);
+  const int pos = positions[t];          // position inside its sequence
+  const int first_row = t - pos;         // row of the sequence's position 0
+  WarpAttn st;
+  attn_load_q(st, q + (size_t)t * q_stride + (size_t)h * hd, hd, lane);
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  for (int j = lo; j <= pos; ++j) {
+    const size_t r = (size_t)(first_row + j);
+    attn_key(st, k + r * k_stride + (size_t)g * hd, v + r * v_stride + (size_t)g * hd, hd, lane, scale,
+             cap);
+  }
+  attn_store(st, out + (size_t)t * out_stride + (size_t)h * hd, hd, lane);
+}
+
+AF_EXPORT int af_attn_prefill_plain(void* out, int out_stride, const void* q, int q_stride,
+                                    const void* k, int k_stride, const void* v, int v_stride, int dtype,
+                                    const int* positions, int n_tokens, int nq, int nkv, int hd,
+                                    float scale, float cap, int window, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  AF_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "af_attn_prefill_plain: heads %d, groups %d", nq, nkv);
+  AF_REQUIRE(hd > 0 && hd <= AF_MAX_HD, "af_attn_prefill_plain: head_dim %d beyond %d", hd, AF_MAX_HD);
+  const long long warps = (long long)n_tokens * nq;
+  const int wpb = 4;
+  const long long blocks = (warps + wpb - 1) / wpb;
+  AF_REQUIRE(blocks < (1ll << 31), "af_attn_prefill_plain: too many rows");
+  AF_DISPATCH_DTYPE(dtype, T,
+                    attn_prefill_plain_kernel<T><<<(unsigned)blocks, wpb * 32, 0, stream>>>(
+                        (T*)out, out_stride, (const T*)q, q_stride, (const T*)k, k_stride, (const T*)v,
+                        v_stride, positions, n_tokens, nq, nkv, hd, scale, cap, window));
+  AF_CHECK_LAUNCH("af_attn_prefill_plain");
+}
+
+// One new token per sequence: keys and values come from the cache pages.
+// `lens[b]` counts the new token, which the cache holds already.
+template <typename T>
+__global__ void attn_decode_plain_kernel(T* __restrict__ out, int out_stride, const T* __restrict__ q,
+                                         int q_stride, const T* __restrict__ kcache,
+                                         const T* __restrict__ vcache, const int* __restrict__ page_table,
+                                         int max_pages, const int* __restrict__ slots,
+                                         const int* __restrict__ lens, int batch, int nq, int nkv, int hd,
+                                         float scale, float cap, int window, int ring_rows) {
+  const int lane = threadIdx.x & 31;
+  const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (w >= (long long)batch * nq) return;
+  const int b = (int)(w / nq), h = (int)(w % nq);
+  const int g = h / (nq / nkv);
+  const int slot = slots[b];
+  T* o = out + (size_t)b * out_stride + (size_t)h * hd;
+  if (slot < 0) {  // padding row
+    for (int d = lane; d < hd; d += 32) o[d] = from_f32<T>(0.f);
+    return;
+  }
+  const int len = lens[b];
+  const int pos = len - 1;
+  WarpAttn st;
+  attn_load_q(st, q + (size_t)b * q_stride + (size_t)h * hd, hd, lane);
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const int* pt = page_table + (size_t)slot * max_pages;
+  for (int j = lo; j <= pos; ++j) {
+    const int r = ring_rows > 0 ? j % ring_rows : j;
+    const size_t base = (((size_t)pt[r / AF_PAGE] * nkv + g) * AF_PAGE + r % AF_PAGE) * hd;
+    attn_key(st, kcache + base, vcache + base, hd, lane, scale, cap);
+  }
+  attn_store(st, o, hd, lane);
+}
+
+AF_EXPORT int af_attn_decode_plain(void* out, int out_stride, const void* q, int q_stride,
+                                   const void* kcache, const void* vcache, int dtype,
+                                   const int* page_table, int max_pages, const int* slots,
+                                   const int* lens, int batch, int nq, int nkv, int hd, float scale,
+                                   float cap, int window, int ring_rows, cudaStream_t stream) {
+  if (batch == 0) return 0;
+  AF_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "af_attn_decode_plain: heads %d, groups %d", nq, nkv);
+  AF_REQUIRE(hd > 0 && hd <= AF_MAX_HD, "af_attn_decode_plain: head_dim %d beyond %d", hd, AF_MAX_HD);
+  AF_REQUIRE(ring_rows % AF_PAGE == 0 && (ring_rows == 0 || window > 0) && (window <= ring_rows || ring_rows == 0),
+             "af_attn_decode_plain: window %d, ring rows %d", window, ring_rows);
+  const long long warps = (long long)batch * nq;
+  const int wpb = 4;
+  const long long blocks = (warps + wpb - 1) / wpb;
+  AF_DISPATCH_DTYPE(dtype, T,
+                    attn_decode_plain_kernel<T><<<(unsigned)blocks, wpb * 32, 0, stream>>>(
+                        (T*)out, out_stride, (const T*)q, q_stride, (const T*)kcache, (const T*)vcache,
+                        page_table, max_pages, slots, lens, batch, nq, nkv, hd, scale, cap, window,
+                        ring_rows));
+  AF_CHECK_LAUNCH("af_attn_decode_plain");
+}

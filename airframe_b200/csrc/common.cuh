@@ -1,0 +1,100 @@
+// Shared helpers of the sm_100a kernel library: dtype codes, conversions,
+// reductions and the error channel of the C entry points.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+#include <stdio.h>
+
+#define AF_EXPORT extern "C" __attribute__((visibility("default")))
+
+// dtype codes of the C interface
+enum AfDtype { AF_F32 = 0, AF_BF16 = 1 };
+
+// activation codes of the gated feed-forward
+enum AfAct { AF_ACT_GELU_TANH = 0, AF_ACT_SILU = 1 };
+
+// rotary pairings
+enum AfPairing { AF_PAIR_HALF = 0, AF_PAIR_ADJACENT = 1 };
+
+// Tokens per cache page.  A sequence holds whole pages.
+#define AF_PAGE 64
+
+// Records a message that af_last_error() returns and yields the error code.
+int af_fail(int code, const char* fmt, ...);
+
+#define AF_REQUIRE(cond, ...)                     \
+  do {                                            \
+    if (!(cond)) return af_fail(-1, __VA_ARGS__); \
+  } while (0)
+
+#define AF_CHECK_LAUNCH(name)                                                    \
+  do {                                                                           \
+    cudaError_t e__ = cudaGetLastError();                                        \
+    if (e__ != cudaSuccess)                                                      \
+      return af_fail((int)e__, "%s: launch failed: %s", name, cudaGetErrorString(e__)); \
+    return 0;                                                                    \
+  } while (0)
+
+template <typename T>
+__device__ __forceinline__ float to_f32(T v);
+template <>
+__device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+template <typename T>
+__device__ __forceinline__ T from_f32(float v);
+template <>
+__device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.
+// `scratch` holds 33 floats of shared memory.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarp = (blockDim.x + 31) >> 5;
+  v = warp_sum(v);
+  __syncthreads();
+  if (lane == 0) scratch[warp] = v;
+  __syncthreads();
+  if (warp == 0) {
+    float t = lane < nwarp ? scratch[lane] : 0.f;
+    t = warp_sum(t);
+    if (lane == 0) scratch[32] = t;
+  }
+  __syncthreads();
+  return scratch[32];
+}
+
+// cap * tanh(x / cap) for cap > 0, x otherwise (exact tanhf).
+__device__ __forceinline__ float softcap_f32(float x, float cap) {
+  return cap > 0.f ? cap * tanhf(x / cap) : x;
+}
+
+// Dispatch on a dtype code: DT becomes float or __nv_bfloat16.
+#define AF_DISPATCH_DTYPE(code, DT, ...)                      \
+  do {                                                        \
+    if ((code) == AF_F32) {                                   \
+      using DT = float;                                       \
+      __VA_ARGS__;                                            \
+    } else if ((code) == AF_BF16) {                           \
+      using DT = __nv_bfloat16;                               \
+      __VA_ARGS__;                                            \
+    } else {                                                  \
+      return af_fail(-1, "unsupported dtype code %d", (code)); \
+    }                                                         \
+  } while (0)

@@ -1,0 +1,206 @@
+// Embedding gather, RMS norms (plain and fused with the residual sum), the
+// gated activation, logit softcap, and the library's error channel.
+//
+// All statistics, the residual sum and the (offset + w) factor are 32-bit.
+// The residual stream is float in both precisions; the normalised rows that
+// feed matrix products are in the compute dtype.
+#include <stdarg.h>
+#include <string.h>
+
+#include "common.cuh"
+
+static thread_local char g_error[512] = "";
+
+int af_fail(int code, const char* fmt, ...) {
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(g_error, sizeof(g_error), fmt, ap);
+  va_end(ap);
+  return code == 0 ? -1 : code;
+}
+
+AF_EXPORT const char* af_last_error() { return g_error; }
+
+AF_EXPORT int af_abi_version() { return 1; }
+
+// ---------------------------------------------------------------- embedding
+
+template <typename TW>
+__global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ table,
+                             const int* __restrict__ ids, int hidden, int vocab, float scale) {
+  const int t = blockIdx.x;
+  int id = ids[t];
+  // ids are validated on the host; a bad one yields zeros rather than a wild read
+  const bool ok = id >= 0 && id < vocab;
+  const TW* row = table + (size_t)(ok ? id : 0) * hidden;
+  float* o = out + (size_t)t * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = ok ? to_f32(row[i]) * scale : 0.f;
+}
+
+AF_EXPORT int af_embed(float* out, const void* table, int table_dtype, const int* ids, int n_tokens,
+                       int hidden, int vocab, float scale, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  AF_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "af_embed: bad sizes");
+  AF_DISPATCH_DTYPE(table_dtype, TW,
+                    embed_kernel<TW><<<n_tokens, 256, 0, stream>>>(out, (const TW*)table, ids, hidden,
+                                                                  vocab, scale));
+  AF_CHECK_LAUNCH("af_embed");
+}
+
+// ---------------------------------------------------------------- RMS norm
+
+// y[r] = x[src(r)] * rsqrt(mean(x^2) + eps) * (offset + w); rows gathered by
+// `rows` when given (the final norm runs at the wanted positions only).
+template <typename TY>
+__global__ void rmsnorm_kernel(TY* __restrict__ y, const float* __restrict__ x,
+                               const float* __restrict__ w, const int* __restrict__ rows, int hidden,
+                               float eps, float offset) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const float* xr = x + (size_t)(rows ? rows[r] : r) * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = xr[i];
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps);
+  TY* yr = y + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    yr[i] = from_f32<TY>(xr[i] * inv * (offset + w[i]));
+}
+
+AF_EXPORT int af_rmsnorm(void* y, int y_dtype, const float* x, const float* w, const int* rows,
+                         int n_rows, int hidden, float eps, float offset, cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  AF_REQUIRE(n_rows > 0 && hidden > 0, "af_rmsnorm: bad sizes");
+  AF_DISPATCH_DTYPE(y_dtype, TY,
+                    rmsnorm_kernel<TY><<<n_rows, 256, 0, stream>>>((TY*)y, x, w, rows, hidden, eps,
+                                                                  offset));
+  AF_CHECK_LAUNCH("af_rmsnorm");
+}
+
+// x += norm(a) * (offset + w_post); then, when y is given,
+// y = norm(x) * (offset + w_next).  `a` may come as `n_parts` partial sums
+// (float, [n_parts, rows, hidden]) that are added in index order first.
+template <typename TA, typename TY>
+__global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__ a, int n_parts,
+                                   size_t part_stride, const float* __restrict__ w_post,
+                                   TY* __restrict__ y, const float* __restrict__ w_next, int hidden,
+                                   float eps_post, float eps_next, float offset) {
+  extern __shared__ float row[];  // hidden floats: a, then the new x
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const TA* ar = a + (size_t)r * hidden;
+  float ss = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = to_f32(ar[i]);
+    for (int p = 1; p < n_parts; ++p) v += to_f32(ar[(size_t)p * part_stride + i]);
+    row[i] = v;
+    ss += v * v;
+  }
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps_post);
+  float* xr = x + (size_t)r * hidden;
+  float ss2 = 0.f;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+    float v = xr[i] + row[i] * inv * (offset + w_post[i]);
+    xr[i] = v;
+    row[i] = v;
+    ss2 += v * v;
+  }
+  if (y == nullptr) return;
+  ss2 = block_sum(ss2, scratch);
+  const float inv2 = rsqrtf(ss2 / (float)hidden + eps_next);
+  TY* yr = y + (size_t)r * hidden;
+  for (int i = threadIdx.x; i < hidden; i += blockDim.x)
+    yr[i] = from_f32<TY>(row[i] * inv2 * (offset + w_next[i]));
+}
+
+AF_EXPORT int af_add_rmsnorm(float* x, const void* a, int a_dtype, int n_parts, long long part_stride,
+                             const float* w_post, void* y, int y_dtype, const float* w_next,
+                             int n_rows, int hidden, float eps_post, float eps_next, float offset,
+                             cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  AF_REQUIRE(n_rows > 0 && hidden > 0 && n_parts >= 1, "af_add_rmsnorm: bad sizes");
+  AF_REQUIRE(hidden * sizeof(float) <= 160 * 1024, "af_add_rmsnorm: hidden %d too wide", hidden);
+  AF_REQUIRE(n_parts == 1 || a_dtype == AF_F32, "af_add_rmsnorm: partial sums must be float");
+  const size_t smem = (size_t)hidden * sizeof(float);
+#define LAUNCH(TA, TY)                                                                          \
+  do {                                                                                          \
+    if (smem > 48 * 1024)                                                                       \
+      cudaFuncSetAttribute(add_rmsnorm_kernel<TA, TY>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
+                           (int)smem);                                                          \
+    add_rmsnorm_kernel<TA, TY><<<n_rows, 256, smem, stream>>>(                                  \
+        x, (const TA*)a, n_parts, (size_t)part_stride, w_post, (TY*)y, w_next, hidden, eps_post, \
+        eps_next, offset);                                                                      \
+  } while (0)
+  AF_DISPATCH_DTYPE(a_dtype, TA, AF_DISPATCH_DTYPE(y_dtype, TY, LAUNCH(TA, TY)));
+#undef LAUNCH
+  AF_CHECK_LAUNCH("af_add_rmsnorm");
+}
+
+// ---------------------------------------------------------------- gated activation
+
+__device__ __forceinline__ float act_f32(float g, int act) {
+  if (act == AF_ACT_GELU_TANH) {
+    const float u = 0.7978845608028654f * (g + 0.044715f * g * g * g);
+    return 0.5f * g * (1.f + tanhf(u));
+  }
+  return g / (1.f + expf(-g));
+}
+
+// out[m, i] = act(gu[m, i]) * gu[m, inter + i]
+template <typename T>
+__global__ void gated_act_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, int act) {
+  const int m = blockIdx.x;
+  const T* g = gu + (size_t)m * 2 * inter;
+  const T* u = g + inter;
+  T* o = out + (size_t)m * inter;
+  for (int i = blockIdx.y * blockDim.x + threadIdx.x; i < inter; i += gridDim.y * blockDim.x)
+    o[i] = from_f32<T>(act_f32(to_f32(g[i]), act) * to_f32(u[i]));
+}
+
+AF_EXPORT int af_gated_act(void* out, const void* gu, int dtype, int n_rows, int inter, int act,
+                           cudaStream_t stream) {
+  if (n_rows == 0) return 0;
+  AF_REQUIRE(n_rows > 0 && inter > 0, "af_gated_act: bad sizes");
+  AF_REQUIRE(act == AF_ACT_GELU_TANH || act == AF_ACT_SILU, "af_gated_act: unknown activation %d", act);
+  dim3 grid(n_rows, (inter + 255) / 256 < 64 ? (inter + 255) / 256 : 64);
+  AF_DISPATCH_DTYPE(dtype, T,
+                    gated_act_kernel<T><<<grid, 256, 0, stream>>>((T*)out, (const T*)gu, inter, act));
+  AF_CHECK_LAUNCH("af_gated_act");
+}
+
+// ---------------------------------------------------------------- residual sum
+
+template <typename T>
+__global__ void add_kernel(float* __restrict__ x, const T* __restrict__ a, size_t n) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    x[i] += to_f32(a[i]);
+}
+
+AF_EXPORT int af_add(float* x, const void* a, int a_dtype, long long n, cudaStream_t stream) {
+  if (n == 0) return 0;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  AF_DISPATCH_DTYPE(a_dtype, T, add_kernel<T><<<(int)blocks, 256, 0, stream>>>(x, (const T*)a, (size_t)n));
+  AF_CHECK_LAUNCH("af_add");
+}
+
+// ---------------------------------------------------------------- softcap
+
+__global__ void softcap_kernel(float* __restrict__ z, size_t n, float cap) {
+  for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
+       i += (size_t)gridDim.x * blockDim.x)
+    z[i] = softcap_f32(z[i], cap);
+}
+
+AF_EXPORT int af_softcap(float* z, long long n, float cap, cudaStream_t stream) {
+  if (n == 0 || cap <= 0.f) return 0;
+  long long blocks = (n + 255) / 256;
+  if (blocks > 148 * 16) blocks = 148 * 16;
+  softcap_kernel<<<(int)blocks, 256, 0, stream>>>(z, (size_t)n, cap);
+  AF_CHECK_LAUNCH("af_softcap");
+}

@@ -1,0 +1,220 @@
+"""Python face of the CUDA kernel library: one function per C entry point.
+
+Arguments are torch tensors on a CUDA device; each function checks device,
+dtype and layout, passes raw pointers and the current stream, and raises
+:class:`KernelError` with the library's message when a kernel refuses its
+sizes.  Nothing here computes on the host and nothing falls back to torch.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .csrc import KernelLibraryError, load_library
+from .kernels_const import PAGE
+
+F32, BF16 = 0, 1
+ACTIVATIONS = {"gelu_tanh": 0, "silu": 1}
+PAIRINGS = {"half": 0, "adjacent": 1}
+
+
+class KernelError(RuntimeError):
+    """A kernel refused its arguments or failed to launch."""
+
+
+def dtype_code(dtype: torch.dtype) -> int:
+    if dtype == torch.float32:
+        return F32
+    if dtype == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16, got {dtype}")
+
+
+def _lib():
+    return load_library()
+
+
+def _stream() -> c_void_p:
+    return c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t, name="tensor", dtype=None, allow_none=False) -> c_void_p:
+    if t is None:
+        if allow_none:
+            return c_void_p(0)
+        raise KernelError(f"{name} is required")
+    if not t.is_cuda:
+        raise KernelError(f"{name} must live on a CUDA device (there is no CPU implementation)")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+    return c_void_p(t.data_ptr())
+
+
+def _rows(t, name) -> int:
+    """Row stride in elements of a 2-D tensor whose rows are dense."""
+    if t.dim() != 2 or t.stride(1) != 1:
+        raise KernelError(f"{name} must be 2-D with dense rows, got shape {tuple(t.shape)} strides {t.stride()}")
+    return t.stride(0)
+
+
+def _check(code: int) -> None:
+    if code != 0:
+        msg = _lib().af_last_error().decode("utf-8", "replace")
+        raise KernelError(f"{msg} (code {code})")
+
+
+def require_cuda_tensor(t, name="tensor"):
+    if not t.is_cuda:
+        raise KernelError(f"{name} must live on a CUDA device")
+
+
+# ---------------------------------------------------------------- elementwise
+
+def embed(out, table, ids, scale: float) -> None:
+    """out[t] = table[ids[t]] * scale; out float32 [T, H]."""
+    T, H = out.shape
+    _check(_lib().af_embed(_ptr(out, "out", torch.float32), _ptr(table, "table"), c_int(dtype_code(table.dtype)),
+                           _ptr(ids, "ids", torch.int32), c_int(T), c_int(H), c_int(table.shape[0]),
+                           c_float(scale), _stream()))
+
+
+def rmsnorm(y, x, w, eps: float, offset: float, rows=None) -> None:
+    """y[r] = norm(x[rows[r]] or x[r]) * (offset + w); x, w float32."""
+    n, H = y.shape
+    if not (x.is_contiguous() and y.is_contiguous()):
+        raise KernelError("rmsnorm: tensors must be contiguous")
+    _check(_lib().af_rmsnorm(_ptr(y, "y"), c_int(dtype_code(y.dtype)), _ptr(x, "x", torch.float32),
+                             _ptr(w, "w", torch.float32), _ptr(rows, "rows", torch.int32, allow_none=True),
+                             c_int(n), c_int(H), c_float(eps), c_float(offset), _stream()))
+
+
+def add_rmsnorm(x, a, w_post, eps_post: float, offset: float, y=None, w_next=None, eps_next: float = 0.0,
+                n_parts: int = 1) -> None:
+    """x += norm(a) * (offset + w_post); if y: y = norm(x) * (offset + w_next).
+    With ``n_parts`` > 1, ``a`` is float32 [n_parts, rows, H] partial sums."""
+    n, H = x.shape
+    if not (x.is_contiguous() and a.is_contiguous() and (y is None or y.is_contiguous())):
+        raise KernelError("add_rmsnorm: tensors must be contiguous")
+    part_stride = n * H
+    _check(_lib().af_add_rmsnorm(_ptr(x, "x", torch.float32), _ptr(a, "a"), c_int(dtype_code(a.dtype)),
+                                 c_int(n_parts), c_longlong(part_stride), _ptr(w_post, "w_post", torch.float32),
+                                 _ptr(y, "y", allow_none=True), c_int(dtype_code(y.dtype) if y is not None else F32),
+                                 _ptr(w_next, "w_next", torch.float32, allow_none=True),
+                                 c_int(n), c_int(H), c_float(eps_post), c_float(eps_next), c_float(offset),
+                                 _stream()))
+
+
+def gated_act(out, gu, activation: str) -> None:
+    """out[m, i] = act(gu[m, i]) * gu[m, I + i]."""
+    n, inter = out.shape
+    if gu.shape != (n, 2 * inter) or not (gu.is_contiguous() and out.is_contiguous()) or gu.dtype != out.dtype:
+        raise KernelError("gated_act: gu must be contiguous [rows, 2 * inter] of out's dtype")
+    if activation not in ACTIVATIONS:
+        raise KernelError(f"gated_act: unknown activation '{activation}' (known: {sorted(ACTIVATIONS)})")
+    _check(_lib().af_gated_act(_ptr(out), _ptr(gu), c_int(dtype_code(out.dtype)), c_int(n), c_int(inter),
+                               c_int(ACTIVATIONS[activation]), _stream()))
+
+
+def softcap_(z, cap: float) -> None:
+    if not z.is_contiguous():
+        raise KernelError("softcap_: tensor must be contiguous")
+    _check(_lib().af_softcap(_ptr(z, "z", torch.float32), c_longlong(z.numel()), c_float(cap), _stream()))
+
+
+# ---------------------------------------------------------------- matrix product
+
+def gemm_plain(out, x, w, cap: float = 0.0) -> None:
+    """out[M, N] = x[M, K] @ w[N, K]^T on the CUDA cores, 32-bit accumulation;
+    x and w share a dtype, out is that dtype or float32."""
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or out.shape != (M, N) or x.dtype != w.dtype:
+        raise KernelError(f"gemm_plain: shapes {tuple(x.shape)} x {tuple(w.shape)}^T -> {tuple(out.shape)}")
+    _check(_lib().af_gemm_plain(_ptr(out), c_int(dtype_code(out.dtype)), c_int(_rows(out, "out")),
+                                _ptr(x), c_int(_rows(x, "x")), _ptr(w), c_int(_rows(w, "w")),
+                                c_int(dtype_code(x.dtype)), c_int(M), c_int(N), c_int(K), c_float(cap),
+                                _stream()))
+
+
+# ---------------------------------------------------------------- attention
+
+def rope_cache_write(qkv, positions, inv_freq, nq: int, nkv: int, hd: int, rot_dim: int, pairing: str,
+                     seq_of_token=None, slots=None, len_after=None, kcache=None, vcache=None,
+                     page_table=None, ring_rows: int = 0) -> None:
+    """Rotate the q and k heads of the packed rows [q | k | v] in place and,
+    when a cache is given, store k and v at each token's row of its page."""
+    T = qkv.shape[0]
+    if qkv.shape[1] != (nq + 2 * nkv) * hd:
+        raise KernelError(f"rope_cache_write: row width {qkv.shape[1]} is not (nq + 2 nkv) * head_dim")
+    if pairing not in PAIRINGS:
+        raise KernelError(f"rope_cache_write: unknown pairing '{pairing}'")
+    if inv_freq.numel() != rot_dim // 2:
+        raise KernelError("rope_cache_write: inv_freq must hold rot_dim / 2 values")
+    max_pages = 0
+    if kcache is not None:
+        if kcache.dtype != qkv.dtype or vcache.dtype != qkv.dtype:
+            raise KernelError("rope_cache_write: cache dtype differs from the activations'")
+        if tuple(kcache.shape[1:]) != (nkv, PAGE, hd) or not kcache.is_contiguous() or not vcache.is_contiguous():
+            raise KernelError(f"rope_cache_write: cache pages must be [pages, {nkv}, {PAGE}, {hd}]")
+        max_pages = page_table.shape[1]
+    _check(_lib().af_rope_cache_write(
+        _ptr(qkv), c_int(dtype_code(qkv.dtype)), c_int(_rows(qkv, "qkv")), _ptr(positions, "positions", torch.int32),
+        _ptr(seq_of_token, "seq_of_token", torch.int32, allow_none=True),
+        _ptr(slots, "slots", torch.int32, allow_none=True),
+        _ptr(len_after, "len_after", torch.int32, allow_none=True),
+        _ptr(inv_freq, "inv_freq", torch.float32), c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(rot_dim),
+        c_int(PAIRINGS[pairing]), _ptr(kcache, allow_none=True), _ptr(vcache, allow_none=True),
+        _ptr(page_table, "page_table", torch.int32, allow_none=True), c_int(max_pages), c_int(ring_rows),
+        _stream()))
+
+
+def attn_prefill_plain(out, q, k, v, positions, nq: int, nkv: int, hd: int, scale: float, cap: float,
+                       window: int) -> None:
+    """Attention of prompts that start at position 0 over the step's own keys.
+    q [T, nq*hd], k/v [T, nkv*hd] are row views (any row stride)."""
+    T = q.shape[0]
+    _check(_lib().af_attn_prefill_plain(
+        _ptr(out), c_int(_rows(out, "out")), _ptr(q), c_int(_rows(q, "q")), _ptr(k), c_int(_rows(k, "k")),
+        _ptr(v), c_int(_rows(v, "v")), c_int(dtype_code(q.dtype)), _ptr(positions, "positions", torch.int32),
+        c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_float(cap), c_int(window), _stream()))
+
+
+def attn_decode_plain(out, q, kcache, vcache, page_table, slots, lens, nq: int, nkv: int, hd: int,
+                      scale: float, cap: float, window: int, ring_rows: int) -> None:
+    """Attention of one new token per sequence over the cache pages."""
+    B = q.shape[0]
+    if kcache.dtype != q.dtype:
+        raise KernelError("attn_decode_plain: cache dtype differs from the activations'")
+    _check(_lib().af_attn_decode_plain(
+        _ptr(out), c_int(_rows(out, "out")), _ptr(q), c_int(_rows(q, "q")), _ptr(kcache), _ptr(vcache),
+        c_int(dtype_code(q.dtype)), _ptr(page_table, "page_table", torch.int32), c_int(page_table.shape[1]),
+        _ptr(slots, "slots", torch.int32), _ptr(lens, "lens", torch.int32), c_int(B), c_int(nq), c_int(nkv),
+        c_int(hd), c_float(scale), c_float(cap), c_int(window), c_int(ring_rows), _stream()))
+
+
+def add_(x, a) -> None:
+    """x += a; x float32, a float32 or bfloat16, same shape."""
+    if x.shape != a.shape or not (x.is_contiguous() and a.is_contiguous()):
+        raise KernelError("add_: tensors must be contiguous and of one shape")
+    _check(_lib().af_add(_ptr(x, "x", torch.float32), _ptr(a), c_int(dtype_code(a.dtype)),
+                         c_longlong(x.numel()), _stream()))
+
+
+def gemm_bf16_supported(M, N, K, x, w, out) -> bool:
+    return False
+
+
+def attn_prefill(out, q, k, v, batch, nq, nkv, hd, scale, cap, window) -> None:
+    """Attention of a prefill step: picks the kernel."""
+    attn_prefill_plain(out, q, k, v, batch.positions, nq, nkv, hd, scale, cap, window)
+
+
+def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window) -> None:
+    """Attention of a decode step over the cache: picks the kernel."""
+    attn_decode_plain(out, q, kv.k, kv.v, kv.page_table, batch.slots, batch.len_after, nq, nkv, hd,
+                      scale, cap, window, kv.ring_rows)
+
+
+__all__ = [n for n in dir() if not n.startswith("_")]

@@ -1,0 +1,84 @@
+"""Grouped-query attention over the paged cache, with score scale, softcap
+and an optional window.
+
+score = softcap(q.k * scale), softmax over the visible keys in 32 bits, times
+v; query head h reads key/value head h // (heads / kv_heads).  Reference:
+``src/backend/bindless/sh_layer_v1.wgsl:662-754`` (scale ``:726``, cap
+``:727-730``, online softmax ``:739-753``, head mapping ``:673,677``), the
+projections ``:499-530`` and ``:775-804``.  The reference fixes the scale at
+head_dim^-0.5 and has no window; both are parameters here.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..config.base import ConfigError, PartSpec
+from ..weights.loader import WeightDecl
+from .base import KVNeed, Mixer, build_part, register_part
+from .linear import linear
+
+
+@register_part("mixer", "attention")
+class Attention(Mixer):
+    """Parameters: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``,
+    ``scale``, ``softcap`` (0 = off), ``window`` (None = all keys), ``position``
+    (a PartSpec of category ``position``), ``q_weight``/``k_weight``/``v_weight``/
+    ``o_weight`` (tensor names)."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden = int(self.param("hidden_size"))
+        self.nq = int(self.param("num_heads"))
+        self.nkv = int(self.param("num_kv_heads"))
+        self.hd = int(self.param("head_dim"))
+        self.scale = float(self.param("scale"))
+        self.softcap = float(self.params.get("softcap") or 0.0)
+        w = self.params.get("window")
+        self.window = int(w) if w else None
+        if self.nq % self.nkv:
+            raise ConfigError(f"attention: {self.nq} heads are not a multiple of {self.nkv} kv heads")
+        pos = self.params.get("position") or PartSpec("none")
+        self.position = build_part("position", pos, ctx)
+        self.names = [self.param(k) for k in ("q_weight", "k_weight", "v_weight", "o_weight")]
+        self.w_qkv = None
+        self.w_o = None
+
+    def kv_need(self):
+        return KVNeed(self.nkv, self.hd, self.window)
+
+    def weight_decls(self):
+        q, k, v, o = self.names
+        return [WeightDecl(q, (self.nq * self.hd, self.hidden)),
+                WeightDecl(k, (self.nkv * self.hd, self.hidden)),
+                WeightDecl(v, (self.nkv * self.hd, self.hidden)),
+                WeightDecl(o, (self.hidden, self.nq * self.hd)),
+                *self.position.weight_decls()]
+
+    def load(self, weights):
+        q, k, v, o = self.names
+        dt = self.ctx.compute_dtype
+        # one matrix product for q, k and v: rows [q heads | k heads | v heads]
+        self.w_qkv = torch.cat([weights[q], weights[k], weights[v]], dim=0).to(dt).contiguous()
+        self.w_o = weights[o].to(dt).contiguous()
+        self.position.load(weights)
+
+    def forward(self, x, batch, view):
+        nq, nkv, hd = self.nq, self.nkv, self.hd
+        qkv = linear(x, self.w_qkv)
+        kv = view.kv
+        self.position.encode_and_store(qkv, batch, nq, nkv, hd, kv if view.writes else None)
+        q = qkv[:, : nq * hd]
+        k = qkv[:, nq * hd: (nq + nkv) * hd]
+        v = qkv[:, (nq + nkv) * hd:]
+        ctx = torch.empty(x.shape[0], nq * hd, dtype=x.dtype, device=x.device)
+        window = self.window or 0
+        if batch.is_prefill:
+            if not view.writes:
+                k, v = batch.step_kv[view.cache_id]
+            elif view.keep_step_kv:
+                batch.step_kv[view.cache_id] = (k.clone(), v.clone())
+            kernels.attn_prefill(ctx, q, k, v, batch, nq, nkv, hd, self.scale, self.softcap, window)
+        else:
+            kernels.attn_decode(ctx, q, kv, batch, nq, nkv, hd, self.scale, self.softcap, window)
+        return linear(ctx, self.w_o)

@@ -1,0 +1,190 @@
+"""The parts a layer is put together from, and their registry.
+
+Five categories: ``norm``, ``position``, ``mixer``, ``feed_forward`` and
+``block`` (the arrangement of the other four in a layer), plus ``embedding``
+and ``head`` at the model's ends.  A part is built from the parameters of its
+:class:`~airframe_b200.config.PartSpec` alone: it takes every size and
+constant from there and does not know which model it is in.  New kinds are
+added with :func:`register_part`; nothing else has to change.
+
+Reference: the parameterised operations of ``src/ops`` behind
+``OpDispatcher`` (``src/ops/dispatch.rs:11-199``).
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Optional
+
+import torch
+
+from ..config.base import ConfigError, PartSpec
+
+CATEGORIES = ("norm", "position", "mixer", "feed_forward", "block", "embedding", "head")
+_REGISTRY: dict = {c: {} for c in CATEGORIES}
+
+
+def register_part(category: str, kind: str):
+    """Class decorator: make ``kind`` buildable in ``category``."""
+    if category not in _REGISTRY:
+        raise ValueError(f"unknown part category '{category}' (known: {CATEGORIES})")
+
+    def deco(cls):
+        _REGISTRY[category][kind] = cls
+        cls.category = category
+        cls.kind = kind
+        return cls
+
+    return deco
+
+
+def unregister_part(category: str, kind: str) -> None:
+    _REGISTRY[category].pop(kind, None)
+
+
+def known_parts(category: str) -> list:
+    return sorted(_REGISTRY[category])
+
+
+@dataclass
+class BuildContext:
+    """What every part is told besides its own parameters."""
+    compute_dtype: torch.dtype      # bfloat16 or float32: activations, matrices, cache
+    device: torch.device
+
+
+def build_part(category: str, spec: PartSpec, ctx: BuildContext, **children):
+    kinds = _REGISTRY[category]
+    if spec.kind not in kinds:
+        raise ConfigError(f"no {category} part of kind '{spec.kind}' (known: {sorted(kinds)})")
+    return kinds[spec.kind](dict(spec.params), ctx, **children)
+
+
+# --------------------------------------------------------------------------
+# what the cache is asked for
+# --------------------------------------------------------------------------
+
+@dataclass(frozen=True)
+class KVNeed:
+    """Keys and values per token.  ``window`` None: all of them are kept;
+    otherwise the last ``window`` rows (a ring)."""
+    num_kv_heads: int
+    head_dim: int
+    window: Optional[int] = None
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """Per-sequence state of fixed size: one tensor of ``shape`` per sequence,
+    zero when the sequence starts."""
+    shape: tuple
+    dtype: str = "float32"
+
+
+# --------------------------------------------------------------------------
+# interfaces
+# --------------------------------------------------------------------------
+
+class Part:
+    """Base of all parts.
+
+    ``weight_decls`` lists the tensors the part reads from the model folder,
+    ``load`` receives name -> tensor (already on the device, bfloat16, or
+    float32 for tensors stored so or on the 32-bit path) and keeps what it
+    needs in the layout its kernels want.
+    """
+    category = ""
+    kind = ""
+
+    def __init__(self, params: dict, ctx: BuildContext):
+        self.params = params
+        self.ctx = ctx
+
+    def weight_decls(self) -> list:
+        return []
+
+    def load(self, weights: dict) -> None:
+        pass
+
+    def param(self, key: str):
+        if key not in self.params:
+            raise ConfigError(f"{self.category} part '{self.kind}' needs parameter '{key}'")
+        return self.params[key]
+
+
+class Norm(Part):
+    """x is the float32 residual stream [rows, H]."""
+
+    def forward(self, x, out_dtype, rows=None):
+        """norm(x) (of the listed rows when ``rows`` is given) in ``out_dtype``."""
+        raise NotImplementedError
+
+    def add_normed(self, x, a, then=None, out_dtype=None):
+        """x += norm(a) in place (32-bit sum).  With ``then`` (another norm),
+        also returns then.forward(x) in ``out_dtype``."""
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    """Applied by a mixer to its packed query/key/value rows."""
+
+    def encode_and_store(self, qkv, batch, nq: int, nkv: int, hd: int, kv) -> None:
+        """Encode positions into the q and k heads of ``qkv`` ([T, (nq + 2 nkv) hd],
+        in place) and, if ``kv`` (a cache view that is written) is given, store
+        k and v in the cache."""
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    """Mixes information between the positions of a sequence."""
+
+    def kv_need(self) -> Optional[KVNeed]:
+        return None
+
+    def state_need(self) -> Optional[StateNeed]:
+        return None
+
+    def forward(self, x, batch, view):
+        """x [T, H] in the compute dtype (normalised) -> [T, H] in the compute
+        dtype.  ``batch`` is the :class:`~airframe_b200.engine.batch.StepBatch`,
+        ``view`` the layer's :class:`~airframe_b200.cache.LayerCacheView`."""
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, x, batch):
+        """x [T, H] compute dtype -> [T, H] compute dtype."""
+        raise NotImplementedError
+
+
+class Block(Part):
+    """The arrangement of norms, mixer and feed-forward around the residual stream."""
+
+    roles: tuple = ()
+
+    def __init__(self, params, ctx, mixer: Mixer, feed_forward: FeedForward, norms: dict):
+        super().__init__(params, ctx)
+        missing = [r for r in self.roles if r not in norms]
+        if missing:
+            raise ConfigError(f"block '{self.kind}' needs norms for {missing}")
+        self.mixer, self.feed_forward, self.norms = mixer, feed_forward, norms
+
+    def children(self):
+        return [self.mixer, self.feed_forward, *self.norms.values()]
+
+    def weight_decls(self):
+        return [d for c in self.children() for d in c.weight_decls()]
+
+    def load(self, weights):
+        for c in self.children():
+            c.load(weights)
+
+    def first_norm(self):
+        """The norm this block applies to x first, or None.  The layer before
+        may compute it in its last kernel and pass the result as ``normed``."""
+        return None
+
+    def forward(self, x, batch, view, normed=None, next_pre=None):
+        """Run the layer on the float32 residual stream x [T, H] in place.
+        Returns next_pre.forward(x) in the compute dtype when ``next_pre`` (the
+        next layer's first norm) is given, else None."""
+        raise NotImplementedError

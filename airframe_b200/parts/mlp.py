@@ -1,0 +1,50 @@
+"""Gated feed-forward: f = W_down (act(W_gate x) * (W_up x)).
+
+Reference: ``src/backend/bindless/sh_layer_v1.wgsl:1024-1070`` (gate and up),
+``:1079`` (tanh-GELU), ``:1082`` (SiLU), ``:1104-1140`` (down).  The reference
+picks the activation by a proxy (softcap > 0); here it is a parameter.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..config.base import ConfigError
+from ..weights.loader import WeightDecl
+from .base import FeedForward, register_part
+from .linear import linear
+
+
+@register_part("feed_forward", "gated_mlp")
+class GatedMlp(FeedForward):
+    """Parameters: ``hidden_size``, ``intermediate_size``, ``activation``
+    (``gelu_tanh`` or ``silu``), ``gate_weight``/``up_weight``/``down_weight``."""
+
+    def __init__(self, params, ctx):
+        super().__init__(params, ctx)
+        self.hidden = int(self.param("hidden_size"))
+        self.inter = int(self.param("intermediate_size"))
+        self.activation = self.param("activation")
+        if self.activation not in kernels.ACTIVATIONS:
+            raise ConfigError(f"gated_mlp: unknown activation '{self.activation}' "
+                              f"(known: {sorted(kernels.ACTIVATIONS)})")
+        self.names = [self.param(k) for k in ("gate_weight", "up_weight", "down_weight")]
+        self.w_gu = None
+        self.w_down = None
+
+    def weight_decls(self):
+        g, u, d = self.names
+        return [WeightDecl(g, (self.inter, self.hidden)), WeightDecl(u, (self.inter, self.hidden)),
+                WeightDecl(d, (self.hidden, self.inter))]
+
+    def load(self, weights):
+        g, u, d = self.names
+        dt = self.ctx.compute_dtype
+        self.w_gu = torch.cat([weights[g], weights[u]], dim=0).to(dt).contiguous()
+        self.w_down = weights[d].to(dt).contiguous()
+
+    def forward(self, x, batch):
+        gu = linear(x, self.w_gu)
+        h = torch.empty(x.shape[0], self.inter, dtype=x.dtype, device=x.device)
+        kernels.gated_act(h, gu, self.activation)
+        return linear(h, self.w_down)

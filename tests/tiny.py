@@ -1,0 +1,49 @@
+"""Tiny Gemma-2 configurations for the tests.  A and B differ in every size
+and option; C has sizes the bfloat16 tensor-core kernels take."""
+from __future__ import annotations
+
+import tempfile
+from pathlib import Path
+
+TINY_A = {
+    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
+    "num_hidden_layers": 2, "hidden_size": 64, "num_attention_heads": 4, "num_key_value_heads": 2,
+    "head_dim": 16, "intermediate_size": 128, "vocab_size": 256, "rope_theta": 10000.0,
+    "sliding_window": 8, "query_pre_attn_scalar": 16, "attn_logit_softcapping": 50.0,
+    "final_logit_softcapping": 30.0, "max_position_embeddings": 64, "rms_norm_eps": 1e-6,
+    "hidden_activation": "gelu_pytorch_tanh", "tie_word_embeddings": True, "eos_token_id": 1,
+    "bos_token_id": 2, "pad_token_id": 0, "torch_dtype": "float32",
+}
+
+TINY_B = {
+    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
+    "num_hidden_layers": 3, "hidden_size": 96, "num_attention_heads": 6, "num_key_value_heads": 1,
+    "head_dim": 32, "intermediate_size": 320, "vocab_size": 384, "rope_theta": 100000.0,
+    "sliding_window": 16, "query_pre_attn_scalar": 24, "attn_logit_softcapping": 20.0,
+    "final_logit_softcapping": 15.0, "max_position_embeddings": 128, "rms_norm_eps": 1e-5,
+    "hidden_activation": "gelu_pytorch_tanh", "tie_word_embeddings": True, "eos_token_id": [3, 7],
+    "bos_token_id": 2, "pad_token_id": 0, "torch_dtype": "float32",
+}
+
+# sizes no power of two, head size 48, window that is no multiple of the page
+TINY_C = {
+    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
+    "num_hidden_layers": 4, "hidden_size": 192, "num_attention_heads": 6, "num_key_value_heads": 3,
+    "head_dim": 48, "intermediate_size": 448, "vocab_size": 1000, "rope_theta": 5000.0,
+    "sliding_window": 40, "query_pre_attn_scalar": 64, "attn_logit_softcapping": 30.0,
+    "final_logit_softcapping": 25.0, "max_position_embeddings": 512, "rms_norm_eps": 1e-6,
+    "hidden_activation": "gelu_pytorch_tanh", "tie_word_embeddings": True, "eos_token_id": 1,
+    "torch_dtype": "bfloat16",
+}
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+
+
+def make_folder(cfg_dict, seed=0, store_dtype=None, root=None):
+    """Write a random model folder for ``cfg_dict`` under a temporary place; returns its path."""
+    from airframe_b200.config import config_from_dict
+    from airframe_b200.weights import write_random_model
+    root = Path(root or tempfile.mkdtemp(prefix="af_model_"))
+    cfg = config_from_dict(cfg_dict)
+    write_random_model(root, cfg, seed, store_dtype or cfg_dict.get("torch_dtype", "bfloat16"))
+    return root
