@@ -1,0 +1,156 @@
+"""The generation loop above the step function: requests are served in
+batches, one batch after another; a batch's prompts (of unequal lengths) run
+in one step, then every live sequence gets one token per step; a sequence
+ends at a stop token (not emitted), at ``max_tokens`` or at the context limit,
+leaves the batch and gives its slot back at once.
+
+Reference: rules 3-5 of the single-sequence loop
+(``crates/airframe_observe/src/isf.rs:333-529``): halt on the end token or an
+extra stop id (``:397-410,477-483``), on max_tokens (``:481-485``); the context
+limit of ``src/bin/shimmy_server_gpu/server_inference.rs:1246-1253``.
+
+The loop needs of its engine: ``take_slot()``, ``free_slot(slot)``,
+``step(entries) -> logits``, ``max_context``, ``vocab_size`` and
+``cache.total_pages`` / ``cache.n_slots``; of its sampler:
+``new_state(params, index)`` and ``sample(logits, states, params) -> tokens``.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Callable, Optional
+
+from ..kernels_const import PAGE
+from .batch import StepEntry
+
+
+class RequestError(ValueError):
+    """A request cannot be served: empty, too long, or a bad token id."""
+
+
+@dataclass
+class _Sequence:
+    index: int                 # position among the requests
+    prompt: list
+    slot: int = -1
+    state: object = None
+    out: list = field(default_factory=list)
+    length: int = 0            # tokens in the cache
+    finish: Optional[str] = None
+
+
+def _pages(n: int) -> int:
+    return (n + PAGE - 1) // PAGE
+
+
+class GenerationLoop:
+    def __init__(self, engine, sampler, stop_token_ids=(), max_batch: Optional[int] = None):
+        self.engine = engine
+        self.sampler = sampler
+        self.model_stop_ids = set(stop_token_ids)
+        self.max_batch = max_batch
+        self.finish_reasons: list = []
+        self.batches_run: list = []
+
+    # ------------------------------------------------------------------ planning
+
+    def check(self, prompts, params) -> None:
+        params.check()
+        for i, p in enumerate(prompts):
+            if len(p) == 0:
+                raise RequestError(f"request {i}: the prompt is empty")
+            if len(p) > self.engine.max_context:
+                raise RequestError(f"request {i}: the prompt has {len(p)} tokens, the context holds "
+                                   f"{self.engine.max_context}")
+            for t in p:
+                if not isinstance(t, int) or not 0 <= t < self.engine.vocab_size:
+                    raise RequestError(f"request {i}: token id {t!r} outside the vocabulary")
+
+    def tokens_held(self, prompt_len: int, params) -> int:
+        """The most tokens a request can come to hold."""
+        return min(prompt_len + max(params.max_tokens - 1, 0), self.engine.max_context)
+
+    def plan_batches(self, prompts, params) -> list:
+        """Requests in order, as many to a batch as slots and cache pages allow."""
+        total_pages = self.engine.cache.total_pages
+        limit = self.engine.cache.n_slots
+        if self.max_batch:
+            limit = min(limit, self.max_batch)
+        batches, cur, cur_pages = [], [], 0
+        for i, p in enumerate(prompts):
+            need = _pages(self.tokens_held(len(p), params))
+            if need > total_pages:
+                raise RequestError(f"request {i} needs {need} cache pages, the cache has {total_pages}")
+            if cur and (len(cur) >= limit or cur_pages + need > total_pages):
+                batches.append(cur)
+                cur, cur_pages = [], 0
+            cur.append(i)
+            cur_pages += need
+        if cur:
+            batches.append(cur)
+        return batches
+
+    # ------------------------------------------------------------------ running
+
+    def generate(self, prompts, params, on_token: Optional[Callable] = None) -> list:
+        """New token ids per request, in request order.  ``on_token(request
+        index, token id)`` is called for every emitted token."""
+        self.check(prompts, params)
+        results = [[] for _ in prompts]
+        self.finish_reasons = [None] * len(prompts)
+        self.batches_run = []
+        if params.max_tokens == 0:
+            self.finish_reasons = ["length"] * len(prompts)
+            return results
+        stops = set(params.stop_token_ids)
+        if not params.ignore_eos:
+            stops |= self.model_stop_ids
+        for batch in self.plan_batches(prompts, params):
+            self.batches_run.append(list(batch))
+            seqs = [_Sequence(i, list(prompts[i])) for i in batch]
+            try:
+                for s in seqs:
+                    s.slot = self.engine.take_slot()
+                    s.state = self.sampler.new_state(params, s.index)
+                self._run_batch(seqs, params, stops, on_token)
+            finally:
+                for s in seqs:
+                    if s.slot >= 0:
+                        self.engine.free_slot(s.slot)
+                        s.slot = -1
+            for s in seqs:
+                results[s.index] = s.out
+                self.finish_reasons[s.index] = s.finish
+        return results
+
+    def _end(self, s: _Sequence, reason: str) -> None:
+        s.finish = reason
+        self.engine.free_slot(s.slot)
+        s.slot = -1
+
+    def _run_batch(self, seqs, params, stops, on_token) -> None:
+        logits = self.engine.step([StepEntry(s.slot, s.prompt, [len(s.prompt) - 1]) for s in seqs])
+        for s in seqs:
+            s.length = len(s.prompt)
+        active = list(seqs)
+        while active:
+            tokens = self.sampler.sample(logits, [s.state for s in active], params)
+            going = []
+            for s, t in zip(active, tokens):
+                if t in stops:
+                    self._end(s, "stop")
+                    continue
+                s.out.append(t)
+                if on_token is not None:
+                    on_token(s.index, t)
+                if len(s.out) >= params.max_tokens:
+                    self._end(s, "length")
+                elif s.length + 1 > self.engine.max_context:
+                    self._end(s, "context")
+                else:
+                    going.append(s)
+            active = going
+            if not active:
+                break
+            logits = self.engine.step([StepEntry(s.slot, [s.out[-1]], [0]) for s in active])
+            for s in active:
+                s.length += 1

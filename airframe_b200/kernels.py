@@ -202,6 +202,24 @@ def add_(x, a) -> None:
                          c_longlong(x.numel()), _stream()))
 
 
+def sample(logits, out, temperature: float, top_p: float, penalty: float, uniform=None, recent=None,
+           n_recent=None) -> None:
+    """One token per row of float32 logits [R, V] into out int32 [R].  The
+    repetition penalty changes ``logits`` in place.  ``recent`` int32 [R, 64]
+    holds each row's last tokens, ``n_recent`` int32 [R] how many are valid,
+    ``uniform`` float32 [R] the draws in [0, 1)."""
+    R, V = logits.shape
+    if out.shape[0] != R:
+        raise KernelError("sample: one output per row")
+    _check(_lib().af_sample(_ptr(logits, "logits", torch.float32), c_int(_rows(logits, "logits")), c_int(R),
+                            c_int(V), _ptr(recent, "recent", torch.int32, allow_none=True),
+                            _ptr(n_recent, "n_recent", torch.int32, allow_none=True),
+                            c_int(recent.stride(0) if recent is not None else 0), c_float(temperature),
+                            c_float(top_p), c_float(penalty),
+                            _ptr(uniform, "uniform", torch.float32, allow_none=True),
+                            _ptr(out, "out", torch.int32), _stream()))
+
+
 def gemm_bf16_supported(M, N, K, x, w, out) -> bool:
     return False
 

@@ -1,0 +1,66 @@
+"""The device sampler: per-sequence state on the host (recent tokens, the
+deterministic generator), one kernel launch per step.
+
+Reference: ``sample_token`` (``src/runtime/gpu.rs:880-962``), the window of 64
+recent tokens (``crates/airframe_observe/src/isf.rs:395-396,505-506``).  Every
+sequence has a generator of its own, seeded ``seed + index of the request``,
+so a sequence's tokens do not depend on what else is in its batch.
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from .params import RECENT_WINDOW, SamplingParams
+from .rng import XorShift64Star
+
+
+class SequenceSamplingState:
+    """What sampling remembers of one sequence."""
+
+    def __init__(self, params: SamplingParams, request_index: int):
+        self.rng = XorShift64Star(params.seed + request_index)
+        self.recent: list = []
+
+    def note(self, token: int) -> None:
+        self.recent.append(token)
+        if len(self.recent) > RECENT_WINDOW:
+            del self.recent[0]
+
+
+class Sampler:
+    def __init__(self, vocab_size: int, device):
+        self.vocab_size = vocab_size
+        self.device = torch.device(device)
+
+    def new_state(self, params: SamplingParams, request_index: int) -> SequenceSamplingState:
+        return SequenceSamplingState(params, request_index)
+
+    def sample(self, logits, states, params: SamplingParams) -> list:
+        """One token for each row of ``logits`` (float32 [R, V] on the device;
+        changed in place by the penalty).  Advances each state's generator and
+        recent-token window."""
+        R = logits.shape[0]
+        if R != len(states):
+            raise ValueError("one sampling state per row of logits")
+        use_penalty = params.repetition_penalty != 1.0
+        n_extra = (RECENT_WINDOW + 1) if use_penalty else 0
+        host = torch.zeros(R, 1 + n_extra, dtype=torch.int32)
+        hv = host.view(torch.float32)
+        for r, st in enumerate(states):
+            if not params.greedy:
+                hv[r, 0] = st.rng.next_f32()
+            if use_penalty:
+                host[r, 1] = len(st.recent)
+                if st.recent:
+                    host[r, 2:2 + len(st.recent)] = torch.tensor(st.recent, dtype=torch.int32)
+        dev = host.pin_memory().to(self.device, non_blocking=True)
+        out = torch.empty(R, dtype=torch.int32, device=self.device)
+        kernels.sample(logits, out, params.temperature, params.top_p, params.repetition_penalty,
+                       uniform=dev.view(torch.float32)[:, 0] if not params.greedy else None,
+                       recent=dev[:, 2:] if use_penalty else None,
+                       n_recent=dev[:, 1] if use_penalty else None)
+        tokens = out.tolist()
+        for st, t in zip(states, tokens):
+            st.note(t)
+        return tokens

@@ -1,0 +1,316 @@
+"""Each kernel alone against the plain implementation's function for the same
+part, at sizes other than the engine tests use (no power of two, head sizes
+in steps of 16, odd numbers of heads and groups)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gemma2 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+PAGE = 64
+
+
+@pytest.fixture(scope="module")
+def K():
+    from airframe_b200 import kernels
+    return kernels
+
+
+def tol(dtype):
+    """32-bit: sums of a few thousand 32-bit products round to about sqrt(K) * 2^-24
+    of the largest value (3e-6 at K = 2304): 1e-5.  bfloat16: one rounding of the
+    result (2^-8) plus 32-bit sums of bfloat16 inputs: 1.2e-2."""
+    return 1e-5 if dtype == torch.float32 else 1.2e-2
+
+
+def close(got, ref, dtype, scale=None):
+    ref = ref.double()
+    s = scale if scale is not None else ref.abs().max().clamp_min(1e-30)
+    err = float((got.double().cpu() - ref).abs().max() / s)
+    assert err < tol(dtype), err
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_embed(K, dtype):
+    V, H = 1000, 200
+    table = torch.randn(V, H).to(dtype)
+    ids = torch.tensor([0, 999, 5, 5, 321], dtype=torch.int32)
+    out = torch.empty(5, H, dtype=torch.float32, device=DEV)
+    K.embed(out, table.to(DEV), ids.to(DEV), math.sqrt(H))
+    close(out, plain.embed(ids.tolist(), table.double(), H), torch.float32)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_rmsnorm_and_row_gather(K, dtype):
+    M, H = 7, 2304 + 48
+    x = torch.randn(M, H) * 3
+    w = torch.randn(H) * 0.1
+    y = torch.empty(M, H, dtype=dtype, device=DEV)
+    K.rmsnorm(y, x.to(DEV), w.to(DEV), 1e-5, 1.0)
+    close(y, plain.rms_norm(x.double(), w.double(), 1e-5), dtype)
+    rows = torch.tensor([6, 0, 3], dtype=torch.int32)
+    y2 = torch.empty(3, H, dtype=dtype, device=DEV)
+    K.rmsnorm(y2, x.to(DEV), w.to(DEV), 1e-5, 1.0, rows.to(DEV))
+    close(y2, plain.rms_norm(x.double()[rows.long()], w.double(), 1e-5), dtype)
+    # offset 0: the weight itself multiplies (other architectures)
+    K.rmsnorm(y, x.to(DEV), w.to(DEV), 1e-5, 0.0)
+    close(y, plain.rms_norm(x.double(), w.double() - 1.0, 1e-5), dtype)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_add_rmsnorm(K, dtype):
+    M, H = 5, 1000
+    x, a = torch.randn(M, H), (torch.randn(M, H) * 2).to(dtype)
+    w1, w2 = torch.randn(H) * 0.1, torch.randn(H) * 0.1
+    want_x = x.double() + plain.rms_norm(a.double(), w1.double(), 1e-6)
+    want_y = plain.rms_norm(want_x, w2.double(), 1e-4)
+    xd = x.to(DEV)
+    y = torch.empty(M, H, dtype=dtype, device=DEV)
+    K.add_rmsnorm(xd, a.to(DEV), w1.to(DEV), 1e-6, 1.0, y=y, w_next=w2.to(DEV), eps_next=1e-4)
+    close(xd, want_x, torch.float32)
+    close(y, want_y, dtype)
+    xd = x.to(DEV)
+    K.add_rmsnorm(xd, a.to(DEV), w1.to(DEV), 1e-6, 1.0)
+    close(xd, want_x, torch.float32)
+    # partial sums, added in order before the norm
+    parts = torch.randn(3, M, H)
+    xd = x.to(DEV)
+    K.add_rmsnorm(xd, parts.to(DEV), w1.to(DEV), 1e-6, 1.0, n_parts=3)
+    close(xd, x.double() + plain.rms_norm(parts.double().sum(0), w1.double(), 1e-6), torch.float32)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_gated_act(K, dtype):
+    M, I = 3, 1111
+    gu = (torch.randn(M, 2 * I) * 2).to(dtype)
+    out = torch.empty(M, I, dtype=dtype, device=DEV)
+    K.gated_act(out, gu.to(DEV), "gelu_tanh")
+    g, u = gu.double()[:, :I], gu.double()[:, I:]
+    close(out, plain.gelu_tanh(g) * u, dtype)
+    K.gated_act(out, gu.to(DEV), "silu")
+    close(out, g * torch.sigmoid(g) * u, dtype)
+    with pytest.raises(K.KernelError, match="unknown activation"):
+        K.gated_act(out, gu.to(DEV), "relu")
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("shape", [(1, 130, 70), (5, 64, 16), (67, 129, 257), (3, 1000, 2304)])
+def test_gemm_plain(K, dtype, shape):
+    M, N, Kd = shape
+    x, w = torch.randn(M, Kd).to(dtype), (torch.randn(N, Kd) * 0.05).to(dtype)
+    out = torch.empty(M, N, dtype=dtype, device=DEV)
+    K.gemm_plain(out, x.to(DEV), w.to(DEV))
+    ref = x.double() @ w.double().T
+    close(out, ref, dtype)
+    out32 = torch.empty(M, N, dtype=torch.float32, device=DEV)
+    K.gemm_plain(out32, x.to(DEV), w.to(DEV), cap=2.0)
+    close(out32, plain.softcap(ref, 2.0), torch.float32)
+
+
+def test_gemm_plain_is_true_32_bit_and_batch_invariant(K):
+    """Values that a reduced-precision product would lose; and a row's result
+    does not change with the rows around it."""
+    x = torch.tensor([[1.0, 2 ** -20, -1.0]])
+    w = torch.tensor([[1.0, 1.0, 1.0]])
+    out = torch.empty(1, 1, dtype=torch.float32, device=DEV)
+    K.gemm_plain(out, x.to(DEV), w.to(DEV))
+    assert out.item() == 2 ** -20
+    x = torch.randn(70, 300)
+    w = torch.randn(90, 300)
+    a = torch.empty(70, 90, device=DEV)
+    b = torch.empty(1, 90, device=DEV)
+    K.gemm_plain(a, x.to(DEV), w.to(DEV))
+    K.gemm_plain(b, x[37:38].to(DEV), w.to(DEV))
+    assert torch.equal(a[37], b[0])
+
+
+def _paged(k, v, order, n_pages, dtype):
+    """Scatter k, v [T, nkv, hd] of one sequence into pages in the given order."""
+    T, nkv, hd = k.shape
+    kc = torch.zeros(n_pages, nkv, PAGE, hd, dtype=dtype)
+    vc = torch.zeros(n_pages, nkv, PAGE, hd, dtype=dtype)
+    for r in range(T):
+        p = order[r // PAGE]
+        kc[p, :, r % PAGE] = k[r]
+        vc[p, :, r % PAGE] = v[r]
+    return kc, vc
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("pairing,rot", [("half", 48), ("half", 32), ("adjacent", 48)])
+def test_rope_and_cache_write(K, dtype, pairing, rot):
+    nq, nkv, hd, theta = 3, 1, 48, 5000.0
+    lens = [70, 3]                                    # two sequences, rows concatenated
+    T = sum(lens)
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd).to(dtype)
+    pos = torch.tensor(list(range(70)) + list(range(3)), dtype=torch.int32)
+    seq = torch.tensor([0] * 70 + [1] * 3, dtype=torch.int32)
+    inv = (torch.tensor(theta, dtype=torch.float64) ** (-2.0 * torch.arange(rot // 2, dtype=torch.float64) / rot)).float()
+    table = torch.tensor([[5, 2, -1], [0, -1, -1], [1, 1, 1]], dtype=torch.int32)   # slot -> pages
+    slots = torch.tensor([0, 1], dtype=torch.int32)
+    kc = torch.zeros(6, nkv, PAGE, hd, dtype=dtype, device=DEV)
+    vc = torch.zeros_like(kc)
+    d = qkv.to(DEV)
+    K.rope_cache_write(d, pos.to(DEV), inv.to(DEV), nq, nkv, hd, rot, pairing, seq_of_token=seq.to(DEV),
+                       slots=slots.to(DEV), len_after=torch.tensor(lens, dtype=torch.int32, device=DEV),
+                       kcache=kc, vcache=vc, page_table=table.to(DEV), ring_rows=0)
+    x = qkv.double().reshape(T, nq + 2 * nkv, hd)
+
+    def rotate(h):                                     # [T, heads, hd] with the plain rope on the rotary part
+        part = h[..., :rot]
+        if pairing == "adjacent":                      # (2p, 2p+1) pairs -> half layout and back
+            part = torch.cat([part[..., 0::2], part[..., 1::2]], -1)
+        r = plain.rope(part, pos.tolist(), theta)
+        if pairing == "adjacent":
+            out = torch.empty_like(r)
+            out[..., 0::2], out[..., 1::2] = r[..., : rot // 2], r[..., rot // 2:]
+            r = out
+        return torch.cat([r, h[..., rot:]], -1)
+
+    want = torch.cat([rotate(x[:, : nq + nkv]), x[:, nq + nkv:]], 1)
+    close(d.reshape(T, -1, hd), want, dtype)
+    got_k = torch.cat([kc[5, :, :, :].cpu(), kc[2, :, :6].cpu()], 1).transpose(0, 1)       # rows 0..69 of slot 0
+    close(got_k, want[:70, nq: nq + nkv], dtype)
+    close(vc[0, :, :3].cpu().transpose(0, 1), want[70:, nq + nkv:], dtype)
+    assert float(kc[1].abs().sum()) == 0 and float(kc[2, :, 6:].abs().sum()) == 0          # nothing else touched
+
+
+def test_ring_keeps_the_last_rows_of_a_long_prompt(K):
+    nq, nkv, hd = 1, 1, 16
+    T, ring = 150, 128
+    qkv = torch.randn(T, 3 * hd)
+    pos = torch.arange(T, dtype=torch.int32)
+    table = torch.tensor([[3, 1]], dtype=torch.int32)
+    kc = torch.zeros(4, nkv, PAGE, hd, device=DEV)
+    vc = torch.zeros_like(kc)
+    K.rope_cache_write(qkv.to(DEV), pos.to(DEV), torch.zeros(0, device=DEV), nq, nkv, hd, 0, "half",
+                       seq_of_token=torch.zeros(T, dtype=torch.int32, device=DEV),
+                       slots=torch.zeros(1, dtype=torch.int32, device=DEV),
+                       len_after=torch.tensor([T], dtype=torch.int32, device=DEV), kcache=kc, vcache=vc,
+                       page_table=table.to(DEV), ring_rows=ring)
+    v = qkv[:, 2 * hd:]
+    for p in range(T - ring, T):                       # positions 22..149 live in row p % 128
+        r = p % ring
+        page = [3, 1][r // PAGE]
+        assert torch.equal(vc[page, 0, r % PAGE].cpu(), v[p]), p
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hd,nq,nkv,window,cap", [(16, 4, 2, 0, 50.0), (80, 6, 2, 7, 0.0), (256, 3, 3, 33, 30.0),
+                                                  (48, 5, 1, 0, 20.0)])
+def test_attention_prefill_plain(K, dtype, hd, nq, nkv, window, cap):
+    lens = [37, 1, 90]
+    T = sum(lens)
+    q = torch.randn(T, nq * hd).to(dtype)
+    k = torch.randn(T, nkv * hd).to(dtype)
+    v = torch.randn(T, nkv * hd).to(dtype)
+    pos = torch.tensor([p for n in lens for p in range(n)], dtype=torch.int32)
+    out = torch.empty(T, nq * hd, dtype=dtype, device=DEV)
+    scale = 0.7 / math.sqrt(hd)
+    K.attn_prefill_plain(out, q.to(DEV), k.to(DEV), v.to(DEV), pos.to(DEV), nq, nkv, hd, scale, cap, window)
+    o = 0
+    for n in lens:
+        ref = plain.attention(q[o:o + n].double().reshape(n, nq, hd), k[o:o + n].double().reshape(n, nkv, hd),
+                              v[o:o + n].double().reshape(n, nkv, hd), scale, cap, window or None)
+        close(out[o:o + n], ref, dtype, scale=1.0)
+        o += n
+
+
+def _decode_case(K, dtype, hd, nq, nkv, window, cap, lens, q, ks, vs, scale):
+    """Sequences with their own lengths in permuted pages; returns kernel output [B, nq*hd]."""
+    B = len(lens)
+    ring = ((window + PAGE - 1) // PAGE) * PAGE if window else 0
+    per_seq = max(((min(n, ring) if ring else n) + PAGE - 1) // PAGE for n in lens)
+    n_pages = B * per_seq + 3
+    perm = torch.randperm(n_pages).tolist()
+    table = torch.full((B + 2, per_seq), -1, dtype=torch.int32)
+    kc = torch.zeros(n_pages, nkv, PAGE, hd, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    slots = [B + 1 - b for b in range(B)]              # slots are not the batch order
+    for b, n in enumerate(lens):
+        for r_pos in range(n):
+            if ring and r_pos + ring < n:
+                continue
+            r = r_pos % ring if ring else r_pos
+            if table[slots[b], r // PAGE] < 0:
+                table[slots[b], r // PAGE] = perm.pop()
+            p = int(table[slots[b], r // PAGE])
+            kc[p, :, r % PAGE] = ks[b][r_pos]
+            vc[p, :, r % PAGE] = vs[b][r_pos]
+    out = torch.empty(B, nq * hd, dtype=dtype, device=DEV)
+    K.attn_decode(out, q.to(DEV), _View(kc.to(DEV), vc.to(DEV), table.to(DEV), ring),
+                  _Batch(torch.tensor(slots, dtype=torch.int32, device=DEV),
+                         torch.tensor(lens, dtype=torch.int32, device=DEV), max(lens)),
+                  nq, nkv, hd, scale, cap, window)
+    return out
+
+
+class _View:
+    def __init__(self, k, v, table, ring):
+        self.k, self.v, self.page_table, self.ring_rows = k, v, table, ring
+
+
+class _Batch:
+    def __init__(self, slots, len_after, max_len_after):
+        self.slots, self.len_after, self.max_len_after = slots, len_after, max_len_after
+        self.n_seqs = slots.shape[0]
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("hd,nq,nkv,window,cap", [(16, 4, 2, 0, 50.0), (80, 6, 2, 70, 0.0), (256, 8, 4, 100, 50.0),
+                                                  (128, 5, 5, 0, 30.0), (48, 6, 1, 64, 0.0)])
+def test_attention_decode_over_pages(K, dtype, hd, nq, nkv, window, cap):
+    torch.manual_seed(hd + nq)
+    lens = [1, 64, 65, 300, 129]
+    scale = 1.3 / math.sqrt(hd)
+    q = torch.randn(len(lens), nq * hd).to(dtype)
+    ks = [torch.randn(n, nkv, hd).to(dtype) for n in lens]
+    vs = [torch.randn(n, nkv, hd).to(dtype) for n in lens]
+    out = _decode_case(K, dtype, hd, nq, nkv, window, cap, lens, q, ks, vs, scale)
+    for b, n in enumerate(lens):
+        # the new token is the last row: build a whole-sequence problem whose last query is q[b]
+        qq = torch.zeros(n, nq, hd, dtype=torch.float64)
+        qq[-1] = q[b].double().reshape(nq, hd)
+        ref = plain.attention(qq, ks[b].double(), vs[b].double(), scale, cap, window or None)[-1]
+        close(out[b], ref, dtype, scale=1.0)
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_attention_finds_one_far_key_and_the_window_edge(K, dtype):
+    """Random keys would hide a lost row among hundreds: one key is made to
+    dominate, first far back, then exactly at and just outside the window's edge."""
+    hd, nq, nkv, n = 64, 2, 1, 700
+    torch.manual_seed(3)
+    q = torch.randn(1, nq * hd).to(dtype)
+    base_k = torch.randn(n, nkv, hd) * 0.01
+    v = torch.randn(n, nkv, hd).to(dtype)
+    qv = q.double().reshape(nq, hd)
+    for window, far in [(0, 5), (0, 333), (257, n - 257), (257, n - 258), (64, n - 64), (64, n - 65)]:
+        k = base_k.clone()
+        k[far, 0] = (qv[0] + qv[1]).float() * 8.0          # both heads score it high
+        k = k.to(dtype)
+        out = _decode_case(K, dtype, hd, nq, nkv, window, 0.0, [n], q, [k], [v], 1.0)
+        visible = window == 0 or (n - 1 - far) < window
+        qq = torch.zeros(n, nq, hd, dtype=torch.float64)
+        qq[-1] = qv
+        ref = plain.attention(qq, k.double(), v.double(), 1.0, 0.0, window or None)[-1]
+        close(out[0], ref, dtype, scale=1.0)
+        near = (out[0].double().cpu().reshape(nq, hd) - v[far, 0].double()).abs().max()
+        assert (near < 0.05) == visible, (window, far, float(near))
+
+
+def test_kernels_refuse_what_they_cannot_do(K):
+    x = torch.zeros(2, 4)
+    with pytest.raises(K.KernelError, match="CUDA device"):
+        K.rmsnorm(x, x, x[0], 1e-6, 1.0)
+    with pytest.raises(K.KernelError, match="float32 or bfloat16"):
+        K.dtype_code(torch.float16)
+    q = torch.zeros(1, 528, device=DEV)
+    with pytest.raises(K.KernelError, match="head_dim 528"):
+        K.attn_prefill_plain(q, q, q, q, torch.zeros(1, dtype=torch.int32, device=DEV), 1, 1, 528, 1.0, 0.0, 0)
+    with pytest.raises(K.KernelError, match="heads 3, groups 2"):
+        K.attn_prefill_plain(q, q, q, q, torch.zeros(1, dtype=torch.int32, device=DEV), 3, 2, 16, 1.0, 0.0, 0)

@@ -1,0 +1,121 @@
+"""The device sampler against the plain implementation."""
+import numpy as np
+import pytest
+import torch
+
+import plain_gemma2 as plain
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+
+
+@pytest.fixture(scope="module")
+def K():
+    from airframe_b200 import kernels
+    return kernels
+
+
+def _sample(K, rows, temperature, top_p, penalty, u=None, recent=None):
+    logits = torch.tensor(np.asarray(rows, dtype=np.float32), device=DEV)
+    R = logits.shape[0]
+    out = torch.empty(R, dtype=torch.int32, device=DEV)
+    rec = nrec = None
+    if recent is not None:
+        rec = torch.zeros(R, 64, dtype=torch.int32)
+        nrec = torch.zeros(R, dtype=torch.int32)
+        for r, lst in enumerate(recent):
+            rec[r, : len(lst)] = torch.tensor(lst, dtype=torch.int32)
+            nrec[r] = len(lst)
+        rec, nrec = rec.to(DEV), nrec.to(DEV)
+    uni = torch.tensor(u, dtype=torch.float32, device=DEV) if u is not None else None
+    K.sample(logits, out, temperature, top_p, penalty, uniform=uni, recent=rec, n_recent=nrec)
+    return out.tolist(), logits.cpu().numpy()
+
+
+@pytest.mark.parametrize("V", [7, 256, 1000, 256000])
+def test_greedy_is_the_first_finite_maximum(K, V):
+    rng = np.random.default_rng(V)
+    rows = rng.standard_normal((5, V)).astype(np.float32)
+    rows[1, [V // 3, V // 2]] = 9.0                     # a tie: the lower index wins
+    rows[2, 0] = np.inf
+    rows[2, V - 1] = np.nan
+    rows[3, :] = np.nan
+    got, _ = _sample(K, rows, 0.0, 0.95, 1.0)
+    assert got == [plain.greedy(r) for r in rows]
+    assert got[1] == V // 3 and got[3] == 0
+
+
+def test_repetition_penalty_changes_the_winner(K):
+    rows = np.array([[1.0, 3.0, 2.9, -1.0], [1.0, -0.5, -0.4, -3.0]], dtype=np.float32)
+    got, changed = _sample(K, rows, 0.0, 1.0, 1.5, recent=[[1, 1], [2, 0, 2]])
+    assert got == [2, 0]
+    want0 = plain.apply_repetition_penalty(rows[0], [1, 1], 1.5)
+    want1 = plain.apply_repetition_penalty(rows[1], [2, 0, 2], 1.5)
+    assert np.allclose(changed[0], want0) and np.allclose(changed[1], want1)
+    assert got == [plain.greedy(want0), plain.greedy(want1)]
+
+
+def _nucleus(row, temperature, top_p):
+    """The reference's nucleus (src/runtime/gpu.rs:924-948) in 64 bits: ids and probabilities."""
+    z = np.asarray(row, dtype=np.float64) / temperature
+    p = np.exp(z - z.max())
+    p /= p.sum()
+    order = np.argsort(-p, kind="stable")
+    cum = np.cumsum(p[order])
+    cutoff = int(np.searchsorted(cum, top_p - 1e-12) + 1)
+    return order[:cutoff], p
+
+
+@pytest.mark.parametrize("V,temperature,top_p", [(50, 0.8, 0.95), (1000, 1.0, 0.5), (1000, 0.3, 0.9),
+                                                 (256000, 0.8, 0.95), (4000, 1.5, 1.0)])
+def test_draw_lands_where_the_uniform_number_points(K, V, temperature, top_p):
+    """The token drawn with u is the one whose interval of the nucleus's
+    cumulative mass, in index order, holds u."""
+    rng = np.random.default_rng(V + int(100 * top_p))
+    R = 16
+    rows = (rng.standard_normal((R, V)) * 2).astype(np.float32)
+    u = rng.random(R).astype(np.float32)
+    u[0], u[1] = 0.0, 0.99999994
+    got, _ = _sample(K, rows, temperature, top_p, 1.0, u=u)
+    for r in range(R):
+        ids, p = _nucleus(rows[r], temperature, top_p)
+        inside = np.zeros(V, dtype=bool)
+        inside[ids] = True
+        assert inside[got[r]], (r, got[r])
+        w = np.where(inside, p, 0.0)
+        cum = np.cumsum(w)
+        mass = cum[-1]
+        lo, hi = (cum[got[r]] - w[got[r]]) / mass, cum[got[r]] / mass
+        assert lo - 1e-4 <= u[r] <= hi + 1e-4, (r, lo, float(u[r]), hi)
+
+
+def test_top_p_keeps_the_tail_out_and_frequencies_follow_the_probabilities(K):
+    probs = np.array([0.4, 0.3, 0.2, 0.06, 0.04])
+    row = np.log(probs).astype(np.float32)
+    n = 4000
+    rows = np.tile(row, (n, 1))
+    u = np.random.default_rng(0).random(n).astype(np.float32)
+    got, _ = _sample(K, rows, 1.0, 0.9, 1.0, u=u)
+    counts = np.bincount(got, minlength=5) / n
+    assert counts[3] == 0 and counts[4] == 0            # 0.4 + 0.3 + 0.2 reaches 0.9
+    assert np.allclose(counts[:3], probs[:3] / 0.9, atol=0.03)
+    got, _ = _sample(K, rows, 1.0, 1.0, 1.0, u=u)
+    assert np.allclose(np.bincount(got, minlength=5) / n, probs, atol=0.03)
+
+
+def test_ties_at_the_cutoff_enter_lowest_index_first(K):
+    row = np.log(np.array([0.25, 0.25, 0.25, 0.25])).astype(np.float32)
+    # top_p 0.5 needs two of the four equal tokens: 0 and 1
+    rows = np.tile(row, (64, 1))
+    u = np.linspace(0, 0.999, 64).astype(np.float32)
+    got, _ = _sample(K, rows, 1.0, 0.5, 1.0, u=u)
+    assert set(got) == {0, 1} and got == sorted(got)
+
+
+def test_a_row_does_not_depend_on_its_batch(K):
+    rng = np.random.default_rng(9)
+    rows = rng.standard_normal((8, 5000)).astype(np.float32)
+    u = rng.random(8).astype(np.float32)
+    together, _ = _sample(K, rows, 0.8, 0.95, 1.1, u=u, recent=[[1, 2, 3]] * 8)
+    alone = [_sample(K, rows[i:i + 1], 0.8, 0.95, 1.1, u=u[i:i + 1], recent=[[1, 2, 3]])[0][0] for i in range(8)]
+    assert together == alone
