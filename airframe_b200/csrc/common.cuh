@@ -28,12 +28,21 @@ int af_fail(int code, const char* fmt, ...);
     if (!(cond)) return af_fail(-1, __VA_ARGS__); \
   } while (0)
 
-#define AF_CHECK_LAUNCH(name)                                                    \
+// Kernels launched by this library since it was loaded (af_launch_count()).
+extern unsigned long long g_af_launches;
+
+#define AF_COUNT_LAUNCH(name)                                                    \
   do {                                                                           \
     cudaError_t e__ = cudaGetLastError();                                        \
     if (e__ != cudaSuccess)                                                      \
       return af_fail((int)e__, "%s: launch failed: %s", name, cudaGetErrorString(e__)); \
-    return 0;                                                                    \
+    ++g_af_launches;                                                             \
+  } while (0)
+
+#define AF_CHECK_LAUNCH(name) \
+  do {                        \
+    AF_COUNT_LAUNCH(name);    \
+    return 0;                 \
   } while (0)
 
 template <typename T>

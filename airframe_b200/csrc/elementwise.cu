@@ -23,6 +23,10 @@ AF_EXPORT const char* af_last_error() { return g_error; }
 
 AF_EXPORT int af_abi_version() { return 1; }
 
+unsigned long long g_af_launches = 0;
+
+AF_EXPORT unsigned long long af_launch_count() { return g_af_launches; }
+
 // ---------------------------------------------------------------- embedding
 
 template <typename TW>

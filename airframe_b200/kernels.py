@@ -65,6 +65,13 @@ def _check(code: int) -> None:
         raise KernelError(f"{msg} (code {code})")
 
 
+def launch_count() -> int:
+    """Kernels this library has launched since it was loaded."""
+    f = _lib().af_launch_count
+    f.restype = ctypes.c_ulonglong
+    return int(f())
+
+
 def require_cuda_tensor(t, name="tensor"):
     if not t.is_cuda:
         raise KernelError(f"{name} must live on a CUDA device")

@@ -1,0 +1,284 @@
+#!/usr/bin/env python3
+"""Decode and prefill throughput of Gemma-2 2B sizes (random weights, bf16) on one B200.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+A step is one decode step of a batch of 8 sequences that hold 2,048-token
+prompts (context limit 8192): the model's step function plus greedy sampling on
+the device.  ``value`` is decoded tokens a second, timed with CUDA events around
+exactly K steps after W warm-up steps.  ``e2e`` is the same through
+``GpuRuntime.generate`` with host token lists in and out.  The line also carries
+the prefill rate of 2,048 tokens with its fraction of the bf16 peak, the decode
+step's fraction of the HBM roofline, decode at batch 1 and 64, the clocks seen
+during the timed region and the number of this library's kernels launched in it.
+Every decode step reads all weights (5.2 GB), far more than the 126 MB L2, so
+no separate L2 flush is needed between iterations.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+
+# Gemma-2 2B layer sizes
+GEMMA2_2B = {
+    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
+    "num_hidden_layers": 26, "hidden_size": 2304, "num_attention_heads": 8, "num_key_value_heads": 4,
+    "head_dim": 256, "intermediate_size": 9216, "vocab_size": 256000, "rope_theta": 10000.0,
+    "sliding_window": 4096, "query_pre_attn_scalar": 256, "attn_logit_softcapping": 50.0,
+    "final_logit_softcapping": 30.0, "max_position_embeddings": 8192, "rms_norm_eps": 1e-6,
+    "hidden_activation": "gelu_pytorch_tanh", "tie_word_embeddings": True, "torch_dtype": "bfloat16",
+}
+FULL_LAYERS = 26
+PROMPT_LEN = 2048
+CONTEXT = 8192
+FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
+
+
+def peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.is_file():
+        try:
+            d = json.loads(p.read_text())
+            return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]), "source": "measured"}
+        except (KeyError, ValueError, TypeError):
+            pass
+    return dict(FALLBACK_PEAKS, source="fallback")
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while a region runs."""
+    QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
+             "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.rows, self.proc, self.thread = [], None, None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.QUERY}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+            return
+        self.thread = threading.Thread(target=self._read, daemon=True)
+        self.thread.start()
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.rows.append([c.strip() for c in line.split(",")])
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        try:
+            self.proc.wait(timeout=5)
+        except subprocess.TimeoutExpired:
+            self.proc.kill()
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in self.rows:
+            if len(r) < 6:
+                continue
+            try:
+                sm.append(float(r[0]))
+                mx.append(float(r[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_bytes(cfg, n_layers):
+    """Bytes of the weights a decode step reads once (bf16)."""
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q = cfg["num_attention_heads"] * cfg["head_dim"]
+    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
+    per_layer = (q + 2 * kv) * h + h * q + 3 * h * i + 4 * h
+    return 2 * (n_layers * per_layer + v * h + h)
+
+
+def cache_bytes(cfg, n_layers, lens):
+    """Bytes of keys and values a decode step reads for sequences of these lengths."""
+    kv_row = 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
+    total = 0
+    for layer in range(n_layers):
+        sliding = layer % 2 == 0
+        for n in lens:
+            total += kv_row * (min(n, cfg["sliding_window"]) if sliding else n)
+    return total
+
+
+def prefill_flops(cfg, n_layers, T, n_logits):
+    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    q = cfg["num_attention_heads"] * cfg["head_dim"]
+    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
+    linear = 2 * T * n_layers * ((q + 2 * kv) * h + h * q + 3 * h * i)
+    attn = 0
+    for layer in range(n_layers):
+        w = cfg["sliding_window"] if layer % 2 == 0 else None
+        pairs = sum(min(t + 1, w) if w else t + 1 for t in range(T))
+        attn += 2 * 2 * pairs * q
+    return linear + attn + 2 * n_logits * v * h
+
+
+def run_ours(args) -> dict:
+    import torch
+    sys.path.insert(0, str(ROOT))
+    from airframe_b200 import kernels
+    from airframe_b200.config import config_from_dict
+    from airframe_b200.engine import GpuRuntime, StepEntry
+    from airframe_b200.sampling import Sampler, SamplingParams
+
+    n_layers = args.layers or FULL_LAYERS
+    cfg_dict = dict(GEMMA2_2B, num_hidden_layers=n_layers)
+    cfg = config_from_dict(cfg_dict)
+    B, K, W = args.batch, args.steps, max(args.warmup, 3)
+    pk = peaks()
+    torch.manual_seed(0)
+    max_b = max([B] + ([] if args.no_points else [1, 64]))
+    budget = max_b * ((PROMPT_LEN + K + W + 8 + 63) // 64 * 64)
+    rt = GpuRuntime.random(cfg, seed=0, dtype="bfloat16", max_tokens=budget, max_context=CONTEXT,
+                           max_sequences=max_b, on_device=True)
+    eng = rt.engine
+    dev = eng.device
+    V = cfg.vocab_size
+    greedy = SamplingParams(max_tokens=1, temperature=0.0, repetition_penalty=1.0, ignore_eos=True)
+
+    def prompts(n, seed):
+        g = torch.Generator().manual_seed(seed)
+        return [torch.randint(0, V, (PROMPT_LEN,), generator=g).tolist() for _ in range(n)]
+
+    def timed(fn, n):
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        for _ in range(n):
+            fn()
+        end.record()
+        torch.cuda.synchronize()
+        return start.elapsed_time(end)
+
+    def decode_rate(batch, steps, warm, clocks=None):
+        """tokens/s, ms/step and launches of `steps` decode steps at `batch` after 2,048-token prompts."""
+        sampler = Sampler(V, dev)
+        states = [sampler.new_state(greedy, i) for i in range(batch)]
+        slots = [eng.take_slot() for _ in range(batch)]
+        try:
+            ps = prompts(batch, 100 + batch)
+            logits = eng.step([StepEntry(s, p, [PROMPT_LEN - 1]) for s, p in zip(slots, ps)])
+            state = {"tokens": sampler.sample(logits, states, greedy)}
+
+            def one():
+                lg = eng.step([StepEntry(s, [t], [0]) for s, t in zip(slots, state["tokens"])])
+                state["tokens"] = sampler.sample(lg, states, greedy)
+
+            for _ in range(warm):
+                one()
+            if clocks is not None:
+                clocks.start()
+            n0 = kernels.launch_count()
+            ms = timed(one, steps)
+            launches = kernels.launch_count() - n0
+            lens = [eng.length(s) for s in slots]
+            return batch * steps / (ms / 1e3), ms / steps, launches, lens
+        finally:
+            for s in slots:
+                eng.free_slot(s)
+
+    # ---- prefill of 2,048 tokens (one sequence, logits at its last position)
+    def prefill_once():
+        s = eng.take_slot()
+        try:
+            eng.step([StepEntry(s, pf_prompt, [PROMPT_LEN - 1])])
+        finally:
+            eng.free_slot(s)
+
+    pf_prompt = prompts(1, 7)[0]
+    for _ in range(3):
+        prefill_once()
+    reps = 5
+    pf_ms = timed(prefill_once, reps) / reps
+    pf_flops = prefill_flops(cfg_dict, n_layers, PROMPT_LEN, 1)
+    prefill = {"value": PROMPT_LEN / (pf_ms / 1e3), "tokens": PROMPT_LEN, "ms": pf_ms,
+               "frac": pf_flops / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+
+    # ---- the headline: decode at batch B
+    clocks = ClockSampler()
+    value, ms_step, launches, lens = decode_rate(B, K, W, clocks)
+    clock_info = clocks.stop()
+    need = model_bytes(cfg_dict, n_layers) + cache_bytes(cfg_dict, n_layers, lens)
+    achieved = need / (ms_step / 1e3) / 1e9
+    roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                "frac": achieved / pk["hbm_gbs"], "peaks": pk["source"]}
+
+    points = {}
+    if not args.no_points:
+        for b in (1, 64):
+            points[f"decode_b{b}"] = decode_rate(b, max(4, K // 2), 3)[0]
+
+    # ---- end to end through the public entry point
+    n_new = K + 1
+    stamps = []
+    params = SamplingParams(max_tokens=n_new, temperature=0.0, repetition_penalty=1.0, ignore_eos=True)
+    ps = prompts(B, 500)
+    rt.generate(ps, SamplingParams(max_tokens=4, temperature=0.0, repetition_penalty=1.0, ignore_eos=True))
+    rt.generate(ps, params, on_token=lambda i, t: stamps.append(time.perf_counter()))
+    torch.cuda.synchronize()
+    t_first = stamps[B - 1]                       # every sequence has its first token: the prompts are done
+    e2e_value = B * (n_new - 1) / (stamps[-1] - t_first)
+    e2e = {"value": e2e_value, "unit": "tokens/s", "h2d_bytes_per_step": (7 * B + 1) * 4 + 4 * B,
+           "d2h_bytes_per_step": 4 * B}
+
+    return {
+        "metric": "Gemma-2 2B bf16 decode tokens/s at batch 8 (2,048-token prompts)",
+        "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms_step,
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic: seeded random weights N(0, 0.02), uniform random token ids",
+        "config": {"model": "gemma-2-2b sizes", "global_batch": B, "seq_len": PROMPT_LEN, "context": CONTEXT,
+                   "parallelism": "single-gpu", "layers": n_layers, "layers_full": FULL_LAYERS,
+                   "hidden": 2304, "heads": 8, "kv_heads": 4, "head_dim": 256, "intermediate": 9216,
+                   "vocab": 256000, "sliding_window": 4096, "sampling": "greedy on device",
+                   "l2": "inputs larger than L2 (weights 5.2 GB per step)"},
+        "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
+        "gpu_launches": launches, "clocks": clock_info, "impl": "ours",
+    }
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=64)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
+    ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is a Rust crate on wgpu (no setup.py/pyproject.toml: pip cannot install "
+                          "it; no Rust toolchain; no graphics stack on this box)"}))
+        return 0
+    if args.gpus != 1:
+        print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
+        return 2
+    print(json.dumps(run_ours(args)))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())
