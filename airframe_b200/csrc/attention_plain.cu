@@ -16,7 +16,8 @@
 // [q heads | k heads | v heads] in place (32-bit angles and arithmetic) and,
 // when a cache is given, stores the rotated k and the v in the row's page.
 template <typename T>
-__global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int* __restrict__ positions,
+__global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const float* __restrict__ parts,
+                                  int n_parts, size_t part_stride, const int* __restrict__ positions,
                                   const int* __restrict__ seq_of_token, const int* __restrict__ slots,
                                   const int* __restrict__ len_after, const float* __restrict__ inv_freq,
                                   int nq, int nkv, int hd, int rot_dim, int pairing,
@@ -26,6 +27,17 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int
   const int pos = positions[t];
   T* row = qkv + (size_t)t * row_stride;
   const int half = rot_dim / 2;
+  if (parts != nullptr) {
+    // the row arrives as split-K partial sums: add them in order first
+    const int width = (nq + 2 * nkv) * hd;
+    const float* pr = parts + (size_t)t * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+      float v = pr[i];
+      for (int p = 1; p < n_parts; ++p) v += pr[(size_t)p * part_stride + i];
+      row[i] = from_f32<T>(v);
+    }
+    __syncthreads();
+  }
   // rotate q and k
   const int n_rot = (nq + nkv) * half;
   for (int idx = threadIdx.x; idx < n_rot; idx += blockDim.x) {
@@ -63,7 +75,10 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const int
   }
 }
 
-AF_EXPORT int af_rope_cache_write(void* qkv, int dtype, int row_stride, const int* positions,
+// `parts` (optional): float [n_parts, n_tokens, row width] partial sums of the
+// rows, part_stride elements apart; they are added in order into qkv first.
+AF_EXPORT int af_rope_cache_write(void* qkv, int dtype, int row_stride, const float* parts, int n_parts,
+                                  long long part_stride, const int* positions,
                                   const int* seq_of_token, const int* slots, const int* len_after,
                                   const float* inv_freq, int n_tokens, int nq, int nkv, int hd,
                                   int rot_dim, int pairing, void* kcache, void* vcache,
@@ -78,7 +93,8 @@ AF_EXPORT int af_rope_cache_write(void* qkv, int dtype, int row_stride, const in
   AF_REQUIRE((kcache == nullptr) == (vcache == nullptr), "af_rope_cache_write: k and v cache");
   AF_DISPATCH_DTYPE(dtype, T,
                     rope_cache_kernel<T><<<n_tokens, 256, 0, stream>>>(
-                        (T*)qkv, row_stride, positions, seq_of_token, slots, len_after, inv_freq, nq,
+                        (T*)qkv, row_stride, parts, n_parts, (size_t)part_stride, positions, seq_of_token,
+                        slots, len_after, inv_freq, nq,
                         nkv, hd, rot_dim, pairing, (T*)kcache, (T*)vcache, page_table, max_pages,
                         ring_rows));
   AF_CHECK_LAUNCH("af_rope_cache_write");

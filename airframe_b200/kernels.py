@@ -149,9 +149,10 @@ def gemm_plain(out, x, w, cap: float = 0.0) -> None:
 
 def rope_cache_write(qkv, positions, inv_freq, nq: int, nkv: int, hd: int, rot_dim: int, pairing: str,
                      seq_of_token=None, slots=None, len_after=None, kcache=None, vcache=None,
-                     page_table=None, ring_rows: int = 0) -> None:
+                     page_table=None, ring_rows: int = 0, parts=None) -> None:
     """Rotate the q and k heads of the packed rows [q | k | v] in place and,
-    when a cache is given, store k and v at each token's row of its page."""
+    when a cache is given, store k and v at each token's row of its page.
+    ``parts`` (float32 [S, T, width] split-K partial sums) are added into qkv first."""
     T = qkv.shape[0]
     if qkv.shape[1] != (nq + 2 * nkv) * hd:
         raise KernelError(f"rope_cache_write: row width {qkv.shape[1]} is not (nq + 2 nkv) * head_dim")
@@ -167,7 +168,9 @@ def rope_cache_write(qkv, positions, inv_freq, nq: int, nkv: int, hd: int, rot_d
             raise KernelError(f"rope_cache_write: cache pages must be [pages, {nkv}, {PAGE}, {hd}]")
         max_pages = page_table.shape[1]
     _check(_lib().af_rope_cache_write(
-        _ptr(qkv), c_int(dtype_code(qkv.dtype)), c_int(_rows(qkv, "qkv")), _ptr(positions, "positions", torch.int32),
+        _ptr(qkv), c_int(dtype_code(qkv.dtype)), c_int(_rows(qkv, "qkv")),
+        _ptr(parts, "parts", torch.float32, allow_none=True), c_int(parts.shape[0] if parts is not None else 0),
+        c_longlong(parts.stride(0) if parts is not None else 0), _ptr(positions, "positions", torch.int32),
         _ptr(seq_of_token, "seq_of_token", torch.int32, allow_none=True),
         _ptr(slots, "slots", torch.int32, allow_none=True),
         _ptr(len_after, "len_after", torch.int32, allow_none=True),
@@ -202,7 +205,12 @@ def attn_decode_plain(out, q, kcache, vcache, page_table, slots, lens, nq: int, 
 
 
 def add_(x, a) -> None:
-    """x += a; x float32, a float32 or bfloat16, same shape."""
+    """x += a; x float32, a float32 or bfloat16, same shape (or [S, *x.shape]
+    partial sums, added one after the other)."""
+    if a.dim() == x.dim() + 1:
+        for part in a:
+            add_(x, part)
+        return
     if x.shape != a.shape or not (x.is_contiguous() and a.is_contiguous()):
         raise KernelError("add_: tensors must be contiguous and of one shape")
     _check(_lib().af_add(_ptr(x, "x", torch.float32), _ptr(a), c_int(dtype_code(a.dtype)),
@@ -227,8 +235,73 @@ def sample(logits, out, temperature: float, top_p: float, penalty: float, unifor
                             _ptr(out, "out", torch.int32), _stream()))
 
 
-def gemm_bf16_supported(M, N, K, x, w, out) -> bool:
-    return False
+_ERR = {}
+
+
+def error_word(device) -> torch.Tensor:
+    """The device word that kernels set when a bounded wait inside them ran out."""
+    key = torch.device(device).index or 0
+    if key not in _ERR:
+        _ERR[key] = torch.zeros(1, dtype=torch.int32, device=device)
+    return _ERR[key]
+
+
+def check_device_errors(device) -> None:
+    """Raise if a kernel reported a wait that ran out of time (reads one word: synchronises)."""
+    w = error_word(device)
+    if int(w.item()) != 0:
+        w.zero_()
+        raise KernelError("a tensor-core kernel gave up waiting on a barrier (results of the step are invalid)")
+
+
+def gemm_tc_supported(x, w, out) -> bool:
+    """Whether the tensor-core product takes these operands: bfloat16, dense
+    rows, K and row strides multiples of 8, 16-byte aligned bases."""
+    if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    if x.dim() != 2 or w.dim() != 2 or x.stride(1) != 1 or w.stride(1) != 1:
+        return False
+    K = x.shape[1]
+    return (K % 8 == 0 and x.stride(0) % 8 == 0 and w.stride(0) % 8 == 0 and x.data_ptr() % 16 == 0
+            and w.data_ptr() % 16 == 0 and (out is None or out.stride(-1) == 1))
+
+
+def gemm_tc_splits(M: int, N: int, K: int) -> int:
+    """How many K splits fill the GPU when a product has few output tiles."""
+    lib = _lib()
+    bn = lib.af_gemm_tc_token_tile(c_int(M))
+    tiles = ((N + 127) // 128) * ((M + bn - 1) // bn)
+    kb = (K + 63) // 64
+    if tiles >= 96 or kb < 8:
+        return 1
+    want = max(1, min(148 // tiles, kb // 4, 16))
+    per = (kb + want - 1) // want
+    return (kb + per - 1) // per
+
+
+def gemm_tc(out, x, w, cap: float = 0.0, splits: int = 1, dual_up_offset: int = -1, activation: str = "gelu_tanh",
+            n_features=None) -> None:
+    """out = x @ w^T on the tcgen05 tensor cores (bfloat16 operands, 32-bit
+    accumulation in TMEM).  splits > 1: out is float32 [splits, M, N] partial
+    sums.  dual_up_offset >= 0: out[m, f] = act(x . w[f]) * (x . w[dual_up_offset + f])."""
+    M, K = x.shape
+    dual = dual_up_offset >= 0
+    N = n_features if n_features is not None else w.shape[0]
+    if not gemm_tc_supported(x, w, out):
+        raise KernelError("gemm_tc: operands must be bfloat16 with dense, 16-byte aligned rows and K % 8 == 0")
+    if splits > 1:
+        if out.dtype != torch.float32 or tuple(out.shape) != (splits, M, N) or not out.is_contiguous():
+            raise KernelError("gemm_tc: split-K wants a contiguous float32 [splits, M, N] output")
+        ldo, part = N, M * N
+    else:
+        if tuple(out.shape) != (M, N):
+            raise KernelError(f"gemm_tc: output shape {tuple(out.shape)}, expected {(M, N)}")
+        ldo, part = out.stride(0), 0
+    _check(_lib().af_gemm_tc(_ptr(out), c_int(dtype_code(out.dtype)), c_longlong(ldo), c_longlong(part), _ptr(x),
+                             c_longlong(x.stride(0)), _ptr(w), c_longlong(w.stride(0)), c_longlong(w.shape[0]),
+                             c_int(M), c_int(N), c_int(K), c_int(1 if dual else 0), c_int(max(dual_up_offset, 0)),
+                             c_int(ACTIVATIONS[activation]), c_float(cap), c_int(splits),
+                             _ptr(error_word(x.device), "err", torch.int32), _stream()))
 
 
 def attn_prefill(out, q, k, v, batch, nq, nkv, hd, scale, cap, window) -> None:

@@ -16,7 +16,7 @@ from .. import kernels
 from ..config.base import ConfigError, PartSpec
 from ..weights.loader import WeightDecl
 from .base import KVNeed, Mixer, build_part, register_part
-from .linear import linear
+from .linear import PartialSums, linear_split
 
 
 @register_part("mixer", "attention")
@@ -65,9 +65,13 @@ class Attention(Mixer):
 
     def forward(self, x, batch, view):
         nq, nkv, hd = self.nq, self.nkv, self.hd
-        qkv = linear(x, self.w_qkv)
+        qkv = linear_split(x, self.w_qkv)
+        parts = None
+        if isinstance(qkv, PartialSums):
+            parts = qkv.parts
+            qkv = torch.empty(x.shape[0], (nq + 2 * nkv) * hd, dtype=x.dtype, device=x.device)
         kv = view.kv
-        self.position.encode_and_store(qkv, batch, nq, nkv, hd, kv if view.writes else None)
+        self.position.encode_and_store(qkv, batch, nq, nkv, hd, kv if view.writes else None, parts=parts)
         q = qkv[:, : nq * hd]
         k = qkv[:, nq * hd: (nq + nkv) * hd]
         v = qkv[:, (nq + nkv) * hd:]
@@ -81,4 +85,4 @@ class Attention(Mixer):
             kernels.attn_prefill(ctx, q, k, v, batch, nq, nkv, hd, self.scale, self.softcap, window)
         else:
             kernels.attn_decode(ctx, q, kv, batch, nq, nkv, hd, self.scale, self.softcap, window)
-        return linear(ctx, self.w_o)
+        return linear_split(ctx, self.w_o)

@@ -127,10 +127,11 @@ class Norm(Part):
 class PositionEncoding(Part):
     """Applied by a mixer to its packed query/key/value rows."""
 
-    def encode_and_store(self, qkv, batch, nq: int, nkv: int, hd: int, kv) -> None:
+    def encode_and_store(self, qkv, batch, nq: int, nkv: int, hd: int, kv, parts=None) -> None:
         """Encode positions into the q and k heads of ``qkv`` ([T, (nq + 2 nkv) hd],
         in place) and, if ``kv`` (a cache view that is written) is given, store
-        k and v in the cache."""
+        k and v in the cache.  ``parts`` (float32 [S, T, width]), when given,
+        are split-K partial sums of the rows: their sum is written to ``qkv`` first."""
         raise NotImplementedError
 
 
@@ -145,7 +146,7 @@ class Mixer(Part):
 
     def forward(self, x, batch, view):
         """x [T, H] in the compute dtype (normalised) -> [T, H] in the compute
-        dtype.  ``batch`` is the :class:`~airframe_b200.engine.batch.StepBatch`,
+        dtype, or a :class:`~airframe_b200.parts.linear.PartialSums` of it.  ``batch`` is the :class:`~airframe_b200.engine.batch.StepBatch`,
         ``view`` the layer's :class:`~airframe_b200.cache.LayerCacheView`."""
         raise NotImplementedError
 

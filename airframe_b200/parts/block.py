@@ -10,6 +10,11 @@ from __future__ import annotations
 
 from .. import kernels
 from .base import Block, register_part
+from .linear import PartialSums
+
+
+def _dense(a):
+    return a.parts if isinstance(a, PartialSums) else a
 
 
 @register_part("block", "sandwich")
@@ -40,8 +45,8 @@ class PreNormBlock(Block):
         n = self.norms
         dt = self.ctx.compute_dtype
         h = normed if normed is not None else n["pre_mixer"].forward(x, dt)
-        kernels.add_(x, self.mixer.forward(h, batch, view))
-        kernels.add_(x, self.feed_forward.forward(n["pre_feed_forward"].forward(x, dt), batch))
+        kernels.add_(x, _dense(self.mixer.forward(h, batch, view)))
+        kernels.add_(x, _dense(self.feed_forward.forward(n["pre_feed_forward"].forward(x, dt), batch)))
         return next_pre.forward(x, dt) if next_pre is not None else None
 
     def first_norm(self):

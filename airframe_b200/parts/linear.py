@@ -18,8 +18,48 @@ def linear(x, w, out_dtype=None, cap: float = 0.0, out=None):
     N = w.shape[0]
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype or x.dtype, device=x.device)
-    if x.dtype == torch.bfloat16 and kernels.gemm_bf16_supported(M, N, x.shape[1], x, w, out):
-        kernels.gemm_bf16(out, x, w, cap)
+    if kernels.gemm_tc_supported(x, w, out):
+        kernels.gemm_tc(out, x, w, cap)
     else:
         kernels.gemm_plain(out, x, w, cap)
+    return out
+
+
+class PartialSums:
+    """The result of a product as float32 split-K partial sums [S, M, N]; the
+    consumer (a norm's ``add_normed``, the rotary kernel) adds them in order."""
+
+    def __init__(self, parts):
+        self.parts = parts
+
+    @property
+    def shape(self):
+        return self.parts.shape[1:]
+
+
+def linear_split(x, w):
+    """x w^T for few rows and a long K: split-K partial sums when that fills
+    the GPU better, else the plain result.  Returns a tensor or PartialSums."""
+    M, K = x.shape
+    N = w.shape[0]
+    if kernels.gemm_tc_supported(x, w, None):
+        splits = kernels.gemm_tc_splits(M, N, K)
+        if splits > 1:
+            parts = torch.empty(splits, M, N, dtype=torch.float32, device=x.device)
+            kernels.gemm_tc(parts, x, w, splits=splits)
+            return PartialSums(parts)
+    return linear(x, w)
+
+
+def gated_linear(x, w_gu, inter: int, activation: str):
+    """act(x w_gate^T) * (x w_up^T) for w_gu = [gate rows; up rows]: one
+    kernel with the activation in its epilogue where the tensor-core kernel
+    takes the operands, else two steps."""
+    M = x.shape[0]
+    out = torch.empty(M, inter, dtype=x.dtype, device=x.device)
+    if kernels.gemm_tc_supported(x, w_gu, out):
+        kernels.gemm_tc(out, x, w_gu, dual_up_offset=inter, activation=activation, n_features=inter)
+    else:
+        gu = linear(x, w_gu)
+        kernels.gated_act(out, gu, activation)
     return out

@@ -12,7 +12,7 @@ from .. import kernels
 from ..config.base import ConfigError
 from ..weights.loader import WeightDecl
 from .base import FeedForward, register_part
-from .linear import linear
+from .linear import gated_linear, linear_split
 
 
 @register_part("feed_forward", "gated_mlp")
@@ -44,7 +44,5 @@ class GatedMlp(FeedForward):
         self.w_down = weights[d].to(dt).contiguous()
 
     def forward(self, x, batch):
-        gu = linear(x, self.w_gu)
-        h = torch.empty(x.shape[0], self.inter, dtype=x.dtype, device=x.device)
-        kernels.gated_act(h, gu, self.activation)
-        return linear(h, self.w_down)
+        h = gated_linear(x, self.w_gu, self.inter, self.activation)
+        return linear_split(h, self.w_down)

@@ -12,6 +12,7 @@ import torch
 from .. import kernels
 from ..weights.loader import WeightDecl
 from .base import Norm, register_part
+from .linear import PartialSums
 
 
 @register_part("norm", "rms_norm")
@@ -39,7 +40,10 @@ class RmsNorm(Norm):
         kernels.rmsnorm(y, x, self.w, self.eps, self.offset, rows)
         return y
 
-    def add_normed(self, x, a, then=None, out_dtype=None, n_parts: int = 1):
+    def add_normed(self, x, a, then=None, out_dtype=None):
+        n_parts = 1
+        if isinstance(a, PartialSums):
+            n_parts, a = a.parts.shape[0], a.parts
         if then is not None and not (isinstance(then, RmsNorm) and then.offset == self.offset):
             kernels.add_rmsnorm(x, a, self.w, self.eps, self.offset, n_parts=n_parts)
             return then.forward(x, out_dtype)

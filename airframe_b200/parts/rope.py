@@ -39,17 +39,17 @@ class Rope(PositionEncoding):
     def load(self, weights):
         self.inv_freq = self._inv_freq_host.to(self.ctx.device)
 
-    def encode_and_store(self, qkv, batch, nq, nkv, hd, kv):
+    def encode_and_store(self, qkv, batch, nq, nkv, hd, kv, parts=None):
         if self.rotary_dim > hd:
             raise ConfigError(f"rope: rotary_dim {self.rotary_dim} exceeds head_dim {hd}")
         if kv is None:
             kernels.rope_cache_write(qkv, batch.positions, self.inv_freq, nq, nkv, hd, self.rotary_dim,
-                                     self.pairing)
+                                     self.pairing, parts=parts)
         else:
             kernels.rope_cache_write(qkv, batch.positions, self.inv_freq, nq, nkv, hd, self.rotary_dim,
                                      self.pairing, seq_of_token=batch.seq_of_token, slots=batch.slots,
                                      len_after=batch.len_after, kcache=kv.k, vcache=kv.v,
-                                     page_table=kv.page_table, ring_rows=kv.ring_rows)
+                                     page_table=kv.page_table, ring_rows=kv.ring_rows, parts=parts)
 
 
 @register_part("position", "none")
@@ -63,10 +63,12 @@ class NoPosition(PositionEncoding):
     def load(self, weights):
         self.inv_freq = torch.zeros(0, dtype=torch.float32, device=self.ctx.device)
 
-    def encode_and_store(self, qkv, batch, nq, nkv, hd, kv):
+    def encode_and_store(self, qkv, batch, nq, nkv, hd, kv, parts=None):
         if kv is None:
+            if parts is not None:
+                kernels.rope_cache_write(qkv, batch.positions, self.inv_freq, nq, nkv, hd, 0, "half", parts=parts)
             return
         kernels.rope_cache_write(qkv, batch.positions, self.inv_freq, nq, nkv, hd, 0, "half",
                                  seq_of_token=batch.seq_of_token, slots=batch.slots,
                                  len_after=batch.len_after, kcache=kv.k, vcache=kv.v,
-                                 page_table=kv.page_table, ring_rows=kv.ring_rows)
+                                 page_table=kv.page_table, ring_rows=kv.ring_rows, parts=parts)

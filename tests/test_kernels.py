@@ -314,3 +314,57 @@ def test_kernels_refuse_what_they_cannot_do(K):
         K.attn_prefill_plain(q, q, q, q, torch.zeros(1, dtype=torch.int32, device=DEV), 1, 1, 528, 1.0, 0.0, 0)
     with pytest.raises(K.KernelError, match="heads 3, groups 2"):
         K.attn_prefill_plain(q, q, q, q, torch.zeros(1, dtype=torch.int32, device=DEV), 3, 2, 16, 1.0, 0.0, 0)
+
+
+@pytest.mark.parametrize("M,N,Kd", [(1, 128, 64), (8, 256, 128), (5, 130, 72), (16, 2304, 2304), (33, 384, 200),
+                                    (64, 100, 1000), (100, 640, 328), (300, 384, 264), (700, 130, 2048)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tensor_cores(K, M, N, Kd, out_dtype):
+    torch.manual_seed(M * N + Kd)
+    x = torch.randn(M, Kd).to(torch.bfloat16)
+    w = (torch.randn(N, Kd) * 0.05).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+    K.gemm_tc(out, x.to(DEV), w.to(DEV))
+    K.check_device_errors(DEV)
+    close(out, ref, out_dtype if out_dtype == torch.bfloat16 else torch.float32)
+    if out_dtype == torch.float32:
+        K.gemm_tc(out, x.to(DEV), w.to(DEV), cap=1.5)
+        close(out, plain.softcap(ref, 1.5), torch.float32)
+        # against the plain kernel on the same inputs: only the order of the 32-bit sums differs
+        twin = torch.empty(M, N, dtype=torch.float32, device=DEV)
+        K.gemm_plain(twin, x.to(DEV), w.to(DEV), cap=1.5)
+        close(out, twin.cpu(), torch.float32)
+
+
+@pytest.mark.parametrize("M,N,Kd,splits", [(8, 256, 1024, 4), (3, 130, 2304, 9), (40, 384, 9216, 16), (16, 128, 520, 3)])
+def test_gemm_tensor_cores_split_k(K, M, N, Kd, splits):
+    x = torch.randn(M, Kd).to(torch.bfloat16)
+    w = (torch.randn(N, Kd) * 0.05).to(torch.bfloat16)
+    out = torch.full((splits, M, N), float("nan"), dtype=torch.float32, device=DEV)
+    K.gemm_tc(out, x.to(DEV), w.to(DEV), splits=splits)
+    K.check_device_errors(DEV)
+    close(out.sum(0), x.double() @ w.double().T, torch.float32)
+    assert 1 <= K.gemm_tc_splits(8, 2304, 9216) <= 16 and K.gemm_tc_splits(8, 256000, 2304) == 1
+
+
+@pytest.mark.parametrize("M,I,Kd,act", [(8, 256, 128, "gelu_tanh"), (5, 200, 72, "silu"), (130, 448, 192, "gelu_tanh"),
+                                        (300, 9216, 2304, "gelu_tanh")])
+def test_gemm_tensor_cores_gated(K, M, I, Kd, act):
+    x = torch.randn(M, Kd).to(torch.bfloat16)
+    w = (torch.randn(2 * I, Kd) * 0.05).to(torch.bfloat16)
+    g = x.double() @ w[:I].double().T
+    u = x.double() @ w[I:].double().T
+    ref = (plain.gelu_tanh(g) if act == "gelu_tanh" else g * torch.sigmoid(g)) * u
+    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
+    K.gemm_tc(out, x.to(DEV), w.to(DEV), dual_up_offset=I, activation=act, n_features=I)
+    K.check_device_errors(DEV)
+    close(out, ref, torch.bfloat16)
+
+
+def test_gemm_tensor_cores_refuses_unaligned(K):
+    x = torch.zeros(4, 12, dtype=torch.bfloat16, device=DEV)
+    w = torch.zeros(8, 12, dtype=torch.bfloat16, device=DEV)
+    assert not K.gemm_tc_supported(x, w, None)
+    with pytest.raises(K.KernelError, match="K % 8"):
+        K.gemm_tc(torch.zeros(4, 8, dtype=torch.bfloat16, device=DEV), x, w)
