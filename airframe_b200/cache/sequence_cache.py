@@ -60,7 +60,6 @@ class KVGroup:
             self.k = torch.zeros(shape, dtype=dtype, device=device)
             self.v = torch.zeros(shape, dtype=dtype, device=device)
             self.table = torch.full((n_slots, self.pages_per_seq), -1, dtype=torch.int32, device=device)
-            self.table_host = self.table_host.pin_memory()
 
     def rows_held(self, length: int) -> int:
         return min(length, self.ring_rows) if self.ring_rows else length
@@ -88,10 +87,16 @@ class KVGroup:
         self.held[slot] = []
 
     def flush(self) -> None:
-        """Bring the device's page table up to date (rows that changed)."""
-        if self.table is not None:
-            for slot in sorted(self.dirty):
-                self.table[slot].copy_(self.table_host[slot], non_blocking=True)
+        """Bring the device's page table up to date (rows that changed).  The
+        rows travel in a buffer of their own: the host table goes on changing
+        while earlier copies may still wait in the stream."""
+        if self.table is not None and self.dirty:
+            slots = sorted(self.dirty)
+            rows = torch.empty(len(slots), 1 + self.pages_per_seq, dtype=torch.int32).pin_memory()
+            rows[:, 0] = torch.tensor(slots, dtype=torch.int32)
+            rows[:, 1:] = self.table_host[slots]
+            dev = rows.to(self.table.device, non_blocking=True)
+            self.table.index_copy_(0, dev[:, 0].long(), dev[:, 1:])
         self.dirty.clear()
 
     def bytes_per_token(self) -> int:
