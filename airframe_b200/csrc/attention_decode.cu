@@ -1,0 +1,287 @@
+// Decode attention over the paged bfloat16 cache, split over the keys so that
+// a step of few sequences still fills the GPU (it is bound by the bytes of K
+// and V it reads; every byte is read once).
+//
+// Pass 1, grid (sequence, kv head x head tile, split): a block of 128 threads
+// walks its share of the sequence's cache pages.  Eight lanes own one key: each
+// holds head_dim / 8 elements of the K row (16-byte loads), dots them with GT
+// query heads of the group, reduces over the eight lanes, and keeps an online
+// softmax (32-bit max, sum, output) per head.  The 16 key groups of a block are
+// merged through shared memory and leave (max, sum, output) in scratch memory.
+// Pass 2, grid (sequence, head): merges the splits and writes bfloat16.
+//
+// Scores are 32-bit; softcap uses tanh.approx and the softmax ex2.approx, which
+// is what the bfloat16 path allows; the 32-bit path uses the plain kernel.
+#include "common.cuh"
+
+namespace {
+
+constexpr int DA_THREADS = 128;
+constexpr int DA_KEY_GROUPS = DA_THREADS / 8;
+
+__device__ __forceinline__ float fast_tanh(float x) {
+  float y;
+  asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+__device__ __forceinline__ float fast_exp2(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+// E bfloat16 values (E even) from p into f[]: 16-byte loads when E % 8 == 0, else 4-byte loads.
+template <int E>
+__device__ __forceinline__ void load_bf16(const __nv_bfloat16* p, float* f) {
+  if constexpr (E % 8 == 0) {
+#pragma unroll
+    for (int i = 0; i < E / 8; ++i) {
+      const uint4 raw = *reinterpret_cast<const uint4*>(p + 8 * i);
+      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        f[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
+        f[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
+      }
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < E / 2; ++i) {
+      const uint32_t w = *reinterpret_cast<const uint32_t*>(p + 2 * i);
+      f[2 * i] = __uint_as_float(w << 16);
+      f[2 * i + 1] = __uint_as_float(w & 0xffff0000u);
+    }
+  }
+}
+
+struct DecodeArgs {
+  const __nv_bfloat16* q;
+  long long q_stride;
+  const __nv_bfloat16* kcache;
+  const __nv_bfloat16* vcache;
+  const int* page_table;
+  int max_pages;
+  const int* slots;
+  const int* lens;
+  int nq, nkv;
+  float scale, cap;
+  int window, ring_rows;
+  int n_splits;
+  float* part_o;   // [batch, nq, splits, HD]
+  float* part_ml;  // [batch, nq, splits, 2]
+};
+
+template <int HD, int GT>
+__global__ void __launch_bounds__(DA_THREADS)
+attn_decode_split_kernel(DecodeArgs a) {
+  constexpr int E = HD / 8;  // elements of a row per lane
+  constexpr float LOG2E = 1.4426950408889634f;
+  constexpr int EP = E + 4;   // padded: the 8 lanes of a key read 16-byte pieces from distinct banks
+  __shared__ __align__(16) float q_s[GT * 8 * EP];
+  __shared__ float m_s[DA_KEY_GROUPS * GT], l_s[DA_KEY_GROUPS * GT];
+  extern __shared__ float o_s[];  // [key group][GT][HD]
+
+  const int b = blockIdx.x;
+  const int group = a.nq / a.nkv;
+  const int tiles = group / GT;
+  const int kvh = blockIdx.y / tiles;
+  const int head0 = kvh * group + (blockIdx.y % tiles) * GT;
+  const int z = blockIdx.z;
+  const int tid = threadIdx.x, kg = tid >> 3, sub = tid & 7;
+  const int slot = a.slots[b];
+  const int len = slot >= 0 ? a.lens[b] : 0;
+  const int pos = len - 1;
+  const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+
+  int pp_begin = 0, pp_end = 0;
+  if (len > 0) {
+    const int first_pp = lo / AF_PAGE, last_pp = pos / AF_PAGE;
+    const int n_pp = last_pp - first_pp + 1;
+    const int per = (n_pp + a.n_splits - 1) / a.n_splits;
+    pp_begin = first_pp + z * per;
+    pp_end = min(pp_begin + per, last_pp + 1);
+  }
+
+  for (int i = tid; i < GT * HD; i += DA_THREADS) {
+    const int h = i / HD, d = i - h * HD;
+    q_s[(h * 8 + d / E) * EP + d % E] =
+        len > 0 ? __bfloat162float(a.q[(size_t)b * a.q_stride + (size_t)(head0 + h) * HD + d]) * a.scale : 0.f;
+  }
+  __syncthreads();
+
+  float m[GT], l[GT], o[GT][E];
+#pragma unroll
+  for (int h = 0; h < GT; ++h) {
+    m[h] = -INFINITY;
+    l[h] = 0.f;
+#pragma unroll
+    for (int e = 0; e < E; ++e) o[h][e] = 0.f;
+  }
+  const int ring_pages = a.ring_rows / AF_PAGE;
+  const int* pt = a.page_table + (size_t)max(slot, 0) * a.max_pages;
+  const float inv_cap = a.cap > 0.f ? 1.f / a.cap : 0.f;
+
+  for (int pp = pp_begin; pp < pp_end; ++pp) {
+    const int page = pt[ring_pages > 0 ? pp % ring_pages : pp];
+    const size_t base = ((size_t)page * a.nkv + kvh) * AF_PAGE * HD;
+#pragma unroll 2
+    for (int jj = kg; jj < AF_PAGE; jj += DA_KEY_GROUPS) {
+      const int j = pp * AF_PAGE + jj;
+      const bool valid = j >= lo && j <= pos;  // uniform over the 8 lanes of a key
+      float kf[E], vf[E];
+      const size_t row = base + (size_t)jj * HD + sub * E;
+      load_bf16<E>(a.kcache + row, kf);
+      load_bf16<E>(a.vcache + row, vf);
+#pragma unroll
+      for (int h = 0; h < GT; ++h) {
+        const float* qh = q_s + (h * 8 + sub) * EP;
+        float dot = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; ++e) dot = fmaf(qh[e], kf[e], dot);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
+        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
+        float s = a.cap > 0.f ? a.cap * fast_tanh(dot * inv_cap) : dot;
+        s = valid ? s * LOG2E : -INFINITY;       // softmax in base 2
+        const float m_new = fmaxf(m[h], s);
+        const float ref = m_new == -INFINITY ? 0.f : m_new;
+        const float corr = fast_exp2(m[h] - ref);
+        const float p = fast_exp2(s - ref);
+        l[h] = l[h] * corr + p;
+#pragma unroll
+        for (int e = 0; e < E; ++e) o[h][e] = fmaf(p, vf[e], o[h][e] * corr);
+        m[h] = m_new;
+      }
+    }
+  }
+
+  // merge the key groups of the block
+#pragma unroll
+  for (int h = 0; h < GT; ++h) {
+    if (sub == 0) {
+      m_s[kg * GT + h] = m[h];
+      l_s[kg * GT + h] = l[h];
+    }
+#pragma unroll
+    for (int e = 0; e < E; ++e) o_s[((size_t)kg * GT + h) * HD + sub * E + e] = o[h][e];
+  }
+  __syncthreads();
+  for (int i = tid; i < GT * HD; i += DA_THREADS) {
+    const int h = i / HD, d = i - h * HD;
+    float M = -INFINITY;
+#pragma unroll
+    for (int g = 0; g < DA_KEY_GROUPS; ++g) M = fmaxf(M, m_s[g * GT + h]);
+    const float ref = M == -INFINITY ? 0.f : M;
+    float L = 0.f, O = 0.f;
+#pragma unroll
+    for (int g = 0; g < DA_KEY_GROUPS; ++g) {
+      const float w = fast_exp2(m_s[g * GT + h] - ref);
+      L += l_s[g * GT + h] * w;
+      O += o_s[((size_t)g * GT + h) * HD + d] * w;
+    }
+    const size_t pidx = ((size_t)b * a.nq + head0 + h) * a.n_splits + z;
+    a.part_o[pidx * HD + d] = O;
+    if (d == 0) {
+      a.part_ml[pidx * 2] = M;
+      a.part_ml[pidx * 2 + 1] = L;
+    }
+  }
+}
+
+template <int HD>
+__global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long long out_stride,
+                                         const float* __restrict__ part_o, const float* __restrict__ part_ml,
+                                         int nq, int n_splits) {
+  const int b = blockIdx.x, h = blockIdx.y;
+  const size_t p0 = ((size_t)b * nq + h) * n_splits;
+  float M = -INFINITY;
+  for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(p0 + s) * 2]);
+  const float ref = M == -INFINITY ? 0.f : M;
+  float L = 0.f;
+  for (int s = 0; s < n_splits; ++s) L += part_ml[(p0 + s) * 2 + 1] * fast_exp2(part_ml[(p0 + s) * 2] - ref);
+  const float inv = L > 0.f ? 1.f / L : 0.f;
+  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+    float O = 0.f;
+    for (int s = 0; s < n_splits; ++s) O += part_o[(p0 + s) * HD + d] * fast_exp2(part_ml[(p0 + s) * 2] - ref);
+    out[(size_t)b * out_stride + (size_t)h * HD + d] = __float2bfloat16_rn(O * inv);
+  }
+}
+
+template <int HD, int GT>
+int launch_decode(const DecodeArgs& a, __nv_bfloat16* out, long long out_stride, int batch, cudaStream_t stream) {
+  const size_t smem = (size_t)DA_KEY_GROUPS * GT * HD * sizeof(float);
+  static bool configured = false;
+  if (!configured && smem > 40 * 1024) {
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_split_kernel<HD, GT>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    if (e != cudaSuccess) return af_fail((int)e, "af_attn_decode: %s", cudaGetErrorString(e));
+    configured = true;
+  }
+  const int group = a.nq / a.nkv;
+  dim3 grid(batch, a.nkv * (group / GT), a.n_splits);
+  attn_decode_split_kernel<HD, GT><<<grid, DA_THREADS, smem, stream>>>(a);
+  AF_COUNT_LAUNCH("af_attn_decode (split)");
+  attn_decode_merge_kernel<HD><<<dim3(batch, a.nq), HD < 128 ? HD : 128, 0, stream>>>(
+      out, out_stride, a.part_o, a.part_ml, a.nq, a.n_splits);
+  AF_CHECK_LAUNCH("af_attn_decode (merge)");
+}
+
+template <int HD>
+int launch_decode_hd(const DecodeArgs& a, __nv_bfloat16* out, long long out_stride, int batch, cudaStream_t s) {
+  // the widest head tile that divides the group and keeps the output in registers
+  constexpr int LIMIT = 512 / HD;  // 2 heads of 256, 4 of 128, 8 of 64
+  const int group = a.nq / a.nkv;
+  if (LIMIT >= 8 && group % 8 == 0) return launch_decode<HD, (LIMIT >= 8 ? 8 : 1)>(a, out, out_stride, batch, s);
+  if (LIMIT >= 4 && group % 4 == 0) return launch_decode<HD, (LIMIT >= 4 ? 4 : 1)>(a, out, out_stride, batch, s);
+  if (LIMIT >= 2 && group % 2 == 0) return launch_decode<HD, (LIMIT >= 2 ? 2 : 1)>(a, out, out_stride, batch, s);
+  return launch_decode<HD, 1>(a, out, out_stride, batch, s);
+}
+
+}  // namespace
+
+// 1 when the split kernel takes this head size (else the plain kernel serves).
+AF_EXPORT int af_attn_decode_supported(int hd) { return hd == 64 || hd == 128 || hd == 256 ? 1 : 0; }
+
+// Floats of scratch memory that af_attn_decode needs: outputs, then (max, sum).
+AF_EXPORT long long af_attn_decode_scratch(int batch, int nq, int hd, int n_splits) {
+  return (long long)batch * nq * n_splits * (hd + 2);
+}
+
+// out [batch, nq * hd] bfloat16 = attention of one new token per sequence over
+// its cache (lens[b] counts the new token, which the cache holds already).
+// scratch: af_attn_decode_scratch(...) floats.  Sequences with slot < 0 give zeros.
+AF_EXPORT int af_attn_decode(void* out, long long out_stride, const void* q, long long q_stride,
+                             const void* kcache, const void* vcache, const int* page_table, int max_pages,
+                             const int* slots, const int* lens, int batch, int nq, int nkv, int hd, float scale,
+                             float cap, int window, int ring_rows, int n_splits, float* scratch,
+                             cudaStream_t stream) {
+  if (batch == 0) return 0;
+  AF_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "af_attn_decode: heads %d, groups %d", nq, nkv);
+  AF_REQUIRE(af_attn_decode_supported(hd), "af_attn_decode: head_dim %d (takes 64, 128, 256)", hd);
+  AF_REQUIRE(ring_rows % AF_PAGE == 0 && (ring_rows == 0 || (window > 0 && window <= ring_rows)),
+             "af_attn_decode: window %d, ring rows %d", window, ring_rows);
+  AF_REQUIRE(n_splits >= 1 && n_splits <= 65535 && scratch != nullptr, "af_attn_decode: splits %d", n_splits);
+  AF_REQUIRE(((uintptr_t)kcache & 15) == 0 && ((uintptr_t)vcache & 15) == 0, "af_attn_decode: cache alignment");
+  DecodeArgs a;
+  a.q = (const __nv_bfloat16*)q;
+  a.q_stride = q_stride;
+  a.kcache = (const __nv_bfloat16*)kcache;
+  a.vcache = (const __nv_bfloat16*)vcache;
+  a.page_table = page_table;
+  a.max_pages = max_pages;
+  a.slots = slots;
+  a.lens = lens;
+  a.nq = nq;
+  a.nkv = nkv;
+  a.scale = scale;
+  a.cap = cap;
+  a.window = window;
+  a.ring_rows = ring_rows;
+  a.n_splits = n_splits;
+  a.part_o = scratch;
+  a.part_ml = scratch + (size_t)batch * nq * n_splits * hd;
+  __nv_bfloat16* o = (__nv_bfloat16*)out;
+  if (hd == 64) return launch_decode_hd<64>(a, o, out_stride, batch, stream);
+  if (hd == 128) return launch_decode_hd<128>(a, o, out_stride, batch, stream);
+  return launch_decode_hd<256>(a, o, out_stride, batch, stream);
+}

@@ -309,8 +309,43 @@ def attn_prefill(out, q, k, v, batch, nq, nkv, hd, scale, cap, window) -> None:
     attn_prefill_plain(out, q, k, v, batch.positions, nq, nkv, hd, scale, cap, window)
 
 
+def attn_decode_splits(batch: int, nkv: int, max_len: int, window: int) -> int:
+    """How many ways the keys of a sequence are split so that the step fills the GPU."""
+    rows = min(max_len, window) if window else max_len
+    pages = max(1, (rows + PAGE - 1) // PAGE + (1 if window else 0))
+    want = max(1, (4 * 148) // max(1, batch * nkv))
+    return max(1, min(want, pages, 64))
+
+
+def attn_decode_split(out, q, kcache, vcache, page_table, slots, lens, nq, nkv, hd, scale, cap, window, ring_rows,
+                      n_splits: int, scratch=None) -> None:
+    """bfloat16 decode attention, split over the keys (two kernels: partial
+    results into ``scratch``, then their merge)."""
+    B = q.shape[0]
+    lib = _lib()
+    lib.af_attn_decode_scratch.restype = ctypes.c_longlong
+    need = lib.af_attn_decode_scratch(c_int(B), c_int(nq), c_int(hd), c_int(n_splits))
+    if scratch is None:
+        scratch = torch.empty(need, dtype=torch.float32, device=q.device)
+    elif scratch.numel() < need or scratch.dtype != torch.float32:
+        raise KernelError(f"attn_decode_split: scratch of {need} floats wanted")
+    if q.dtype != torch.bfloat16 or kcache.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attn_decode_split: bfloat16 only")
+    _check(lib.af_attn_decode(
+        _ptr(out), c_longlong(_rows(out, "out")), _ptr(q), c_longlong(_rows(q, "q")), _ptr(kcache), _ptr(vcache),
+        _ptr(page_table, "page_table", torch.int32), c_int(page_table.shape[1]), _ptr(slots, "slots", torch.int32),
+        _ptr(lens, "lens", torch.int32), c_int(B), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_float(cap),
+        c_int(window), c_int(ring_rows), c_int(n_splits), _ptr(scratch, "scratch", torch.float32), _stream()))
+
+
 def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window) -> None:
-    """Attention of a decode step over the cache: picks the kernel."""
+    """Attention of a decode step over the cache: the split kernel for
+    bfloat16 and head sizes it takes, else the plain kernel."""
+    if q.dtype == torch.bfloat16 and _lib().af_attn_decode_supported(c_int(hd)):
+        n = attn_decode_splits(batch.n_seqs, nkv, batch.max_len_after, window)
+        attn_decode_split(out, q, kv.k, kv.v, kv.page_table, batch.slots, batch.len_after, nq, nkv, hd, scale, cap,
+                          window, kv.ring_rows, n)
+        return
     attn_decode_plain(out, q, kv.k, kv.v, kv.page_table, batch.slots, batch.len_after, nq, nkv, hd,
                       scale, cap, window, kv.ring_rows)
 
