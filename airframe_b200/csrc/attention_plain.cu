@@ -12,9 +12,25 @@
 
 // ---------------------------------------------------------------- rope + cache write
 
-// One block per token.  Rotates the q and k heads of the packed row
-// [q heads | k heads | v heads] in place (32-bit angles and arithmetic) and,
-// when a cache is given, stores the rotated k and the v in the row's page.
+// One block per (token, head) of the packed row [q heads | k heads | v heads].
+// Rotates q and k heads in place (32-bit angles and arithmetic) and, when a
+// cache is given, stores the rotated k and the v in the row's page.  The row
+// may arrive as split-K partial sums (float), added in index order first.
+template <typename T>
+__device__ __forceinline__ float rope_src(const T* row, const float* parts, int n_parts, size_t part_stride,
+                                          int i) {
+  if (parts == nullptr) return to_f32(row[i]);
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  float v = 0.f;
+  for (int p0 = 0; p0 < n_parts; p0 += 4) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) acc[u] = p0 + u < n_parts ? parts[(size_t)(p0 + u) * part_stride + i] : 0.f;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) v += acc[u];
+  }
+  return v;
+}
+
 template <typename T>
 __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const float* __restrict__ parts,
                                   int n_parts, size_t part_stride, const int* __restrict__ positions,
@@ -23,55 +39,54 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const flo
                                   int nq, int nkv, int hd, int rot_dim, int pairing,
                                   T* __restrict__ kcache, T* __restrict__ vcache,
                                   const int* __restrict__ page_table, int max_pages, int ring_rows) {
-  const int t = blockIdx.x;
+  const int t = blockIdx.x, head = blockIdx.y;
   const int pos = positions[t];
-  T* row = qkv + (size_t)t * row_stride;
+  T* row = qkv + (size_t)t * row_stride + (size_t)head * hd;
+  const float* pr = parts ? parts + (size_t)t * (nq + 2 * nkv) * hd + (size_t)head * hd : nullptr;
   const int half = rot_dim / 2;
-  if (parts != nullptr) {
-    // the row arrives as split-K partial sums: add them in order first
-    const int width = (nq + 2 * nkv) * hd;
-    const float* pr = parts + (size_t)t * width;
-    for (int i = threadIdx.x; i < width; i += blockDim.x) {
-      float v = pr[i];
-      for (int p = 1; p < n_parts; ++p) v += pr[(size_t)p * part_stride + i];
-      row[i] = from_f32<T>(v);
+  // where this head's row goes in the cache (k and v heads only)
+  T* dst = nullptr;
+  if (kcache != nullptr && head >= nq) {
+    const int seq = seq_of_token[t];
+    const int slot = slots[seq];
+    // of the tokens of this step that share a ring row only the last is kept; padding rows are skipped
+    if (slot >= 0 && !(ring_rows > 0 && pos + ring_rows < len_after[seq])) {
+      const int r = ring_rows > 0 ? pos % ring_rows : pos;
+      const int page = page_table[(size_t)slot * max_pages + r / AF_PAGE];
+      const bool is_v = head >= nq + nkv;
+      const int h = head - nq - (is_v ? nkv : 0);
+      dst = (is_v ? vcache : kcache) + (((size_t)page * nkv + h) * AF_PAGE + r % AF_PAGE) * hd;
     }
-    __syncthreads();
   }
-  // rotate q and k
-  const int n_rot = (nq + nkv) * half;
-  for (int idx = threadIdx.x; idx < n_rot; idx += blockDim.x) {
-    const int h = idx / half, p = idx - h * half;
-    T* x = row + (size_t)h * hd;
+  const bool rotate = head < nq + nkv;
+  // rotary pairs
+  for (int p = threadIdx.x; p < half; p += blockDim.x) {
     const int i0 = pairing == AF_PAIR_HALF ? p : 2 * p;
     const int i1 = pairing == AF_PAIR_HALF ? p + half : 2 * p + 1;
-    const float ang = (float)pos * inv_freq[p];
-    float s, c;
-    sincosf(ang, &s, &c);
-    const float a = to_f32(x[i0]), b = to_f32(x[i1]);
-    x[i0] = from_f32<T>(a * c - b * s);
-    x[i1] = from_f32<T>(b * c + a * s);
+    float a = rope_src(row, pr, n_parts, part_stride, i0);
+    float b = rope_src(row, pr, n_parts, part_stride, i1);
+    if (rotate) {
+      float s, c;
+      sincosf((float)pos * inv_freq[p], &s, &c);
+      const float ra = a * c - b * s, rb = b * c + a * s;
+      a = ra;
+      b = rb;
+    }
+    const T ta = from_f32<T>(a), tb = from_f32<T>(b);
+    if (rotate || pr != nullptr) {
+      row[i0] = ta;
+      row[i1] = tb;
+    }
+    if (dst != nullptr) {
+      dst[i0] = ta;
+      dst[i1] = tb;
+    }
   }
-  if (kcache == nullptr) return;
-  __syncthreads();
-  const int seq = seq_of_token[t];
-  const int slot = slots[seq];
-  if (slot < 0) return;  // padding row
-  int r = pos;
-  if (ring_rows > 0) {
-    // of the tokens of this step that share a ring row only the last is kept
-    if (pos + ring_rows < len_after[seq]) return;
-    r = pos % ring_rows;
-  }
-  const int page = page_table[(size_t)slot * max_pages + r / AF_PAGE];
-  const int in_page = r % AF_PAGE;
-  const T* k = row + (size_t)nq * hd;
-  const T* v = k + (size_t)nkv * hd;
-  for (int idx = threadIdx.x; idx < nkv * hd; idx += blockDim.x) {
-    const int h = idx / hd, d = idx - h * hd;
-    const size_t dst = (((size_t)page * nkv + h) * AF_PAGE + in_page) * hd + d;
-    kcache[dst] = k[idx];
-    vcache[dst] = v[idx];
+  // elements beyond the rotary part
+  for (int i = rot_dim + threadIdx.x; i < hd; i += blockDim.x) {
+    const T v = from_f32<T>(rope_src(row, pr, n_parts, part_stride, i));
+    if (pr != nullptr) row[i] = v;
+    if (dst != nullptr) dst[i] = v;
   }
 }
 
@@ -92,7 +107,7 @@ AF_EXPORT int af_rope_cache_write(void* qkv, int dtype, int row_stride, const fl
   AF_REQUIRE(ring_rows % AF_PAGE == 0, "af_rope_cache_write: ring rows %d not whole pages", ring_rows);
   AF_REQUIRE((kcache == nullptr) == (vcache == nullptr), "af_rope_cache_write: k and v cache");
   AF_DISPATCH_DTYPE(dtype, T,
-                    rope_cache_kernel<T><<<n_tokens, 256, 0, stream>>>(
+                    rope_cache_kernel<T><<<dim3(n_tokens, nq + 2 * nkv), hd / 2 < 32 ? 32 : (hd / 2 > 256 ? 256 : hd / 2), 0, stream>>>(
                         (T*)qkv, row_stride, parts, n_parts, (size_t)part_stride, positions, seq_of_token,
                         slots, len_after, inv_freq, nq,
                         nkv, hd, rot_dim, pairing, (T*)kcache, (T*)vcache, page_table, max_pages,

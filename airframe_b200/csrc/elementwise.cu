@@ -121,6 +121,74 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
     yr[i] = from_f32<TY>(row[i] * inv2 * (offset + w_next[i]));
 }
 
+// The same for rows of up to 4096 elements with hidden % 4 == 0: one thread per
+// four elements, every load issued before the first reduction (the rows are
+// short; what costs is the chain of memory latencies, not the bytes).
+template <typename TA, typename TY>
+__global__ void __launch_bounds__(1024)
+add_rmsnorm_row_kernel(float* __restrict__ x, const TA* __restrict__ a, int n_parts, size_t part_stride,
+                       const float* __restrict__ w_post, TY* __restrict__ y, const float* __restrict__ w_next,
+                       int hidden, float eps_post, float eps_next, float offset) {
+  __shared__ float scratch[33];
+  const int r = blockIdx.x;
+  const int i = threadIdx.x * 4;
+  const bool on = i < hidden;
+  float av[4] = {0.f, 0.f, 0.f, 0.f}, xv[4] = {0.f, 0.f, 0.f, 0.f}, wp[4] = {0.f, 0.f, 0.f, 0.f},
+        wn[4] = {0.f, 0.f, 0.f, 0.f};
+  if (on) {
+    const size_t at = (size_t)r * hidden + i;
+    if constexpr (sizeof(TA) == 4) {
+      const float* ap = reinterpret_cast<const float*>(a) + at;
+      for (int p0 = 0; p0 < n_parts; p0 += 8) {
+        float4 t[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          t[u] = p0 + u < n_parts ? *reinterpret_cast<const float4*>(ap + (size_t)(p0 + u) * part_stride)
+                                  : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {
+          av[0] += t[u].x;
+          av[1] += t[u].y;
+          av[2] += t[u].z;
+          av[3] += t[u].w;
+        }
+      }
+    } else {
+      const uint2 raw = *reinterpret_cast<const uint2*>(a + at);
+      av[0] = __uint_as_float(raw.x << 16);
+      av[1] = __uint_as_float(raw.x & 0xffff0000u);
+      av[2] = __uint_as_float(raw.y << 16);
+      av[3] = __uint_as_float(raw.y & 0xffff0000u);
+    }
+    const float4 xt = *reinterpret_cast<const float4*>(x + at);
+    const float4 pt = *reinterpret_cast<const float4*>(w_post + i);
+    xv[0] = xt.x, xv[1] = xt.y, xv[2] = xt.z, xv[3] = xt.w;
+    wp[0] = pt.x, wp[1] = pt.y, wp[2] = pt.z, wp[3] = pt.w;
+    if (y != nullptr) {
+      const float4 nt = *reinterpret_cast<const float4*>(w_next + i);
+      wn[0] = nt.x, wn[1] = nt.y, wn[2] = nt.z, wn[3] = nt.w;
+    }
+  }
+  float ss = av[0] * av[0] + av[1] * av[1] + av[2] * av[2] + av[3] * av[3];
+  ss = block_sum(ss, scratch);
+  const float inv = rsqrtf(ss / (float)hidden + eps_post);
+  float ss2 = 0.f;
+#pragma unroll
+  for (int u = 0; u < 4; ++u) {
+    xv[u] = xv[u] + av[u] * inv * (offset + wp[u]);
+    ss2 += on ? xv[u] * xv[u] : 0.f;
+  }
+  if (on) *reinterpret_cast<float4*>(x + (size_t)r * hidden + i) = make_float4(xv[0], xv[1], xv[2], xv[3]);
+  if (y == nullptr) return;
+  ss2 = block_sum(ss2, scratch);
+  const float inv2 = rsqrtf(ss2 / (float)hidden + eps_next);
+  if (on) {
+    TY* yr = y + (size_t)r * hidden + i;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) yr[u] = from_f32<TY>(xv[u] * inv2 * (offset + wn[u]));
+  }
+}
+
 AF_EXPORT int af_add_rmsnorm(float* x, const void* a, int a_dtype, int n_parts, long long part_stride,
                              const float* w_post, void* y, int y_dtype, const float* w_next,
                              int n_rows, int hidden, float eps_post, float eps_next, float offset,
@@ -129,6 +197,18 @@ AF_EXPORT int af_add_rmsnorm(float* x, const void* a, int a_dtype, int n_parts, 
   AF_REQUIRE(n_rows > 0 && hidden > 0 && n_parts >= 1, "af_add_rmsnorm: bad sizes");
   AF_REQUIRE(hidden * sizeof(float) <= 160 * 1024, "af_add_rmsnorm: hidden %d too wide", hidden);
   AF_REQUIRE(n_parts == 1 || a_dtype == AF_F32, "af_add_rmsnorm: partial sums must be float");
+  const bool aligned = (((uintptr_t)x | (uintptr_t)a | (uintptr_t)w_post | (uintptr_t)w_next) & 15) == 0 &&
+                       (part_stride % 4 == 0);
+  if (hidden % 4 == 0 && hidden <= 4096 && aligned) {
+    const int threads = ((hidden / 4 + 31) / 32) * 32;
+#define LAUNCH_ROW(TA, TY)                                                                           \
+  add_rmsnorm_row_kernel<TA, TY><<<n_rows, threads, 0, stream>>>(x, (const TA*)a, n_parts,           \
+                                                                 (size_t)part_stride, w_post, (TY*)y, \
+                                                                 w_next, hidden, eps_post, eps_next, offset)
+    AF_DISPATCH_DTYPE(a_dtype, TA, AF_DISPATCH_DTYPE(y_dtype, TY, LAUNCH_ROW(TA, TY)));
+#undef LAUNCH_ROW
+    AF_CHECK_LAUNCH("af_add_rmsnorm");
+  }
   const size_t smem = (size_t)hidden * sizeof(float);
 #define LAUNCH(TA, TY)                                                                          \
   do {                                                                                          \

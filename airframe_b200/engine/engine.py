@@ -27,7 +27,7 @@ class Engine:
     longest single sequence (the model's own limit by default)."""
 
     def __init__(self, model: Model, max_tokens: int, max_context: Optional[int] = None,
-                 max_sequences: Optional[int] = None):
+                 max_sequences: Optional[int] = None, use_graphs: bool = True):
         if not model.loaded:
             raise ValueError("the model has no weights yet")
         self.model = model
@@ -38,6 +38,11 @@ class Engine:
                                    dtype=model.ctx.compute_dtype, device=self.device,
                                    max_sequences=max_sequences)
         self.vocab_size = model.spec.vocab_size
+        # decode steps of models whose parts allow it are captured into CUDA graphs,
+        # one per padded batch size
+        self.use_graphs = bool(use_graphs) and self.device.type == "cuda" and model.graph_safe
+        self._graphs: dict = {}
+        self.replayed_launches = 0      # kernels launched through graph replays
 
     # ------------------------------------------------------------------ slots
 
@@ -81,16 +86,82 @@ class Engine:
             raise StepError("sequences that go on bring one token each")
         return lens
 
-    def step(self, entries, pad_to: int = 0):
+    def step(self, entries, pad_to: int = 0, borrow: bool = False):
         """Run one step.  Returns float32 logits [wanted, vocab] on the device,
         in the order of the entries and of their ``want`` lists, or None when
-        nothing is wanted."""
+        nothing is wanted.  ``borrow``: the caller uses the logits before the
+        next step and may get a buffer that the next step overwrites (saves a
+        copy when the step ran as a CUDA graph)."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         lens = self.check(entries)
         growth = {e.slot: n + len(e.tokens) for e, n in zip(entries, lens)}
         self.cache.reserve(growth)
         self.cache.flush()
-        batch = build_batch(entries, lens, self.device, pad_to=pad_to)
-        logits = self.model.forward(batch, self.cache)
+        if self.use_graphs and lens[0] > 0 and all(e.want == [0] for e in entries):
+            logits = self._decode_graphed(entries, lens)
+            if not borrow:
+                logits = logits.clone()
+        else:
+            batch = build_batch(entries, lens, self.device, pad_to=pad_to)
+            logits = self.model.forward(batch, self.cache)
         self.cache.commit(growth)
         return logits
+
+    # ------------------------------------------------------------------ captured decode steps
+
+    @staticmethod
+    def padded_batch(n: int) -> int:
+        """Decode batches are padded (slot -1, token 0) to these sizes so that
+        few graphs serve every batch size."""
+        for b in (1, 2, 4, 8, 12, 16, 24, 32, 48, 64, 96, 128, 192, 256):
+            if n <= b:
+                return b
+        return (n + 127) // 128 * 128
+
+    def _decode_graphed(self, entries, lens):
+        """One decode step, every sequence wanting its token's logits, through
+        a CUDA graph.  The result is the graph's own output buffer: it is
+        valid until the next step of the same padded size."""
+        B = len(entries)
+        Bp = self.padded_batch(B)
+        g = self._graphs.get(Bp)
+        if g is None:
+            g = self._capture(Bp)
+            self._graphs[Bp] = g
+        tokens = [e.tokens[0] for e in entries] + [0] * (Bp - B)
+        positions = list(lens) + [0] * (Bp - B)
+        slots = [e.slot for e in entries] + [-1] * (Bp - B)
+        len_after = [n + 1 for n in lens] + [0] * (Bp - B)
+        host = torch.tensor(tokens + positions + slots + len_after, dtype=torch.int32).pin_memory()
+        g["dynamic"].copy_(host, non_blocking=True)
+        g["graph"].replay()
+        self.replayed_launches += g["launches"]
+        return g["logits"][:B]
+
+    def _capture(self, Bp: int) -> dict:
+        dev = self.device
+        # [tokens | positions | slots | len_after] change every step; the rest is fixed
+        dynamic = torch.zeros(4 * Bp, dtype=torch.int32, device=dev)
+        dynamic[2 * Bp: 3 * Bp] = -1
+        fixed = torch.cat([torch.arange(Bp, dtype=torch.int32), torch.arange(Bp + 1, dtype=torch.int32),
+                           torch.arange(Bp, dtype=torch.int32)]).to(dev)
+        batch = StepBatch(
+            is_prefill=False, n_tokens=Bp, n_seqs=Bp, max_len=1, seq_lens=[1] * Bp,
+            tokens=dynamic[:Bp], positions=dynamic[Bp: 2 * Bp], seq_of_token=fixed[:Bp],
+            slots=dynamic[2 * Bp: 3 * Bp], len_after=dynamic[3 * Bp:], seq_starts=fixed[Bp: 2 * Bp + 1],
+            want_rows=fixed[2 * Bp + 1:], n_want=Bp,
+            max_len_after=self.max_context)          # kernels size their splits for the longest context
+        # a run outside the graph first: kernels set their attributes and load lazily
+        side = torch.cuda.Stream(device=dev)
+        side.wait_stream(torch.cuda.current_stream(dev))
+        with torch.cuda.stream(side):
+            self.model.forward(batch, self.cache)
+        torch.cuda.current_stream(dev).wait_stream(side)
+        torch.cuda.synchronize(dev)
+        from .. import kernels
+        graph = torch.cuda.CUDAGraph()
+        n0 = kernels.launch_count()
+        with torch.cuda.graph(graph):
+            logits = self.model.forward(batch, self.cache)
+        return {"graph": graph, "dynamic": dynamic, "logits": logits, "batch": batch, "fixed": fixed,
+                "launches": kernels.launch_count() - n0}

@@ -151,6 +151,6 @@ class GenerationLoop:
             active = going
             if not active:
                 break
-            logits = self.engine.step([StepEntry(s.slot, [s.out[-1]], [0]) for s in active])
+            logits = self.engine.step([StepEntry(s.slot, [s.out[-1]], [0]) for s in active], borrow=True)
             for s in active:
                 s.length += 1

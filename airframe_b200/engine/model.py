@@ -60,6 +60,11 @@ class Model:
             p.load(weights)
         self.loaded = True
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a decode step of this model can be captured into a CUDA graph."""
+        return all(p.graph_safe for p in self.parts())
+
     # ------------------------------------------------------------------ cache
 
     def cache_needs(self) -> list:

@@ -313,7 +313,7 @@ def attn_decode_splits(batch: int, nkv: int, max_len: int, window: int) -> int:
     """How many ways the keys of a sequence are split so that the step fills the GPU."""
     rows = min(max_len, window) if window else max_len
     pages = max(1, (rows + PAGE - 1) // PAGE + (1 if window else 0))
-    want = max(1, (4 * 148) // max(1, batch * nkv))
+    want = max(1, 148 // max(1, batch * nkv))      # one wave of blocks, each with a long run of pages
     return max(1, min(want, pages, 64))
 
 
@@ -335,7 +335,8 @@ def attn_decode_split(out, q, kcache, vcache, page_table, slots, lens, nq, nkv, 
         _ptr(out), c_longlong(_rows(out, "out")), _ptr(q), c_longlong(_rows(q, "q")), _ptr(kcache), _ptr(vcache),
         _ptr(page_table, "page_table", torch.int32), c_int(page_table.shape[1]), _ptr(slots, "slots", torch.int32),
         _ptr(lens, "lens", torch.int32), c_int(B), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_float(cap),
-        c_int(window), c_int(ring_rows), c_int(n_splits), _ptr(scratch, "scratch", torch.float32), _stream()))
+        c_int(window), c_int(ring_rows), c_int(n_splits), _ptr(scratch, "scratch", torch.float32),
+        _ptr(error_word(q.device), "err", torch.int32), _stream()))
 
 
 def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window) -> None:

@@ -26,6 +26,11 @@ class Attention(Mixer):
     (a PartSpec of category ``position``), ``q_weight``/``k_weight``/``v_weight``/
     ``o_weight`` (tensor names)."""
 
+    @property
+    def graph_safe(self):
+        return self.position.graph_safe
+
+
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
         self.hidden = int(self.param("hidden_size"))

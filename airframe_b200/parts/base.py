@@ -94,6 +94,10 @@ class Part:
     """
     category = ""
     kind = ""
+    # True when ``forward`` only launches kernels on the current stream (no
+    # host reads of device data, no synchronisation), so that a decode step can
+    # be captured into a CUDA graph.  A model is captured only if all its parts say so.
+    graph_safe = False
 
     def __init__(self, params: dict, ctx: BuildContext):
         self.params = params
@@ -171,6 +175,10 @@ class Block(Part):
 
     def children(self):
         return [self.mixer, self.feed_forward, *self.norms.values()]
+
+    @property
+    def graph_safe(self):
+        return all(c.graph_safe for c in self.children())
 
     def weight_decls(self):
         return [d for c in self.children() for d in c.weight_decls()]

@@ -20,6 +20,8 @@ from .linear import linear
 @register_part("embedding", "token_embedding")
 class TokenEmbedding(Part):
     """Parameters: ``weight``, ``vocab_size``, ``hidden_size``, ``scale``."""
+    graph_safe = True
+
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
@@ -47,6 +49,8 @@ class LmHead(Part):
     """Parameters: ``vocab_size``, ``hidden_size``, ``softcap`` (0 = off) and
     either ``weight`` or ``tied_to`` (+ ``optional_weight`` that wins when the
     folder holds it)."""
+    graph_safe = True
+
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)

@@ -19,6 +19,8 @@ from .linear import gated_linear, linear_split
 class GatedMlp(FeedForward):
     """Parameters: ``hidden_size``, ``intermediate_size``, ``activation``
     (``gelu_tanh`` or ``silu``), ``gate_weight``/``up_weight``/``down_weight``."""
+    graph_safe = True
+
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)

@@ -18,6 +18,8 @@ from .linear import PartialSums
 @register_part("norm", "rms_norm")
 class RmsNorm(Norm):
     """Parameters: ``weight`` (tensor name), ``size``, ``eps``, ``weight_offset``."""
+    graph_safe = True
+
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)

@@ -21,6 +21,8 @@ from .base import PositionEncoding, register_part
 @register_part("position", "rope")
 class Rope(PositionEncoding):
     """Parameters: ``theta``, ``rotary_dim``, ``pairing``."""
+    graph_safe = True
+
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)
@@ -55,6 +57,8 @@ class Rope(PositionEncoding):
 @register_part("position", "none")
 class NoPosition(PositionEncoding):
     """No encoding: only stores k and v."""
+    graph_safe = True
+
 
     def __init__(self, params, ctx):
         super().__init__(params, ctx)

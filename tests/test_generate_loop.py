@@ -29,7 +29,7 @@ class FakeEngine:
         self.pool.give_back(s)
         del self.lens[s]
 
-    def step(self, entries):
+    def step(self, entries, borrow=False):
         starting = [self.lens[e.slot] == 0 for e in entries]
         assert all(starting) or not any(starting)
         if not all(starting):
@@ -133,7 +133,7 @@ def test_bad_requests_and_zero_tokens():
 
 def test_slots_come_back_when_a_step_fails():
     class Failing(FakeEngine):
-        def step(self, entries):
+        def step(self, entries, borrow=False):
             if len(self.steps) == 1:
                 raise RuntimeError("boom")
             return super().step(entries)
