@@ -304,8 +304,25 @@ def gemm_tc(out, x, w, cap: float = 0.0, splits: int = 1, dual_up_offset: int = 
                              _ptr(error_word(x.device), "err", torch.int32), _stream()))
 
 
+def attn_prefill_mma(out, q, k, v, seq_starts, n_seqs: int, max_len: int, nq, nkv, hd, scale, cap, window) -> None:
+    """bfloat16 prefill attention on the tensor cores; sequences packed row
+    after row, ``seq_starts`` int32 [n_seqs + 1]."""
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attn_prefill_mma: bfloat16 only")
+    _check(_lib().af_attn_prefill(
+        _ptr(out), c_longlong(_rows(out, "out")), _ptr(q), c_longlong(_rows(q, "q")), _ptr(k),
+        c_longlong(_rows(k, "k")), _ptr(v), c_longlong(_rows(v, "v")), _ptr(seq_starts, "seq_starts", torch.int32),
+        c_int(n_seqs), c_int(max_len), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_float(cap), c_int(window),
+        _stream()))
+
+
 def attn_prefill(out, q, k, v, batch, nq, nkv, hd, scale, cap, window) -> None:
-    """Attention of a prefill step: picks the kernel."""
+    """Attention of a prefill step: the tensor-core kernel for bfloat16 and
+    the head sizes it takes, else the plain kernel."""
+    if (q.dtype == torch.bfloat16 and _lib().af_attn_prefill_supported(c_int(hd))
+            and all(t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 for t in (q, k, v))):
+        attn_prefill_mma(out, q, k, v, batch.seq_starts, batch.n_seqs, batch.max_len, nq, nkv, hd, scale, cap, window)
+        return
     attn_prefill_plain(out, q, k, v, batch.positions, nq, nkv, hd, scale, cap, window)
 
 

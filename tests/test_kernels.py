@@ -368,3 +368,47 @@ def test_gemm_tensor_cores_refuses_unaligned(K):
     assert not K.gemm_tc_supported(x, w, None)
     with pytest.raises(K.KernelError, match="K % 8"):
         K.gemm_tc(torch.zeros(4, 8, dtype=torch.bfloat16, device=DEV), x, w)
+
+
+@pytest.mark.parametrize("hd,nq,nkv,window,cap", [(64, 4, 2, 0, 50.0), (128, 6, 2, 70, 0.0), (256, 4, 2, 300, 30.0),
+                                                  (256, 2, 1, 0, 0.0), (64, 3, 3, 5, 20.0), (128, 2, 2, 64, 10.0)])
+def test_attention_prefill_tensor_cores(K, hd, nq, nkv, window, cap):
+    torch.manual_seed(hd + window)
+    lens = [37, 1, 200, 128, 129, 64, 513]
+    T = sum(lens)
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd).to(torch.bfloat16).to(DEV)      # packed rows, as the mixer holds them
+    q, k, v = qkv[:, : nq * hd], qkv[:, nq * hd: (nq + nkv) * hd], qkv[:, (nq + nkv) * hd:]
+    starts = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    out = torch.full((T, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    scale = 1.1 / math.sqrt(hd)
+    K.attn_prefill_mma(out, q, k, v, starts, len(lens), max(lens), nq, nkv, hd, scale, cap, window)
+    o = 0
+    for n in lens:
+        ref = plain.attention(q[o:o + n].double().cpu().reshape(n, nq, hd), k[o:o + n].double().cpu().reshape(n, nkv, hd),
+                              v[o:o + n].double().cpu().reshape(n, nkv, hd), scale, cap, window or None)
+        close(out[o:o + n], ref, torch.bfloat16, scale=1.0)
+        o += n
+
+
+def test_attention_prefill_tensor_cores_finds_one_far_key_and_the_window_edge(K):
+    hd, nq, nkv, n = 128, 2, 1, 700
+    torch.manual_seed(4)
+    q = (torch.randn(n, nq * hd) * 0.05)
+    base_k = torch.randn(n, nkv * hd) * 0.01
+    v = torch.randn(n, nkv * hd).to(torch.bfloat16)
+    starts = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+    row = n - 1
+    qv = torch.randn(nq, hd)
+    q[row] = qv.reshape(-1)
+    for window, far in [(0, 5), (0, 333), (257, row - 256), (257, row - 257), (64, row - 63), (64, row - 64)]:
+        k = base_k.clone()
+        k[far] = (qv[0] + qv[1]) * 8.0
+        qb, kb = q.to(torch.bfloat16), k.to(torch.bfloat16)
+        out = torch.empty(n, nq * hd, dtype=torch.bfloat16, device=DEV)
+        K.attn_prefill_mma(out, qb.to(DEV), kb.to(DEV), v.to(DEV), starts, 1, n, nq, nkv, hd, 1.0, 0.0, window)
+        ref = plain.attention(qb.double().reshape(n, nq, hd), kb.double().reshape(n, nkv, hd),
+                              v.double().reshape(n, nkv, hd), 1.0, 0.0, window or None)
+        close(out, ref, torch.bfloat16, scale=1.0)
+        visible = window == 0 or (row - far) < window
+        near = (out[row].double().cpu().reshape(nq, hd) - v[far].double()).abs().max()
+        assert (near < 0.05) == visible, (window, far, float(near))
