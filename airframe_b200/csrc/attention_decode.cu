@@ -15,6 +15,9 @@
 //
 // Scores are 32-bit; softcap uses tanh.approx and the softmax ex2.approx, which
 // is what the bfloat16 path allows; the 32-bit path uses the plain kernel.
+#include <mutex>
+
+#include "airframe_b200.h"
 #include "common.cuh"
 
 namespace {
@@ -409,4 +412,59 @@ AF_EXPORT int af_attn_decode(void* out, long long out_stride, const void* q, lon
   if (hd == 64) return launch_decode_hd<64>(a, o, out_stride, batch, stream);
   if (hd == 128) return launch_decode_hd<128>(a, o, out_stride, batch, stream);
   return launch_decode_hd<256>(a, o, out_stride, batch, stream);
+}
+
+// ---------------------------------------------------------------- no allocation
+
+// Scratch of af_attn_decode_static: the split pass's partial results.  It lives
+// in the library image, so every GPU that loads the library holds these 4 MiB
+// until the process exits.
+static __device__ __align__(256) float g_decode_scratch[AF_ATTN_DECODE_STATIC_FLOATS];
+
+namespace {
+constexpr int kMaxDevices = 64;
+float* g_scratch_addr[kMaxDevices] = {};
+std::mutex g_scratch_mutex;
+
+// The array's address on the current device.  In host code the array's name
+// stands for a host-side shadow, not for device memory, so the address comes
+// from cudaGetSymbolAddress, once per device, with that device current.
+int decode_scratch_address(float** out) {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return af_fail((int)e, "af_attn_decode_static: cudaGetDevice: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return af_fail(-1, "af_attn_decode_static: device ordinal %d beyond %d", dev, kMaxDevices);
+  std::lock_guard<std::mutex> lock(g_scratch_mutex);
+  if (g_scratch_addr[dev] == nullptr) {
+    float* p = nullptr;
+    e = cudaGetSymbolAddress((void**)&p, g_decode_scratch);
+    if (e != cudaSuccess || p == nullptr)
+      return af_fail(e != cudaSuccess ? (int)e : -1, "af_attn_decode_static: cudaGetSymbolAddress: %s",
+                     cudaGetErrorString(e));
+    g_scratch_addr[dev] = p;
+  }
+  *out = g_scratch_addr[dev];
+  return 0;
+}
+}  // namespace
+
+AF_EXPORT long long af_attn_decode_static_capacity() { return AF_ATTN_DECODE_STATIC_FLOATS; }
+
+AF_EXPORT int af_attn_decode_static(void* out, long long out_stride, const void* q, long long q_stride,
+                                    const void* kcache, const void* vcache, const int* page_table, int max_pages,
+                                    const int* slots, const int* lens, int batch, int nq, int nkv, int hd,
+                                    float scale, float cap, int window, int ring_rows, int n_splits, int* err,
+                                    cudaStream_t stream) {
+  if (batch == 0) return 0;
+  AF_REQUIRE(batch > 0 && nq > 0 && hd > 0 && n_splits >= 1, "af_attn_decode_static: bad sizes");
+  const long long need = af_attn_decode_scratch(batch, nq, hd, n_splits);
+  AF_REQUIRE(need <= AF_ATTN_DECODE_STATIC_FLOATS,
+             "af_attn_decode_static: batch %d x heads %d x splits %d x (head_dim %d + 2) = %lld floats of scratch, "
+             "the built-in array holds %d; use fewer splits or af_attn_decode with scratch of your own",
+             batch, nq, n_splits, hd, need, AF_ATTN_DECODE_STATIC_FLOATS);
+  float* scratch = nullptr;
+  const int rc = decode_scratch_address(&scratch);
+  if (rc) return rc;
+  return af_attn_decode(out, out_stride, q, q_stride, kcache, vcache, page_table, max_pages, slots, lens, batch, nq,
+                        nkv, hd, scale, cap, window, ring_rows, n_splits, scratch, err, stream);
 }
