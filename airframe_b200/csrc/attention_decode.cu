@@ -145,6 +145,8 @@ attn_decode_split_kernel(DecodeArgs a) {
   __shared__ int give_up_s;
   volatile int* give_up = &give_up_s;
 
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x;
   const int group = a.nq / a.nkv;
   const int tiles = group / GT;
@@ -317,6 +319,8 @@ template <int HD>
 __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long long out_stride,
                                          const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          int nq, int n_splits) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int b = blockIdx.x, h = blockIdx.y;
   const size_t p0 = ((size_t)b * nq + h) * n_splits;
   float M = -INFINITY;
@@ -346,9 +350,9 @@ int launch_decode(const DecodeArgs& a, __nv_bfloat16* out, long long out_stride,
   }
   const int group = a.nq / a.nkv;
   dim3 grid(batch, a.nkv * (group / GT), a.n_splits);
-  attn_decode_split_kernel<HD, GT><<<grid, DA_THREADS, smem, stream>>>(a);
+  af_launch(attn_decode_split_kernel<HD, GT>, dim3(grid), dim3(DA_THREADS), smem, stream, a);
   AF_COUNT_LAUNCH("af_attn_decode (split)");
-  attn_decode_merge_kernel<HD><<<dim3(batch, a.nq), HD < 128 ? HD : 128, 0, stream>>>(
+  af_launch(attn_decode_merge_kernel<HD>, dim3(dim3(batch, a.nq)), dim3(HD < 128 ? HD : 128), 0, stream, 
       out, out_stride, a.part_o, a.part_ml, a.nq, a.n_splits);
   AF_CHECK_LAUNCH("af_attn_decode (merge)");
 }

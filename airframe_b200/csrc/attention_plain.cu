@@ -39,6 +39,8 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const flo
                                   int nq, int nkv, int hd, int rot_dim, int pairing,
                                   T* __restrict__ kcache, T* __restrict__ vcache,
                                   const int* __restrict__ page_table, int max_pages, int ring_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x, head = blockIdx.y;
   const int pos = positions[t];
   T* row = qkv + (size_t)t * row_stride + (size_t)head * hd;
@@ -107,7 +109,7 @@ AF_EXPORT int af_rope_cache_write(void* qkv, int dtype, int row_stride, const fl
   AF_REQUIRE(ring_rows % AF_PAGE == 0, "af_rope_cache_write: ring rows %d not whole pages", ring_rows);
   AF_REQUIRE((kcache == nullptr) == (vcache == nullptr), "af_rope_cache_write: k and v cache");
   AF_DISPATCH_DTYPE(dtype, T,
-                    rope_cache_kernel<T><<<dim3(n_tokens, nq + 2 * nkv), hd / 2 < 32 ? 32 : (hd / 2 > 256 ? 256 : hd / 2), 0, stream>>>(
+                    af_launch(rope_cache_kernel<T>, dim3(dim3(n_tokens, nq + 2 * nkv)), dim3(hd / 2 < 32 ? 32 : (hd / 2 > 256 ? 256 : hd / 2)), 0, stream, 
                         (T*)qkv, row_stride, parts, n_parts, (size_t)part_stride, positions, seq_of_token,
                         slots, len_after, inv_freq, nq,
                         nkv, hd, rot_dim, pairing, (T*)kcache, (T*)vcache, page_table, max_pages,
@@ -179,6 +181,8 @@ __global__ void attn_prefill_plain_kernel(T* __restrict__ out, int out_stride, c
                                           const int* __restrict__ positions,
                                           int n_tokens, int nq, int nkv, int hd, float scale, float cap,
                                           int window) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (w >= (long long)n_tokens * nq) return;
@@ -209,7 +213,7 @@ AF_EXPORT int af_attn_prefill_plain(void* out, int out_stride, const void* q, in
   const long long blocks = (warps + wpb - 1) / wpb;
   AF_REQUIRE(blocks < (1ll << 31), "af_attn_prefill_plain: too many rows");
   AF_DISPATCH_DTYPE(dtype, T,
-                    attn_prefill_plain_kernel<T><<<(unsigned)blocks, wpb * 32, 0, stream>>>(
+                    af_launch(attn_prefill_plain_kernel<T>, dim3((unsigned)blocks), dim3(wpb * 32), 0, stream, 
                         (T*)out, out_stride, (const T*)q, q_stride, (const T*)k, k_stride, (const T*)v,
                         v_stride, positions, n_tokens, nq, nkv, hd, scale, cap, window));
   AF_CHECK_LAUNCH("af_attn_prefill_plain");
@@ -224,6 +228,8 @@ __global__ void attn_decode_plain_kernel(T* __restrict__ out, int out_stride, co
                                          int max_pages, const int* __restrict__ slots,
                                          const int* __restrict__ lens, int batch, int nq, int nkv, int hd,
                                          float scale, float cap, int window, int ring_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int lane = threadIdx.x & 31;
   const long long w = (long long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (w >= (long long)batch * nq) return;
@@ -263,7 +269,7 @@ AF_EXPORT int af_attn_decode_plain(void* out, int out_stride, const void* q, int
   const int wpb = 4;
   const long long blocks = (warps + wpb - 1) / wpb;
   AF_DISPATCH_DTYPE(dtype, T,
-                    attn_decode_plain_kernel<T><<<(unsigned)blocks, wpb * 32, 0, stream>>>(
+                    af_launch(attn_decode_plain_kernel<T>, dim3((unsigned)blocks), dim3(wpb * 32), 0, stream, 
                         (T*)out, out_stride, (const T*)q, q_stride, (const T*)kcache, (const T*)vcache,
                         page_table, max_pages, slots, lens, batch, nq, nkv, hd, scale, cap, window,
                         ring_rows));

@@ -93,6 +93,8 @@ __device__ __forceinline__ void pf_load_tile(unsigned char* tile, const __nv_bfl
 template <int HD>
 __global__ void __launch_bounds__(PF_THREADS, 1)
 attn_prefill_mma_kernel(PrefillArgs a) {
+  pdl_launch_dependents();
+  pdl_wait();
   constexpr int KSTEPS = HD / 16;      // k-steps of Q K^T
   constexpr int ONT = HD / 8;          // n-tiles of the output
   constexpr int SNT = PF_BN / 8;       // n-tiles of the scores
@@ -264,7 +266,7 @@ int launch_prefill(const PrefillArgs& a, int n_seqs, int max_len, cudaStream_t s
     configured = true;
   }
   dim3 grid((max_len + PF_BM - 1) / PF_BM, n_seqs, a.nq);
-  attn_prefill_mma_kernel<HD><<<grid, PF_THREADS, smem, stream>>>(a);
+  af_launch(attn_prefill_mma_kernel<HD>, dim3(grid), dim3(PF_THREADS), smem, stream, a);
   AF_CHECK_LAUNCH("af_attn_prefill");
 }
 

@@ -45,6 +45,36 @@ extern unsigned long long g_af_launches;
     return 0;                 \
   } while (0)
 
+// ---- programmatic dependent launch
+// Kernels are launched so that a kernel's blocks may become resident while the
+// kernel before it in the stream still runs.  Every kernel calls
+// pdl_launch_dependents() at its start and pdl_wait() before it reads or writes
+// global memory that earlier kernels touch; pdl_wait() returns once every
+// earlier kernel has finished and its memory is visible.  What a kernel does
+// before the wait (barrier set-up, TMEM allocation, loads of weights) overlaps
+// the tail of its predecessor.  af_set_pdl(0) turns the launch attribute off;
+// the two instructions are then no-ops.
+extern int g_af_pdl;
+
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t af_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = stream;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = g_af_pdl ? 1 : 0;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+
 template <typename T>
 __device__ __forceinline__ float to_f32(T v);
 template <>

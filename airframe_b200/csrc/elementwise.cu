@@ -24,6 +24,10 @@ AF_EXPORT const char* af_last_error() { return g_error; }
 AF_EXPORT int af_abi_version() { return 1; }
 
 unsigned long long g_af_launches = 0;
+int g_af_pdl = 1;
+
+// 1 (default): kernels may start while their predecessor in the stream is finishing; 0: plain stream order.
+AF_EXPORT void af_set_pdl(int on) { g_af_pdl = on ? 1 : 0; }
 
 AF_EXPORT unsigned long long af_launch_count() { return g_af_launches; }
 
@@ -32,6 +36,8 @@ AF_EXPORT unsigned long long af_launch_count() { return g_af_launches; }
 template <typename TW>
 __global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ table,
                              const int* __restrict__ ids, int hidden, int vocab, float scale) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int t = blockIdx.x;
   int id = ids[t];
   // ids are validated on the host; a bad one yields zeros rather than a wild read
@@ -46,7 +52,7 @@ AF_EXPORT int af_embed(float* out, const void* table, int table_dtype, const int
   if (n_tokens == 0) return 0;
   AF_REQUIRE(n_tokens > 0 && hidden > 0 && vocab > 0, "af_embed: bad sizes");
   AF_DISPATCH_DTYPE(table_dtype, TW,
-                    embed_kernel<TW><<<n_tokens, 256, 0, stream>>>(out, (const TW*)table, ids, hidden,
+                    af_launch(embed_kernel<TW>, dim3(n_tokens), dim3(256), 0, stream, out, (const TW*)table, ids, hidden,
                                                                   vocab, scale));
   AF_CHECK_LAUNCH("af_embed");
 }
@@ -59,6 +65,8 @@ template <typename TY>
 __global__ void rmsnorm_kernel(TY* __restrict__ y, const float* __restrict__ x,
                                const float* __restrict__ w, const int* __restrict__ rows, int hidden,
                                float eps, float offset) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const float* xr = x + (size_t)(rows ? rows[r] : r) * hidden;
@@ -79,7 +87,7 @@ AF_EXPORT int af_rmsnorm(void* y, int y_dtype, const float* x, const float* w, c
   if (n_rows == 0) return 0;
   AF_REQUIRE(n_rows > 0 && hidden > 0, "af_rmsnorm: bad sizes");
   AF_DISPATCH_DTYPE(y_dtype, TY,
-                    rmsnorm_kernel<TY><<<n_rows, 256, 0, stream>>>((TY*)y, x, w, rows, hidden, eps,
+                    af_launch(rmsnorm_kernel<TY>, dim3(n_rows), dim3(256), 0, stream, (TY*)y, x, w, rows, hidden, eps,
                                                                   offset));
   AF_CHECK_LAUNCH("af_rmsnorm");
 }
@@ -92,6 +100,8 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
                                    size_t part_stride, const float* __restrict__ w_post,
                                    TY* __restrict__ y, const float* __restrict__ w_next, int hidden,
                                    float eps_post, float eps_next, float offset) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ float row[];  // hidden floats: a, then the new x
   __shared__ float scratch[33];
   const int r = blockIdx.x;
@@ -129,6 +139,8 @@ __global__ void __launch_bounds__(1024)
 add_rmsnorm_row_kernel(float* __restrict__ x, const TA* __restrict__ a, int n_parts, size_t part_stride,
                        const float* __restrict__ w_post, TY* __restrict__ y, const float* __restrict__ w_next,
                        int hidden, float eps_post, float eps_next, float offset) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   const int i = threadIdx.x * 4;
@@ -202,7 +214,7 @@ AF_EXPORT int af_add_rmsnorm(float* x, const void* a, int a_dtype, int n_parts, 
   if (hidden % 4 == 0 && hidden <= 4096 && aligned) {
     const int threads = ((hidden / 4 + 31) / 32) * 32;
 #define LAUNCH_ROW(TA, TY)                                                                           \
-  add_rmsnorm_row_kernel<TA, TY><<<n_rows, threads, 0, stream>>>(x, (const TA*)a, n_parts,           \
+  af_launch(add_rmsnorm_row_kernel<TA, TY>, dim3(n_rows), dim3(threads), 0, stream, x, (const TA*)a, n_parts,           \
                                                                  (size_t)part_stride, w_post, (TY*)y, \
                                                                  w_next, hidden, eps_post, eps_next, offset)
     AF_DISPATCH_DTYPE(a_dtype, TA, AF_DISPATCH_DTYPE(y_dtype, TY, LAUNCH_ROW(TA, TY)));
@@ -215,7 +227,7 @@ AF_EXPORT int af_add_rmsnorm(float* x, const void* a, int a_dtype, int n_parts, 
     if (smem > 48 * 1024)                                                                       \
       cudaFuncSetAttribute(add_rmsnorm_kernel<TA, TY>, cudaFuncAttributeMaxDynamicSharedMemorySize, \
                            (int)smem);                                                          \
-    add_rmsnorm_kernel<TA, TY><<<n_rows, 256, smem, stream>>>(                                  \
+    af_launch(add_rmsnorm_kernel<TA, TY>, dim3(n_rows), dim3(256), smem, stream,                                   \
         x, (const TA*)a, n_parts, (size_t)part_stride, w_post, (TY*)y, w_next, hidden, eps_post, \
         eps_next, offset);                                                                      \
   } while (0)
@@ -237,6 +249,8 @@ __device__ __forceinline__ float act_f32(float g, int act) {
 // out[m, i] = act(gu[m, i]) * gu[m, inter + i]
 template <typename T>
 __global__ void gated_act_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, int act) {
+  pdl_launch_dependents();
+  pdl_wait();
   const int m = blockIdx.x;
   const T* g = gu + (size_t)m * 2 * inter;
   const T* u = g + inter;
@@ -252,7 +266,7 @@ AF_EXPORT int af_gated_act(void* out, const void* gu, int dtype, int n_rows, int
   AF_REQUIRE(act == AF_ACT_GELU_TANH || act == AF_ACT_SILU, "af_gated_act: unknown activation %d", act);
   dim3 grid(n_rows, (inter + 255) / 256 < 64 ? (inter + 255) / 256 : 64);
   AF_DISPATCH_DTYPE(dtype, T,
-                    gated_act_kernel<T><<<grid, 256, 0, stream>>>((T*)out, (const T*)gu, inter, act));
+                    af_launch(gated_act_kernel<T>, dim3(grid), dim3(256), 0, stream, (T*)out, (const T*)gu, inter, act));
   AF_CHECK_LAUNCH("af_gated_act");
 }
 
@@ -260,6 +274,8 @@ AF_EXPORT int af_gated_act(void* out, const void* gu, int dtype, int n_rows, int
 
 template <typename T>
 __global__ void add_kernel(float* __restrict__ x, const T* __restrict__ a, size_t n) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (size_t)gridDim.x * blockDim.x)
     x[i] += to_f32(a[i]);
@@ -269,13 +285,15 @@ AF_EXPORT int af_add(float* x, const void* a, int a_dtype, long long n, cudaStre
   if (n == 0) return 0;
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  AF_DISPATCH_DTYPE(a_dtype, T, add_kernel<T><<<(int)blocks, 256, 0, stream>>>(x, (const T*)a, (size_t)n));
+  AF_DISPATCH_DTYPE(a_dtype, T, af_launch(add_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, x, (const T*)a, (size_t)n));
   AF_CHECK_LAUNCH("af_add");
 }
 
 // ---------------------------------------------------------------- softcap
 
 __global__ void softcap_kernel(float* __restrict__ z, size_t n, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < n;
        i += (size_t)gridDim.x * blockDim.x)
     z[i] = softcap_f32(z[i], cap);
@@ -285,6 +303,6 @@ AF_EXPORT int af_softcap(float* z, long long n, float cap, cudaStream_t stream) 
   if (n == 0 || cap <= 0.f) return 0;
   long long blocks = (n + 255) / 256;
   if (blocks > 148 * 16) blocks = 148 * 16;
-  softcap_kernel<<<(int)blocks, 256, 0, stream>>>(z, (size_t)n, cap);
+  af_launch(softcap_kernel, dim3((int)blocks), dim3(256), 0, stream, z, (size_t)n, cap);
   AF_CHECK_LAUNCH("af_softcap");
 }

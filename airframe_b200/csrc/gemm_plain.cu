@@ -14,6 +14,8 @@ template <typename T, typename TO>
 __global__ void __launch_bounds__(256)
 gemm_plain_kernel(TO* __restrict__ out, int ldo, const T* __restrict__ x, int ldx,
                   const T* __restrict__ w, int ldw, int M, int N, int K, float cap) {
+  pdl_launch_dependents();
+  pdl_wait();
   __shared__ float xs[GP_BK][GP_BM + 1];
   __shared__ float ws[GP_BK][GP_BN + 1];
   const int tid = threadIdx.x;
@@ -72,7 +74,7 @@ AF_EXPORT int af_gemm_plain(void* out, int out_dtype, int ldo, const void* x, in
   AF_REQUIRE(grid.y <= 65535, "af_gemm_plain: M %d too large", M);
   AF_DISPATCH_DTYPE(dtype, T,
                     AF_DISPATCH_DTYPE(out_dtype, TO,
-                                      gemm_plain_kernel<T, TO><<<grid, 256, 0, stream>>>(
+                                      af_launch(gemm_plain_kernel<T, TO>, dim3(grid), dim3(256), 0, stream, 
                                           (TO*)out, ldo, (const T*)x, ldx, (const T*)w, ldw, M, N, K,
                                           cap)));
   AF_CHECK_LAUNCH("af_gemm_plain");

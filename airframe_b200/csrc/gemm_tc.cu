@@ -156,6 +156,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   __shared__ int give_up_s;
   volatile int* give_up = &give_up_s;
 
+  pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int n0 = blockIdx.x * TC_BM, m0 = blockIdx.y * BN;
   const int total_kb = (a.K + TC_BK - 1) / TC_BK;
@@ -183,7 +184,21 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   if (warp == 0) {
     if (lane == 0) {
-      for (int kb = 0; kb < kb_count; ++kb) {
+      // The weights do not depend on earlier kernels: the first stages' weight
+      // tiles are fetched before the wait for them, the activations after it.
+      const int early = min(STAGES, kb_count);
+      for (int kb = 0; kb < early; ++kb) {
+        unsigned char* st = tiles + (size_t)kb * STAGE_BYTES;
+        mbar_expect_tx(&full[kb], STAGE_BYTES);
+        const int k = (kb0 + kb) * TC_BK;
+        tma_load_2d(st, &map_w, k, n0, &full[kb]);
+        if (DUAL) tma_load_2d(st + A_BYTES, &map_w, k, a.up_offset + n0, &full[kb]);
+      }
+      pdl_wait();
+      for (int kb = 0; kb < early; ++kb)
+        tma_load_2d(tiles + (size_t)kb * STAGE_BYTES + (DUAL ? 2 : 1) * A_BYTES, &map_x, (kb0 + kb) * TC_BK, m0,
+                    &full[kb]);
+      for (int kb = early; kb < kb_count; ++kb) {
         const int s = kb % STAGES;
         const uint32_t ph = (kb / STAGES) & 1;
         if (!mbar_wait(&empty[s], ph ^ 1, give_up)) break;
@@ -229,6 +244,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // epilogue: warp w reads TMEM lanes [32 * (w % 4), + 32)
     const int quarter = warp & 3;
     const int f = n0 + quarter * 32 + lane;
+    pdl_wait();
     const bool done = mbar_wait(&acc_full, 0, give_up);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     if (done) {
@@ -306,7 +322,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, int sp
     configured = true;
   }
   dim3 grid((a.N + TC_BM - 1) / TC_BM, (a.M + BN - 1) / BN, splits);
-  gemm_tc_kernel<BN, DUAL, TO><<<grid, TC_THREADS, smem, stream>>>(mw, mx, a);
+  af_launch(gemm_tc_kernel<BN, DUAL, TO>, dim3(grid), dim3(TC_THREADS), smem, stream, mw, mx, a);
   AF_CHECK_LAUNCH("af_gemm_tc");
 }
 

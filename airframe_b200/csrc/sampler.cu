@@ -81,6 +81,8 @@ __global__ void __launch_bounds__(SM_THREADS)
 sample_kernel(float* __restrict__ logits, int ld, int V, const int* __restrict__ recent,
               const int* __restrict__ n_recent, int recent_stride, float temperature, float top_p,
               float penalty, const float* __restrict__ uniform, int* __restrict__ out) {
+  pdl_launch_dependents();
+  pdl_wait();
   extern __shared__ u64 bins[];  // SM_BINS
   __shared__ u64 scratch[33];
   __shared__ float s_val[32];
@@ -308,7 +310,7 @@ AF_EXPORT int af_sample(float* logits, int ld, int rows, int vocab, const int* r
     if (e != cudaSuccess) return af_fail((int)e, "af_sample: %s", cudaGetErrorString(e));
     configured = true;
   }
-  sample_kernel<<<rows, SM_THREADS, smem, stream>>>(logits, ld, vocab, recent, n_recent, recent_stride,
+  af_launch(sample_kernel, dim3(rows), dim3(SM_THREADS), smem, stream, logits, ld, vocab, recent, n_recent, recent_stride,
                                                     temperature, top_p, penalty, uniform, out);
   AF_CHECK_LAUNCH("af_sample");
 }
