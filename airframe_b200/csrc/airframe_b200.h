@@ -17,9 +17,9 @@ long long af_attn_decode_scratch(int batch, int nq, int hd, int n_splits);
 // Decode attention over the paged bfloat16 cache (see attention_decode.cu).
 // `scratch` is the caller's: af_attn_decode_scratch(...) floats of device memory.
 int af_attn_decode(void* out, long long out_stride, const void* q, long long q_stride, const void* kcache,
-                   const void* vcache, const int* page_table, int max_pages, const int* slots, const int* lens,
-                   int batch, int nq, int nkv, int hd, float scale, float cap, int window, int ring_rows,
-                   int n_splits, float* scratch, int* err, cudaStream_t stream);
+                   const void* vcache, long long n_pages, const int* page_table, int max_pages, const int* slots,
+                   const int* lens, int batch, int nq, int nkv, int hd, float scale, float cap, int window,
+                   int ring_rows, int n_splits, float* scratch, int* err, cudaStream_t stream);
 
 // ---------------------------------------------------------------------------
 // af_attn_decode_static: the same attention for callers that cannot allocate.
@@ -57,9 +57,9 @@ int af_attn_decode(void* out, long long out_stride, const void* q, long long q_s
 long long af_attn_decode_static_capacity(void);
 
 int af_attn_decode_static(void* out, long long out_stride, const void* q, long long q_stride, const void* kcache,
-                          const void* vcache, const int* page_table, int max_pages, const int* slots,
-                          const int* lens, int batch, int nq, int nkv, int hd, float scale, float cap, int window,
-                          int ring_rows, int n_splits, int* err, cudaStream_t stream);
+                          const void* vcache, long long n_pages, const int* page_table, int max_pages,
+                          const int* slots, const int* lens, int batch, int nq, int nkv, int hd, float scale,
+                          float cap, int window, int ring_rows, int n_splits, int* err, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -2,14 +2,13 @@
 // a step of few sequences still fills the GPU (it is bound by the bytes of K
 // and V it reads; every byte is read once).
 //
-// Pass 1, grid (sequence, kv head x head tile, split): a block of 256 threads
-// walks its share of the sequence's cache pages.  A page of one kv head is
-// contiguous, so one thread brings K and V pages in with bulk copies
-// (cp.async.bulk, mbarrier-tracked) through a ring of shared-memory stages.
-// Eight lanes own one key: each holds head_dim / 8 elements of the K row, dots
-// them with GT query heads of the group, reduces over the eight lanes, and
-// keeps an online softmax (32-bit max, sum, output) per head.  The 32 key
-// groups of a block are merged through shared memory and leave (max, sum,
+// Pass 1, grid (sequence, kv head, split): a block of 4 warps walks its share
+// of the sequence's cache pages.  One thread brings the K and V tiles of a page
+// in by TMA (128-byte swizzled boxes, mbarrier-tracked) through a ring of
+// shared-memory stages.  The query heads of the kv group are the rows of an
+// m16n8k16 tile (mma.sync, 32-bit accumulators): Q K^T, online softmax in
+// registers (32-bit max, sum, output), P V.  Each warp takes 16 of a page's 64
+// keys; the four warps are merged through shared memory and leave (max, sum,
 // output) in scratch memory.  Waits on the copies are bounded in time.
 // Pass 2, grid (sequence, head): merges the splits and writes bfloat16.
 //
@@ -18,12 +17,11 @@
 #include <mutex>
 
 #include "airframe_b200.h"
-#include "common.cuh"
+#include "tma.cuh"
 
 namespace {
 
-constexpr int DA_THREADS = 256;
-constexpr int DA_KEY_GROUPS = DA_THREADS / 8;
+constexpr int DA_THREADS = 128;
 
 __device__ __forceinline__ float fast_tanh(float x) {
   float y;
@@ -34,30 +32,6 @@ __device__ __forceinline__ float fast_exp2(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
-}
-
-// E bfloat16 values (E even) from p into f[]: 16-byte loads when E % 8 == 0, else 4-byte loads.
-template <int E>
-__device__ __forceinline__ void load_bf16(const __nv_bfloat16* p, float* f) {
-  if constexpr (E % 8 == 0) {
-#pragma unroll
-    for (int i = 0; i < E / 8; ++i) {
-      const uint4 raw = *reinterpret_cast<const uint4*>(p + 8 * i);
-      const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        f[8 * i + 2 * j] = __uint_as_float(w[j] << 16);
-        f[8 * i + 2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
-      }
-    }
-  } else {
-#pragma unroll
-    for (int i = 0; i < E / 2; ++i) {
-      const uint32_t w = *reinterpret_cast<const uint32_t*>(p + 2 * i);
-      f[2 * i] = __uint_as_float(w << 16);
-      f[2 * i + 1] = __uint_as_float(w & 0xffff0000u);
-    }
-  }
 }
 
 struct DecodeArgs {
@@ -78,82 +52,72 @@ struct DecodeArgs {
   int* err;        // set to 1 when a bounded wait ran out
 };
 
-__device__ __forceinline__ uint32_t da_smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
-__device__ __forceinline__ unsigned long long da_now_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
+__device__ __forceinline__ void da_ldm4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
 }
-__device__ __forceinline__ bool da_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
+__device__ __forceinline__ void da_ldm4t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0, %1, %2, %3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3)
+               : "r"(addr));
+}
+__device__ __forceinline__ void da_mma(float* c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0,
+                                       uint32_t b1) {
   asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(da_smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
+      "mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, "
+      "{%0, %1, %2, %3};"
+      : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
 }
-// Bounded wait: false when two seconds pass or another thread gave up.
-__device__ __forceinline__ bool da_wait(uint64_t* bar, uint32_t parity, volatile int* give_up) {
-  if (da_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = da_now_ns();
-  for (;;) {
-    if (da_try_wait(bar, parity)) return true;
-    if (*give_up) return false;
-    if (da_now_ns() - t0 > 2000000000ull) {
-      *give_up = 1;
-      return false;
-    }
-  }
-}
-// One page of one kv head is contiguous in the cache: a single bulk copy brings it in.
-__device__ __forceinline__ void da_bulk_load(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
-  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
-               ::"r"(da_smem_u32(dst)), "l"(src), "r"(bytes), "r"(da_smem_u32(bar))
-               : "memory");
+__device__ __forceinline__ uint32_t da_pack(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
 }
 
 template <int HD>
 __host__ __device__ constexpr int da_stages() { return HD >= 256 ? 3 : 4; }
 
-// 8 bfloat16 (one 16-byte piece) -> floats
-__device__ __forceinline__ void da_unpack8(const uint4& raw, float* f) {
-  const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-#pragma unroll
-  for (int j = 0; j < 4; ++j) {
-    f[2 * j] = __uint_as_float(w[j] << 16);
-    f[2 * j + 1] = __uint_as_float(w[j] & 0xffff0000u);
-  }
+// Address of the 16-byte piece `c` (of HD / 8) of key row `r` in a page tile:
+// HD / 64 sub-tiles of [64 rows][128 bytes], each swizzled as TMA writes it.
+__device__ __forceinline__ uint32_t da_piece(uint32_t tile, int r, int c) {
+  return tile + (uint32_t)((c >> 3) * 8192 + r * 128 + (((c & 7) ^ (r & 7)) << 4));
 }
 
-template <int HD, int GT>
+// The heads of one kv group are the (up to 16) rows of an m16n8k16 tile; the
+// four warps of a block share each page's 64 keys, 16 keys a warp.
+template <int HD>
 __global__ void __launch_bounds__(DA_THREADS, 1)
-attn_decode_split_kernel(DecodeArgs a) {
-  // A row of HD elements is HD / 8 pieces of 16 bytes; lane `sub` of a key's 8
-  // lanes owns the pieces sub, sub + 8, ...: the 8 lanes read 128 contiguous bytes.
-  constexpr int U = HD / 64;               // pieces per lane
-  constexpr int E = U * 8;                 // elements per lane
+attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
+                         DecodeArgs a) {
+  constexpr int KSTEPS = HD / 16;
+  constexpr int ONT = HD / 8;
   constexpr int STAGES = da_stages<HD>();
-  constexpr uint32_t PAGE_BYTES = AF_PAGE * HD * 2;
+  constexpr uint32_t TILE_BYTES = AF_PAGE * HD * 2;
   constexpr float LOG2E = 1.4426950408889634f;
-  extern __shared__ __align__(128) unsigned char da_smem[];  // STAGES x (K page, V page); later the merge buffer
-  __shared__ __align__(16) float q_s[GT * HD];               // [h][u][half][sub][4]
-  __shared__ float m_s[DA_KEY_GROUPS * GT], l_s[DA_KEY_GROUPS * GT];
+  extern __shared__ unsigned char da_smem_raw[];
+  unsigned char* da_smem = (unsigned char*)(((uintptr_t)da_smem_raw + 1023) & ~(uintptr_t)1023);
+  __shared__ float m_s[4 * 16], l_s[4 * 16];
   __shared__ uint64_t full[STAGES];
   __shared__ int give_up_s;
   volatile int* give_up = &give_up_s;
 
   pdl_launch_dependents();
-  pdl_wait();
   const int b = blockIdx.x;
   const int group = a.nq / a.nkv;
-  const int tiles = group / GT;
+  const int tiles = (group + 15) / 16;
   const int kvh = blockIdx.y / tiles;
-  const int head0 = kvh * group + (blockIdx.y % tiles) * GT;
+  const int row_head0 = kvh * group + (blockIdx.y % tiles) * 16;        // head of tile row 0
+  const int n_rows = min(16, kvh * group + group - row_head0);           // heads in this tile
   const int z = blockIdx.z;
-  const int tid = threadIdx.x, kg = tid >> 3, sub = tid & 7;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int g = lane >> 2, t = lane & 3;
+  if (tid == 0) {
+    for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
+    give_up_s = 0;
+    mbar_fence_init();
+  }
+  pdl_wait();
   const int slot = a.slots[b];
   const int len = slot >= 0 ? a.lens[b] : 0;
   const int pos = len - 1;
@@ -170,142 +134,156 @@ attn_decode_split_kernel(DecodeArgs a) {
   const int n_pages = max(pp_end - pp_begin, 0);
   const int ring_pages = a.ring_rows / AF_PAGE;
   const int* pt = a.page_table + (size_t)max(slot, 0) * a.max_pages;
-
-  if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s)
-      asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(da_smem_u32(&full[s])), "r"(1));
-    give_up_s = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-  }
-  for (int i = tid; i < GT * HD; i += DA_THREADS) {
-    const int h = i / HD, d = i - h * HD;
-    const int c = d >> 3, w = d & 7;
-    const int idx = (((h * U + (c >> 3)) * 2 + (w >> 2)) * 8 + (c & 7)) * 4 + (w & 3);
-    q_s[idx] = len > 0 ? __bfloat162float(a.q[(size_t)b * a.q_stride + (size_t)(head0 + h) * HD + d]) * a.scale : 0.f;
-  }
   __syncthreads();
 
   auto issue = [&](int i) {  // page i of this block's share into stage i % STAGES
     const int pp = pp_begin + i;
     const int page = pt[ring_pages > 0 ? pp % ring_pages : pp];
-    const size_t off = ((size_t)page * a.nkv + kvh) * AF_PAGE * HD;
-    unsigned char* st = da_smem + (size_t)(i % STAGES) * 2 * PAGE_BYTES;
-    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(da_smem_u32(&full[i % STAGES])),
-                 "r"(2 * PAGE_BYTES)
-                 : "memory");
-    da_bulk_load(st, a.kcache + off, PAGE_BYTES, &full[i % STAGES]);
-    da_bulk_load(st + PAGE_BYTES, a.vcache + off, PAGE_BYTES, &full[i % STAGES]);
+    const int row = (page * a.nkv + kvh) * AF_PAGE;
+    unsigned char* st = da_smem + (size_t)(i % STAGES) * 2 * TILE_BYTES;
+    uint64_t* bar = &full[i % STAGES];
+    mbar_expect_tx(bar, 2 * TILE_BYTES);
+#pragma unroll
+    for (int c = 0; c < HD / 64; ++c) {
+      tma_load_2d(st + c * 8192, &map_k, c * 64, row, bar);
+      tma_load_2d(st + TILE_BYTES + c * 8192, &map_v, c * 64, row, bar);
+    }
   };
   if (tid == 0)
     for (int i = 0; i < STAGES && i < n_pages; ++i) issue(i);
 
-  float m[GT], l[GT], o[GT][E];
+  // the query heads as A fragments: rows g and g + 8 of the tile
+  uint32_t qf[KSTEPS][4];
+  {
+    const __nv_bfloat16* q0 = a.q + (size_t)b * a.q_stride + (size_t)(row_head0 + g) * HD;
+    const __nv_bfloat16* q1 = q0 + (size_t)8 * HD;
+    const bool on0 = len > 0 && g < n_rows, on1 = len > 0 && g + 8 < n_rows;
 #pragma unroll
-  for (int h = 0; h < GT; ++h) {
-    m[h] = -INFINITY;
-    l[h] = 0.f;
-#pragma unroll
-    for (int e = 0; e < E; ++e) o[h][e] = 0.f;
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      const int d = ks * 16 + 2 * t;
+      qf[ks][0] = on0 ? *reinterpret_cast<const uint32_t*>(q0 + d) : 0u;
+      qf[ks][1] = on1 ? *reinterpret_cast<const uint32_t*>(q1 + d) : 0u;
+      qf[ks][2] = on0 ? *reinterpret_cast<const uint32_t*>(q0 + d + 8) : 0u;
+      qf[ks][3] = on1 ? *reinterpret_cast<const uint32_t*>(q1 + d + 8) : 0u;
+    }
   }
-  const float inv_cap = a.cap > 0.f ? 1.f / a.cap : 0.f;
+  float o[ONT][4];
+#pragma unroll
+  for (int n = 0; n < ONT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+  float mx[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f};
+  const float cs = a.cap > 0.f ? a.scale / a.cap : a.scale * LOG2E;
+  const float cap2 = a.cap * LOG2E;
 
-  int landed = 0;  // pages whose copies are known to be complete (for the exit path)
   for (int i = 0; i < n_pages; ++i) {
     const int s = i % STAGES;
-    if (!da_wait(&full[s], (i / STAGES) & 1, give_up)) break;
-    landed = i + 1;
-    const unsigned char* kst = da_smem + (size_t)s * 2 * PAGE_BYTES;
-    const unsigned char* vst = kst + PAGE_BYTES;
-    const int pp = pp_begin + i;
-#pragma unroll 1
-    for (int jj = kg; jj < AF_PAGE; jj += DA_KEY_GROUPS) {
-      const int j = pp * AF_PAGE + jj;
-      const bool valid = j >= lo && j <= pos;  // uniform over the 8 lanes of a key
-      float kf[E];
+    if (!mbar_wait(&full[s], (i / STAGES) & 1, give_up)) break;
+    const uint32_t k_t = smem_u32(da_smem + (size_t)s * 2 * TILE_BYTES);
+    const uint32_t v_t = k_t + TILE_BYTES;
+    // ---- S = Q K^T for this warp's 16 keys
+    float sc[2][4];
 #pragma unroll
-      for (int u = 0; u < U; ++u)
-        da_unpack8(*reinterpret_cast<const uint4*>(kst + ((size_t)jj * HD + (u * 8 + sub) * 8) * 2), kf + 8 * u);
-      float sc[GT];
+    for (int n = 0; n < 2; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
 #pragma unroll
-      for (int h = 0; h < GT; ++h) {
-        float dot = 0.f;
+    for (int ks = 0; ks < KSTEPS; ++ks) {
+      uint32_t b0, b1, b2, b3;
+      da_ldm4(da_piece(k_t, warp * 16 + (lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
+      da_mma(sc[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
+      da_mma(sc[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+    }
+    // ---- scale, softcap, mask, online softmax (base 2)
+    const int j0 = (pp_begin + i) * AF_PAGE + warp * 16;
+    float new_max[2] = {mx[0], mx[1]};
 #pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const float4 q0 = *reinterpret_cast<const float4*>(q_s + (((h * U + u) * 2 + 0) * 8 + sub) * 4);
-          const float4 q1 = *reinterpret_cast<const float4*>(q_s + (((h * U + u) * 2 + 1) * 8 + sub) * 4);
-          dot = fmaf(q0.x, kf[8 * u + 0], dot);
-          dot = fmaf(q0.y, kf[8 * u + 1], dot);
-          dot = fmaf(q0.z, kf[8 * u + 2], dot);
-          dot = fmaf(q0.w, kf[8 * u + 3], dot);
-          dot = fmaf(q1.x, kf[8 * u + 4], dot);
-          dot = fmaf(q1.y, kf[8 * u + 5], dot);
-          dot = fmaf(q1.z, kf[8 * u + 6], dot);
-          dot = fmaf(q1.w, kf[8 * u + 7], dot);
-        }
-        dot += __shfl_xor_sync(0xffffffffu, dot, 4);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 2);
-        dot += __shfl_xor_sync(0xffffffffu, dot, 1);
-        const float t = a.cap > 0.f ? a.cap * fast_tanh(dot * inv_cap) : dot;
-        sc[h] = valid ? t * LOG2E : -INFINITY;  // softmax in base 2
+    for (int n = 0; n < 2; ++n) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v = sc[n][e] * cs;
+        if (a.cap > 0.f) v = cap2 * fast_tanh(v);
+        const int j = j0 + n * 8 + 2 * t + (e & 1);
+        v = (j >= lo && j <= pos) ? v : -INFINITY;
+        sc[n][e] = v;
+        new_max[e >> 1] = fmaxf(new_max[e >> 1], v);
       }
-      float vf[E];
+    }
+    float corr[2], ref[2];
 #pragma unroll
-      for (int u = 0; u < U; ++u)
-        da_unpack8(*reinterpret_cast<const uint4*>(vst + ((size_t)jj * HD + (u * 8 + sub) * 8) * 2), vf + 8 * u);
+    for (int r = 0; r < 2; ++r) {
+      new_max[r] = fmaxf(new_max[r], __shfl_xor_sync(0xffffffffu, new_max[r], 1));
+      new_max[r] = fmaxf(new_max[r], __shfl_xor_sync(0xffffffffu, new_max[r], 2));
+      ref[r] = new_max[r] == -INFINITY ? 0.f : new_max[r];
+      corr[r] = fast_exp2(mx[r] - ref[r]);
+      mx[r] = new_max[r];
+      sum[r] *= corr[r];
+    }
 #pragma unroll
-      for (int h = 0; h < GT; ++h) {
-        const float m_new = fmaxf(m[h], sc[h]);
-        const float ref = m_new == -INFINITY ? 0.f : m_new;
-        const float corr = fast_exp2(m[h] - ref);
-        const float p = fast_exp2(sc[h] - ref);
-        l[h] = l[h] * corr + p;
+    for (int n = 0; n < 2; ++n) {
 #pragma unroll
-        for (int e = 0; e < E; ++e) o[h][e] = fmaf(p, vf[e], o[h][e] * corr);
-        m[h] = m_new;
+      for (int e = 0; e < 4; ++e) {
+        const float p = fast_exp2(sc[n][e] - ref[e >> 1]);
+        sc[n][e] = p;
+        sum[e >> 1] += p;
+      }
+    }
+    if (corr[0] != 1.f || corr[1] != 1.f) {
+#pragma unroll
+      for (int n = 0; n < ONT; ++n) {
+        o[n][0] *= corr[0];
+        o[n][1] *= corr[0];
+        o[n][2] *= corr[1];
+        o[n][3] *= corr[1];
+      }
+    }
+    // ---- O += P V over this warp's 16 keys
+    {
+      const uint32_t a0 = da_pack(sc[0][0], sc[0][1]), a1 = da_pack(sc[0][2], sc[0][3]);
+      const uint32_t a2 = da_pack(sc[1][0], sc[1][1]), a3 = da_pack(sc[1][2], sc[1][3]);
+#pragma unroll
+      for (int np = 0; np < ONT / 2; ++np) {
+        uint32_t b0, b1, b2, b3;
+        da_ldm4t(da_piece(v_t, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, np * 2 + (lane >> 4)), b0, b1, b2, b3);
+        da_mma(o[2 * np], a0, a1, a2, a3, b0, b1);
+        da_mma(o[2 * np + 1], a0, a1, a2, a3, b2, b3);
       }
     }
     __syncthreads();  // everyone is done with stage s
     if (tid == 0 && i + STAGES < n_pages && !*give_up) issue(i + STAGES);
   }
-  if (*give_up) {
-    // copies that were issued must land before the stage memory is reused below
-    if (tid == 0) {
-      const unsigned long long t0 = da_now_ns();
-      while (da_now_ns() - t0 < 1000000ull) {
-      }
-    }
-    (void)landed;
-  }
+  if (*give_up && tid == 0) grace_period();
   __syncthreads();
 
-  // merge the key groups of the block; the stage memory serves as the buffer
-  float* o_s = reinterpret_cast<float*>(da_smem);  // [key group][GT][HD]
+  // ---- merge the four warps (each saw a quarter of the keys); the stage memory is the buffer
+  float* o_s = reinterpret_cast<float*>(da_smem);  // [warp][16 rows][HD]
 #pragma unroll
-  for (int h = 0; h < GT; ++h) {
-    if (sub == 0) {
-      m_s[kg * GT + h] = m[h];
-      l_s[kg * GT + h] = l[h];
+  for (int r = 0; r < 2; ++r) {
+    sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+    sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+    const int row = g + 8 * r;
+    if (t == 0) {
+      m_s[warp * 16 + row] = mx[r];
+      l_s[warp * 16 + row] = sum[r];
     }
 #pragma unroll
-    for (int u = 0; u < U; ++u)
-#pragma unroll
-      for (int w = 0; w < 8; ++w) o_s[((size_t)kg * GT + h) * HD + (u * 8 + sub) * 8 + w] = o[h][8 * u + w];
+    for (int n = 0; n < ONT; ++n) {
+      float* dst = o_s + ((size_t)(warp * 16 + row)) * HD + n * 8 + 2 * t;
+      dst[0] = o[n][2 * r];
+      dst[1] = o[n][2 * r + 1];
+    }
   }
   __syncthreads();
-  for (int i = tid; i < GT * HD; i += DA_THREADS) {
-    const int h = i / HD, d = i - h * HD;
+  for (int i = tid; i < n_rows * HD; i += DA_THREADS) {
+    const int row = i / HD, d = i - row * HD;
     float M = -INFINITY;
 #pragma unroll
-    for (int g = 0; g < DA_KEY_GROUPS; ++g) M = fmaxf(M, m_s[g * GT + h]);
+    for (int w = 0; w < 4; ++w) M = fmaxf(M, m_s[w * 16 + row]);
     const float ref = M == -INFINITY ? 0.f : M;
     float L = 0.f, O = 0.f;
-#pragma unroll 8
-    for (int g = 0; g < DA_KEY_GROUPS; ++g) {
-      const float w = fast_exp2(m_s[g * GT + h] - ref);
-      L += l_s[g * GT + h] * w;
-      O += o_s[((size_t)g * GT + h) * HD + d] * w;
+#pragma unroll
+    for (int w = 0; w < 4; ++w) {
+      const float f = fast_exp2(m_s[w * 16 + row] - ref);
+      L += l_s[w * 16 + row] * f;
+      O += o_s[((size_t)(w * 16 + row)) * HD + d] * f;
     }
-    const size_t pidx = ((size_t)b * a.nq + head0 + h) * a.n_splits + z;
+    const size_t pidx = ((size_t)b * a.nq + row_head0 + row) * a.n_splits + z;
     a.part_o[pidx * HD + d] = O;
     if (d == 0) {
       a.part_ml[pidx * 2] = M;
@@ -336,36 +314,32 @@ __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long l
   }
 }
 
-template <int HD, int GT>
-int launch_decode(const DecodeArgs& a, __nv_bfloat16* out, long long out_stride, int batch, cudaStream_t stream) {
+template <int HD>
+int launch_decode(const DecodeArgs& a, __nv_bfloat16* out, long long out_stride, int batch, long long n_pages,
+                  cudaStream_t stream) {
   const size_t stage_bytes = (size_t)da_stages<HD>() * 2 * AF_PAGE * HD * 2;
-  const size_t merge_bytes = (size_t)DA_KEY_GROUPS * GT * HD * sizeof(float);
-  const size_t smem = stage_bytes > merge_bytes ? stage_bytes : merge_bytes;
+  const size_t merge_bytes = (size_t)4 * 16 * HD * sizeof(float);
+  const size_t smem = (stage_bytes > merge_bytes ? stage_bytes : merge_bytes) + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(attn_decode_split_kernel<HD, GT>,
-                                         cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t e = cudaFuncSetAttribute(attn_decode_split_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                         (int)smem);
     if (e != cudaSuccess) return af_fail((int)e, "af_attn_decode: %s", cudaGetErrorString(e));
     configured = true;
   }
+  // the cache of one layer as a matrix [pages * kv heads * 64 rows, HD]; boxes of 64 rows x 64 columns
+  CUtensorMap mk, mv;
+  int rc = af_make_map_bf16(&mk, a.kcache, n_pages * a.nkv * AF_PAGE, HD, HD, AF_PAGE);
+  if (rc) return rc;
+  rc = af_make_map_bf16(&mv, a.vcache, n_pages * a.nkv * AF_PAGE, HD, HD, AF_PAGE);
+  if (rc) return rc;
   const int group = a.nq / a.nkv;
-  dim3 grid(batch, a.nkv * (group / GT), a.n_splits);
-  af_launch(attn_decode_split_kernel<HD, GT>, dim3(grid), dim3(DA_THREADS), smem, stream, a);
+  dim3 grid(batch, a.nkv * ((group + 15) / 16), a.n_splits);
+  af_launch(attn_decode_split_kernel<HD>, grid, dim3(DA_THREADS), smem, stream, mk, mv, a);
   AF_COUNT_LAUNCH("af_attn_decode (split)");
-  af_launch(attn_decode_merge_kernel<HD>, dim3(dim3(batch, a.nq)), dim3(HD < 128 ? HD : 128), 0, stream, 
-      out, out_stride, a.part_o, a.part_ml, a.nq, a.n_splits);
+  af_launch(attn_decode_merge_kernel<HD>, dim3(batch, a.nq), dim3(HD < 128 ? HD : 128), 0, stream, out, out_stride,
+            a.part_o, a.part_ml, a.nq, a.n_splits);
   AF_CHECK_LAUNCH("af_attn_decode (merge)");
-}
-
-template <int HD>
-int launch_decode_hd(const DecodeArgs& a, __nv_bfloat16* out, long long out_stride, int batch, cudaStream_t s) {
-  // the widest head tile that divides the group and keeps the output in registers
-  constexpr int LIMIT = 512 / HD;  // 2 heads of 256, 4 of 128, 8 of 64
-  const int group = a.nq / a.nkv;
-  if (LIMIT >= 8 && group % 8 == 0) return launch_decode<HD, (LIMIT >= 8 ? 8 : 1)>(a, out, out_stride, batch, s);
-  if (LIMIT >= 4 && group % 4 == 0) return launch_decode<HD, (LIMIT >= 4 ? 4 : 1)>(a, out, out_stride, batch, s);
-  if (LIMIT >= 2 && group % 2 == 0) return launch_decode<HD, (LIMIT >= 2 ? 2 : 1)>(a, out, out_stride, batch, s);
-  return launch_decode<HD, 1>(a, out, out_stride, batch, s);
 }
 
 }  // namespace
@@ -380,12 +354,13 @@ AF_EXPORT long long af_attn_decode_scratch(int batch, int nq, int hd, int n_spli
 
 // out [batch, nq * hd] bfloat16 = attention of one new token per sequence over
 // its cache (lens[b] counts the new token, which the cache holds already).
-// scratch: af_attn_decode_scratch(...) floats.  Sequences with slot < 0 give zeros.
+// The cache of the layer holds n_pages pages [kv heads][64][hd].  scratch:
+// af_attn_decode_scratch(...) floats.  Sequences with slot < 0 give zeros.
 AF_EXPORT int af_attn_decode(void* out, long long out_stride, const void* q, long long q_stride,
-                             const void* kcache, const void* vcache, const int* page_table, int max_pages,
-                             const int* slots, const int* lens, int batch, int nq, int nkv, int hd, float scale,
-                             float cap, int window, int ring_rows, int n_splits, float* scratch, int* err,
-                             cudaStream_t stream) {
+                             const void* kcache, const void* vcache, long long n_pages, const int* page_table,
+                             int max_pages, const int* slots, const int* lens, int batch, int nq, int nkv, int hd,
+                             float scale, float cap, int window, int ring_rows, int n_splits, float* scratch,
+                             int* err, cudaStream_t stream) {
   if (batch == 0) return 0;
   AF_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "af_attn_decode: heads %d, groups %d", nq, nkv);
   AF_REQUIRE(af_attn_decode_supported(hd), "af_attn_decode: head_dim %d (takes 64, 128, 256)", hd);
@@ -413,9 +388,10 @@ AF_EXPORT int af_attn_decode(void* out, long long out_stride, const void* q, lon
   a.part_ml = scratch + (size_t)batch * nq * n_splits * hd;
   a.err = err;
   __nv_bfloat16* o = (__nv_bfloat16*)out;
-  if (hd == 64) return launch_decode_hd<64>(a, o, out_stride, batch, stream);
-  if (hd == 128) return launch_decode_hd<128>(a, o, out_stride, batch, stream);
-  return launch_decode_hd<256>(a, o, out_stride, batch, stream);
+  AF_REQUIRE(n_pages > 0 && n_pages * nkv * AF_PAGE < (1ll << 31), "af_attn_decode: %lld cache pages", n_pages);
+  if (hd == 64) return launch_decode<64>(a, o, out_stride, batch, n_pages, stream);
+  if (hd == 128) return launch_decode<128>(a, o, out_stride, batch, n_pages, stream);
+  return launch_decode<256>(a, o, out_stride, batch, n_pages, stream);
 }
 
 // ---------------------------------------------------------------- no allocation
@@ -455,10 +431,10 @@ int decode_scratch_address(float** out) {
 AF_EXPORT long long af_attn_decode_static_capacity() { return AF_ATTN_DECODE_STATIC_FLOATS; }
 
 AF_EXPORT int af_attn_decode_static(void* out, long long out_stride, const void* q, long long q_stride,
-                                    const void* kcache, const void* vcache, const int* page_table, int max_pages,
-                                    const int* slots, const int* lens, int batch, int nq, int nkv, int hd,
-                                    float scale, float cap, int window, int ring_rows, int n_splits, int* err,
-                                    cudaStream_t stream) {
+                                    const void* kcache, const void* vcache, long long n_pages,
+                                    const int* page_table, int max_pages, const int* slots, const int* lens,
+                                    int batch, int nq, int nkv, int hd, float scale, float cap, int window,
+                                    int ring_rows, int n_splits, int* err, cudaStream_t stream) {
   if (batch == 0) return 0;
   AF_REQUIRE(batch > 0 && nq > 0 && hd > 0 && n_splits >= 1, "af_attn_decode_static: bad sizes");
   const long long need = af_attn_decode_scratch(batch, nq, hd, n_splits);
@@ -469,6 +445,6 @@ AF_EXPORT int af_attn_decode_static(void* out, long long out_stride, const void*
   float* scratch = nullptr;
   const int rc = decode_scratch_address(&scratch);
   if (rc) return rc;
-  return af_attn_decode(out, out_stride, q, q_stride, kcache, vcache, page_table, max_pages, slots, lens, batch, nq,
-                        nkv, hd, scale, cap, window, ring_rows, n_splits, scratch, err, stream);
+  return af_attn_decode(out, out_stride, q, q_stride, kcache, vcache, n_pages, page_table, max_pages, slots, lens,
+                        batch, nq, nkv, hd, scale, cap, window, ring_rows, n_splits, scratch, err, stream);
 }

@@ -20,16 +20,13 @@
 // Every wait on an mbarrier is bounded in time.  A wait that runs out sets an
 // error word that the host reads after the launch; the CTA then lets its
 // copies in flight land, releases its TMEM and returns.
-#include <cuda.h>
-
-#include "common.cuh"
+#include "tma.cuh"
 
 namespace {
 
 constexpr int TC_BM = 128;  // features per CTA = UMMA M
 constexpr int TC_BK = 64;   // K per stage: 128 bytes of bfloat16 = one swizzle row
 constexpr int TC_THREADS = 192;
-constexpr unsigned long long TC_WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 constexpr int TC_SMEM_BUDGET = 200 * 1024;
 
 __host__ __device__ constexpr int tc_stage_bytes(int bn, bool dual) {
@@ -44,52 +41,6 @@ __host__ __device__ constexpr int tc_tmem_cols(int bn, bool dual) {
   return c < 32 ? 32 : c;  // bn is a power of two
 }
 
-__device__ __forceinline__ uint32_t smem_u32(const void* p) {
-  return (uint32_t)__cvta_generic_to_shared(p);
-}
-__device__ __forceinline__ unsigned long long now_ns() {
-  unsigned long long t;
-  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-  return t;
-}
-__device__ __forceinline__ void mbar_init(uint64_t* bar, uint32_t count) {
-  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
-}
-__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
-  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
-               : "memory");
-}
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
-      "selp.u32 %0, 1, 0, p;\n\t}"
-      : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity)
-      : "memory");
-  return ok != 0;
-}
-// Waits until the barrier's phase `parity` is complete.  False when the time
-// limit ran out or another role gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* give_up) {
-  if (mbar_try_wait(bar, parity)) return true;
-  const unsigned long long t0 = now_ns();
-  for (;;) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if (*give_up) return false;
-    if (now_ns() - t0 > TC_WAIT_LIMIT_NS) {
-      *give_up = 1;
-      return false;
-    }
-  }
-}
-__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
-  asm volatile(
-      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
-      : "memory");
-}
 // K-major operand tile in 128-byte swizzled rows: 8-row groups are 1024 bytes apart.
 __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr) {
   return (uint64_t)((smem_addr >> 4) & 0x3FFF) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
@@ -170,7 +121,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     }
     mbar_init(&acc_full, 1);
     give_up_s = 0;
-    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    mbar_fence_init();
   }
   if (warp == 1) {
     asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_s)),
@@ -209,12 +160,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         if (DUAL) tma_load_2d(st + A_BYTES, &map_w, k, a.up_offset + n0, &full[s]);
         tma_load_2d(st + (DUAL ? 2 : 1) * A_BYTES, &map_x, k, m0, &full[s]);
       }
-      if (*give_up) {
-        // let copies that were issued land before the block's shared memory goes away
-        const unsigned long long t0 = now_ns();
-        while (now_ns() - t0 < 1000000ull) {
-        }
-      }
+      if (*give_up) grace_period();
     }
   } else if (warp == 1) {
     if (lane == 0) {
@@ -281,37 +227,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
 // ---------------------------------------------------------------- host side
 
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-EncodeTiledFn encode_tiled() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* p = nullptr;
-    cudaDriverEntryPointQueryResult q;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
-        q == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)p;
-  }
-  return fn;
-}
-
-// A [rows, K] bfloat16 matrix with dense rows of stride `ld` elements; boxes of 64 x box_rows.
-int make_map(CUtensorMap* map, const void* base, long long rows, long long K, long long ld, int box_rows) {
-  EncodeTiledFn enc = encode_tiled();
-  if (enc == nullptr) return af_fail(-1, "gemm_tc: the driver has no cuTensorMapEncodeTiled");
-  cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld * 2};
-  cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return af_fail(-1, "gemm_tc: cuTensorMapEncodeTiled failed (%d)", (int)r);
-  return 0;
-}
-
 template <int BN, bool DUAL, typename TO>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, int splits, cudaStream_t stream) {
   constexpr int smem = tc_stages(BN, DUAL) * tc_stage_bytes(BN, DUAL) + 1024;
@@ -368,9 +283,9 @@ AF_EXPORT int af_gemm_tc(void* out, int out_dtype, long long ldo, long long part
   AF_REQUIRE((splits - 1) * kb_per_split < total_kb, "af_gemm_tc: an empty K split");
   const int bn = af_gemm_tc_token_tile(M);
   CUtensorMap mw, mx;
-  int rc = make_map(&mw, w, n_w_rows, K, ldw, TC_BM);
+  int rc = af_make_map_bf16(&mw, w, n_w_rows, K, ldw, TC_BM);
   if (rc) return rc;
-  rc = make_map(&mx, x, M, K, ldx, bn);
+  rc = af_make_map_bf16(&mx, x, M, K, ldx, bn);
   if (rc) return rc;
   TcArgs a{out, ldo, part_stride, M, N, K, kb_per_split, up_offset, act, cap, err};
   if (dual) {

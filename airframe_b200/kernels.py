@@ -350,7 +350,8 @@ def attn_decode_split(out, q, kcache, vcache, page_table, slots, lens, nq, nkv, 
         raise KernelError("attn_decode_split: bfloat16 only")
     _check(lib.af_attn_decode(
         _ptr(out), c_longlong(_rows(out, "out")), _ptr(q), c_longlong(_rows(q, "q")), _ptr(kcache), _ptr(vcache),
-        _ptr(page_table, "page_table", torch.int32), c_int(page_table.shape[1]), _ptr(slots, "slots", torch.int32),
+        c_longlong(kcache.shape[0]), _ptr(page_table, "page_table", torch.int32), c_int(page_table.shape[1]),
+        _ptr(slots, "slots", torch.int32),
         _ptr(lens, "lens", torch.int32), c_int(B), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_float(cap),
         c_int(window), c_int(ring_rows), c_int(n_splits), _ptr(scratch, "scratch", torch.float32),
         _ptr(error_word(q.device), "err", torch.int32), _stream()))

@@ -51,7 +51,7 @@ def _call(lib, fn, p, batch, nq, nkv, hd, splits, scratch=None):
     ring = ((p["window"] + PAGE - 1) // PAGE) * PAGE if p["window"] else 0
     args = [c_void_p(out.data_ptr()), c_longlong(out.stride(0)), c_void_p(p["q"].data_ptr()),
             c_longlong(p["q"].stride(0)), c_void_p(p["kc"].data_ptr()), c_void_p(p["vc"].data_ptr()),
-            c_void_p(p["table"].data_ptr()), c_int(p["table"].shape[1]), c_void_p(p["slots"].data_ptr()),
+            c_longlong(p["kc"].shape[0]), c_void_p(p["table"].data_ptr()), c_int(p["table"].shape[1]), c_void_p(p["slots"].data_ptr()),
             c_void_p(p["lens"].data_ptr()), c_int(batch), c_int(nq), c_int(nkv), c_int(hd),
             c_float(1.0 / math.sqrt(hd)), c_float(30.0), c_int(p["window"]), c_int(ring), c_int(splits)]
     if scratch is not None:
