@@ -12,10 +12,12 @@
 //   warp 1      TMEM allocation, MMA issue (one lane), TMEM release
 //   warps 2..5  epilogue: TMEM -> registers -> global
 //
-// Variants: DUAL keeps two accumulators (rows n and up_offset + n of the weight,
-// the gate and up halves of a gated feed-forward) and writes act(g) * u;
-// split-K (gridDim.z > 1) writes float partial sums [split, M, N] that the
-// consumer adds in order; `cap` > 0 applies cap * tanh(v / cap).
+// Variants: NACC = 2 keeps two accumulators (two consecutive 128-feature tiles
+// share one token tile: fewer bytes per flop for prefill); GATED expects a
+// weight whose 32-row groups hold 16 gate rows then the 16 up rows of the same
+// features, and writes act(g) * u (the halves meet by warp shuffles in the
+// epilogue); split-K (gridDim.z > 1) writes float partial sums [split, M, N]
+// that the consumer adds in order; `cap` > 0 applies cap * tanh(v / cap).
 //
 // Every wait on an mbarrier is bounded in time.  A wait that runs out sets an
 // error word that the host reads after the launch; the CTA then lets its
@@ -27,17 +29,17 @@ namespace {
 constexpr int TC_BM = 128;  // features per CTA = UMMA M
 constexpr int TC_BK = 64;   // K per stage: 128 bytes of bfloat16 = one swizzle row
 constexpr int TC_THREADS = 192;
-constexpr int TC_SMEM_BUDGET = 200 * 1024;
+constexpr int TC_SMEM_BUDGET = 192 * 1024;
 
-__host__ __device__ constexpr int tc_stage_bytes(int bn, bool dual) {
-  return (dual ? 2 : 1) * TC_BM * TC_BK * 2 + bn * TC_BK * 2;
+__host__ __device__ constexpr int tc_stage_bytes(int bn, int nacc) {
+  return nacc * TC_BM * TC_BK * 2 + bn * TC_BK * 2;
 }
-__host__ __device__ constexpr int tc_stages(int bn, bool dual) {
-  int s = TC_SMEM_BUDGET / tc_stage_bytes(bn, dual);
+__host__ __device__ constexpr int tc_stages(int bn, int nacc) {
+  int s = TC_SMEM_BUDGET / tc_stage_bytes(bn, nacc);
   return s > 8 ? 8 : s;
 }
-__host__ __device__ constexpr int tc_tmem_cols(int bn, bool dual) {
-  int c = dual ? 2 * bn : bn;
+__host__ __device__ constexpr int tc_tmem_cols(int bn, int nacc) {
+  int c = nacc * bn;
   return c < 32 ? 32 : c;  // bn is a power of two
 }
 
@@ -70,34 +72,55 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
       : "r"(taddr));
 }
 
+// The activation of the gated epilogue.  Its result is rounded to bfloat16, so
+// tanh.approx (relative error 2^-11) and ex2.approx serve.
+// c ? a : b as one select instruction (keeps both operands in registers)
+__device__ __forceinline__ float pick(int c, float a, float b) {
+  float r;
+  asm("{\n\t.reg .pred p;\n\tsetp.ne.s32 p, %3, 0;\n\tselp.f32 %0, %1, %2, p;\n\t}" : "=f"(r) : "f"(a), "f"(b), "r"(c));
+  return r;
+}
+
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
+  uint32_t* r = reinterpret_cast<uint32_t*>(v);
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+        "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+        "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+        "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr));
+}
+
 __device__ __forceinline__ float tc_act(float g, int act) {
   if (act == AF_ACT_GELU_TANH) {
     const float u = 0.7978845608028654f * (g + 0.044715f * g * g * g);
-    return 0.5f * g * (1.f + tanhf(u));
+    float t;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(t) : "f"(u));
+    return 0.5f * g * (1.f + t);
   }
-  return g / (1.f + expf(-g));
+  return g / (1.f + __expf(-g));
 }
 
 struct TcArgs {
   void* out;
   long long ldo;          // row stride of out in elements
   long long part_stride;  // elements between split-K partial results
-  int M, N, K;
+  int M, N, K;            // N: output features (GATED: half the weight's rows)
   int kb_per_split;       // K blocks handled by one z-slice
-  int up_offset;          // DUAL: weight row of feature 0's second operand
   int act;
   float cap;
   int* err;
 };
 
-template <int BN, bool DUAL, typename TO>
+template <int BN, int NACC, bool GATED, typename TO>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcArgs a) {
-  constexpr int STAGES = tc_stages(BN, DUAL);
+  constexpr int STAGES = tc_stages(BN, NACC);
   constexpr int A_BYTES = TC_BM * TC_BK * 2;
-  constexpr int B_BYTES = BN * TC_BK * 2;
-  constexpr int STAGE_BYTES = tc_stage_bytes(BN, DUAL);
-  constexpr int COLS = tc_tmem_cols(BN, DUAL);
+  constexpr int STAGE_BYTES = tc_stage_bytes(BN, NACC);
+  constexpr int COLS = tc_tmem_cols(BN, NACC);
   constexpr uint32_t IDESC = umma_idesc(BN);
 
   extern __shared__ unsigned char smem_raw[];
@@ -109,7 +132,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * TC_BM, m0 = blockIdx.y * BN;
+  const int n0 = blockIdx.x * (TC_BM * NACC), m0 = blockIdx.y * BN;  // first weight row, first token
   const int total_kb = (a.K + TC_BK - 1) / TC_BK;
   const int kb0 = blockIdx.z * a.kb_per_split;
   const int kb_count = min(a.kb_per_split, total_kb - kb0);
@@ -142,13 +165,20 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         unsigned char* st = tiles + (size_t)kb * STAGE_BYTES;
         mbar_expect_tx(&full[kb], STAGE_BYTES);
         const int k = (kb0 + kb) * TC_BK;
-        tma_load_2d(st, &map_w, k, n0, &full[kb]);
-        if (DUAL) tma_load_2d(st + A_BYTES, &map_w, k, a.up_offset + n0, &full[kb]);
+#pragma unroll
+        for (int acc = 0; acc < NACC; ++acc) tma_load_2d(st + acc * A_BYTES, &map_w, k, n0 + acc * TC_BM, &full[kb]);
+      }
+      // few tokens: the product is bound by the weight stream, so the rest of this block's
+      // weights is asked into L2 while the kernel before still runs
+      if (BN <= 64) {
+        for (int kb = early; kb < kb_count; ++kb) {
+#pragma unroll
+          for (int acc = 0; acc < NACC; ++acc) tma_prefetch_2d(&map_w, (kb0 + kb) * TC_BK, n0 + acc * TC_BM);
+        }
       }
       pdl_wait();
       for (int kb = 0; kb < early; ++kb)
-        tma_load_2d(tiles + (size_t)kb * STAGE_BYTES + (DUAL ? 2 : 1) * A_BYTES, &map_x, (kb0 + kb) * TC_BK, m0,
-                    &full[kb]);
+        tma_load_2d(tiles + (size_t)kb * STAGE_BYTES + NACC * A_BYTES, &map_x, (kb0 + kb) * TC_BK, m0, &full[kb]);
       for (int kb = early; kb < kb_count; ++kb) {
         const int s = kb % STAGES;
         const uint32_t ph = (kb / STAGES) & 1;
@@ -156,9 +186,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
         mbar_expect_tx(&full[s], STAGE_BYTES);
         const int k = (kb0 + kb) * TC_BK;
-        tma_load_2d(st, &map_w, k, n0, &full[s]);
-        if (DUAL) tma_load_2d(st + A_BYTES, &map_w, k, a.up_offset + n0, &full[s]);
-        tma_load_2d(st + (DUAL ? 2 : 1) * A_BYTES, &map_x, k, m0, &full[s]);
+#pragma unroll
+        for (int acc = 0; acc < NACC; ++acc) tma_load_2d(st + acc * A_BYTES, &map_w, k, n0 + acc * TC_BM, &full[s]);
+        tma_load_2d(st + NACC * A_BYTES, &map_x, k, m0, &full[s]);
       }
       if (*give_up) grace_period();
     }
@@ -174,13 +204,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t st = smem_u32(tiles + (size_t)s * STAGE_BYTES);
-        const uint64_t da = umma_desc(st);
-        const uint64_t db = umma_desc(st + (DUAL ? 2 : 1) * A_BYTES);
+        const uint64_t db = umma_desc(st + NACC * A_BYTES);
 #pragma unroll
         for (int k = 0; k < TC_BK / 16; ++k) {
-          const uint32_t acc = (kb > 0 || k > 0) ? 1u : 0u;
-          umma_f16(tmem_base, da + 2 * k, db + 2 * k, IDESC, acc);  // 32 bytes of K per step
-          if (DUAL) umma_f16(tmem_base + BN, umma_desc(st + A_BYTES) + 2 * k, db + 2 * k, IDESC, acc);
+          const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+#pragma unroll
+          for (int acc = 0; acc < NACC; ++acc)  // 32 bytes of K per step
+            umma_f16(tmem_base + acc * BN, umma_desc(st + acc * A_BYTES) + 2 * k, db + 2 * k, IDESC, accum);
         }
         umma_commit(&empty[s]);
       }
@@ -189,28 +219,78 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   } else {
     // epilogue: warp w reads TMEM lanes [32 * (w % 4), + 32)
     const int quarter = warp & 3;
-    const int f = n0 + quarter * 32 + lane;
     pdl_wait();
-    const bool done = mbar_wait(&acc_full, 0, give_up);
+    bool done = mbar_wait(&acc_full, 0, give_up);  // (not const: experiments may clear it)
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#ifdef AF_EXP_NOEPI
+    done = false;
+#endif
     if (done) {
       TO* out = reinterpret_cast<TO*>(a.out) + (size_t)blockIdx.z * a.part_stride;
       const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
+      // CW columns (tokens) per round: the TMEM loads of a round are issued
+      // together and waited for once
+      constexpr int CW = BN >= 64 ? 64 : BN;
+      int round = 0;
 #pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 16) {
-        float v[16], u[16];
-        tmem_ld16(lane_base + c0, v);
-        if (DUAL) tmem_ld16(lane_base + BN + c0, u);
-        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (f < a.N) {
+      for (int acc = 0; acc < NACC; ++acc) {
+        // the output feature of this lane: a weight row, or for GATED the feature whose gate row it is
+        const int tile = blockIdx.x * NACC + acc;
+        const int f = GATED ? tile * 64 + quarter * 16 + (lane & 15) : tile * TC_BM + quarter * 32 + lane;
+#pragma unroll 1
+        for (int c0 = 0; c0 < BN; c0 += CW, ++round) {
+          float v[CW];
+          if constexpr (CW >= 32) {
 #pragma unroll
-          for (int j = 0; j < 16; ++j) {
-            const int m = m0 + c0 + j;
-            if (m < a.M) {
-              float r = v[j];
-              if (DUAL) r = tc_act(r, a.act) * u[j];
-              r = softcap_f32(r, a.cap);
-              out[(size_t)m * a.ldo + f] = from_f32<TO>(r);
+            for (int c = 0; c < CW; c += 32) tmem_ld32(lane_base + acc * BN + c0 + c, v + c);
+          } else {
+            tmem_ld16(lane_base + acc * BN + c0, v);
+          }
+          asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#ifdef AF_EXP_LDONLY
+          {
+            float accx = 0.f;
+#pragma unroll
+            for (int j = 0; j < CW; ++j) accx += v[j];
+            if (accx == 12345.678f) out[0] = from_f32<TO>(accx);
+            continue;
+          }
+#endif
+          if (GATED) {
+            // Within a warp lanes 0..15 hold gate rows and lanes 16..31 the up rows of the
+            // same 16 features.  Each half keeps one half of the round's tokens and gets
+            // the partner's values for them with one shuffle per token.
+            const int low = lane < 16 ? 1 : 0;
+#pragma unroll
+            for (int j = 0; j < CW / 2; ++j) {
+              const float got = __shfl_xor_sync(0xffffffffu, pick(low, v[j + CW / 2], v[j]), 16);
+              // low lanes: g(own) * u(partner) for tokens [0, CW/2); high lanes: g(partner) * u(own) for [CW/2, CW)
+              const float g = pick(low, v[j], got), u = pick(low, got, v[j + CW / 2]);
+              v[j] = tc_act(g, a.act) * u;
+            }
+          }
+          if (a.cap > 0.f) {  // (fully unrolled: v stays in registers)
+#pragma unroll
+            for (int j = 0; j < CW; ++j) v[j] = a.cap * tanhf(v[j] / a.cap);
+          }
+          if (GATED) {
+            // lane l and lane l + 16 write the same feature, for the first and the second half of the tokens
+            const int tok0 = m0 + c0 + (lane < 16 ? 0 : CW / 2);
+            if (f < a.N) {
+              TO* o = out + (size_t)tok0 * a.ldo + f;
+#pragma unroll
+              for (int j = 0; j < CW / 2; ++j)
+                if (tok0 + j < a.M) o[(size_t)j * a.ldo] = from_f32<TO>(v[j]);
+            }
+          } else if (f < a.N) {
+            TO* o = out + (size_t)(m0 + c0) * a.ldo + f;
+            if (m0 + c0 + CW <= a.M) {
+#pragma unroll
+              for (int j = 0; j < CW; ++j) o[(size_t)j * a.ldo] = from_f32<TO>(v[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < CW; ++j)
+                if (m0 + c0 + j < a.M) o[(size_t)j * a.ldo] = from_f32<TO>(v[j]);
             }
           }
         }
@@ -227,30 +307,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
 // ---------------------------------------------------------------- host side
 
-template <int BN, bool DUAL, typename TO>
-int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, int splits, cudaStream_t stream) {
-  constexpr int smem = tc_stages(BN, DUAL) * tc_stage_bytes(BN, DUAL) + 1024;
+template <int BN, int NACC, bool GATED, typename TO>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, long long n_w_rows, int splits,
+           cudaStream_t stream) {
+  constexpr int smem = tc_stages(BN, NACC) * tc_stage_bytes(BN, NACC) + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, DUAL, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, NACC, GATED, TO>,
+                                         cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return af_fail((int)e, "gemm_tc: %s", cudaGetErrorString(e));
     configured = true;
   }
-  dim3 grid((a.N + TC_BM - 1) / TC_BM, (a.M + BN - 1) / BN, splits);
-  af_launch(gemm_tc_kernel<BN, DUAL, TO>, dim3(grid), dim3(TC_THREADS), smem, stream, mw, mx, a);
+  const long long w_tiles = (n_w_rows + TC_BM - 1) / TC_BM;
+  dim3 grid((unsigned)((w_tiles + NACC - 1) / NACC), (a.M + BN - 1) / BN, splits);
+  af_launch(gemm_tc_kernel<BN, NACC, GATED, TO>, grid, dim3(TC_THREADS), smem, stream, mw, mx, a);
   AF_CHECK_LAUNCH("af_gemm_tc");
 }
 
-template <bool DUAL, typename TO>
-int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, int splits, cudaStream_t s) {
+template <int NACC, bool GATED, typename TO>
+int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, long long rows, int splits,
+              cudaStream_t s) {
   switch (bn) {
-    case 16: return launch<16, DUAL, TO>(mw, mx, a, splits, s);
-    case 32: return launch<32, DUAL, TO>(mw, mx, a, splits, s);
-    case 64: return launch<64, DUAL, TO>(mw, mx, a, splits, s);
-    case 128: return launch<128, DUAL, TO>(mw, mx, a, splits, s);
-    case 256: return launch<256, DUAL, TO>(mw, mx, a, splits, s);
+    case 16: return launch<16, NACC, GATED, TO>(mw, mx, a, rows, splits, s);
+    case 32: return launch<32, NACC, GATED, TO>(mw, mx, a, rows, splits, s);
+    case 64: return launch<64, NACC, GATED, TO>(mw, mx, a, rows, splits, s);
+    case 128: return launch<128, NACC, GATED, TO>(mw, mx, a, rows, splits, s);
+    case 256: return launch<256, NACC, GATED, TO>(mw, mx, a, rows, splits, s);
   }
   return af_fail(-1, "gemm_tc: token tile %d", bn);
+}
+
+template <typename TO>
+int launch_variant(int nacc, int gated, int bn, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a,
+                   long long rows, int splits, cudaStream_t s) {
+  if (gated) {
+    if (nacc == 2) return launch_bn<2, true, TO>(bn, mw, mx, a, rows, 1, s);
+    return launch_bn<1, true, TO>(bn, mw, mx, a, rows, 1, s);
+  }
+  if (nacc == 2) return launch_bn<2, false, TO>(bn, mw, mx, a, rows, splits, s);
+  return launch_bn<1, false, TO>(bn, mw, mx, a, rows, splits, s);
 }
 
 }  // namespace
@@ -262,21 +357,23 @@ AF_EXPORT int af_gemm_tc_token_tile(int M) {
 
 // out = x w^T on the tensor cores.  x [M, K] and w [n_w_rows, K] bfloat16 with
 // dense rows (strides ldx, ldw elements, multiples of 8; bases 16-byte
-// aligned).  N output features.  dual != 0: w holds 2 operands per feature,
-// rows f and up_offset + f, and out = act(x w_f) * (x w_{up_offset + f}).
-// splits > 1: out is float [splits, M, N] partial sums (part_stride elements
-// apart) and out_dtype must be AF_F32.  err: device word set to 1 when a wait
-// inside the kernel ran out of time.
+// aligned).  gated == 0: N = n_w_rows output features.  gated != 0: w holds,
+// in every group of 32 rows, 16 gate rows followed by the up rows of the same
+// 16 features, N = n_w_rows / 2, and out[m, f] = act(x . gate_f) * (x . up_f).
+// n_acc: 1 or 2 weight tiles per block.  splits > 1: out is float [splits, M,
+// N] partial sums (part_stride elements apart) and out_dtype must be AF_F32.
+// err: device word set to 1 when a wait inside the kernel ran out of time.
 AF_EXPORT int af_gemm_tc(void* out, int out_dtype, long long ldo, long long part_stride, const void* x,
-                         long long ldx, const void* w, long long ldw, long long n_w_rows, int M, int N, int K,
-                         int dual, int up_offset, int act, float cap, int splits, int* err,
-                         cudaStream_t stream) {
-  if (M == 0 || N == 0) return 0;
-  AF_REQUIRE(M > 0 && N > 0 && K > 0, "af_gemm_tc: bad sizes %d %d %d", M, N, K);
+                         long long ldx, const void* w, long long ldw, long long n_w_rows, int M, int K, int gated,
+                         int act, int n_acc, float cap, int splits, int* err, cudaStream_t stream) {
+  if (M == 0 || n_w_rows == 0) return 0;
+  AF_REQUIRE(M > 0 && n_w_rows > 0 && K > 0, "af_gemm_tc: bad sizes %d %lld %d", M, n_w_rows, K);
   AF_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "af_gemm_tc: K %d and row strides must be multiples of 8", K);
   AF_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "af_gemm_tc: operands must be 16-byte aligned");
   AF_REQUIRE(splits >= 1 && (splits == 1 || out_dtype == AF_F32), "af_gemm_tc: split-K partial sums are float");
-  AF_REQUIRE(!(dual && splits > 1), "af_gemm_tc: the gated variant does not split K");
+  AF_REQUIRE(!(gated && splits > 1), "af_gemm_tc: the gated variant does not split K");
+  AF_REQUIRE(!gated || n_w_rows % 32 == 0, "af_gemm_tc: a gated weight holds whole groups of 16 + 16 rows");
+  AF_REQUIRE(n_acc == 1 || n_acc == 2, "af_gemm_tc: %d accumulators", n_acc);
   const int total_kb = (K + TC_BK - 1) / TC_BK;
   AF_REQUIRE(splits <= total_kb, "af_gemm_tc: %d splits of %d K blocks", splits, total_kb);
   const int kb_per_split = (total_kb + splits - 1) / splits;
@@ -287,11 +384,8 @@ AF_EXPORT int af_gemm_tc(void* out, int out_dtype, long long ldo, long long part
   if (rc) return rc;
   rc = af_make_map_bf16(&mx, x, M, K, ldx, bn);
   if (rc) return rc;
-  TcArgs a{out, ldo, part_stride, M, N, K, kb_per_split, up_offset, act, cap, err};
-  if (dual) {
-    if (out_dtype == AF_BF16) return launch_bn<true, __nv_bfloat16>(bn, mw, mx, a, 1, stream);
-    return launch_bn<true, float>(bn, mw, mx, a, 1, stream);
-  }
-  if (out_dtype == AF_BF16) return launch_bn<false, __nv_bfloat16>(bn, mw, mx, a, splits, stream);
-  return launch_bn<false, float>(bn, mw, mx, a, splits, stream);
+  const int N = gated ? (int)(n_w_rows / 2) : (int)n_w_rows;
+  TcArgs a{out, ldo, part_stride, M, N, K, kb_per_split, act, cap, err};
+  if (out_dtype == AF_BF16) return launch_variant<__nv_bfloat16>(n_acc, gated, bn, mw, mx, a, n_w_rows, splits, stream);
+  return launch_variant<float>(n_acc, gated, bn, mw, mx, a, n_w_rows, splits, stream);
 }

@@ -279,14 +279,17 @@ def gemm_tc_splits(M: int, N: int, K: int) -> int:
     return (kb + per - 1) // per
 
 
-def gemm_tc(out, x, w, cap: float = 0.0, splits: int = 1, dual_up_offset: int = -1, activation: str = "gelu_tanh",
-            n_features=None) -> None:
+def gemm_tc(out, x, w, cap: float = 0.0, splits: int = 1, gated: bool = False, activation: str = "gelu_tanh",
+            n_acc: int = 0) -> None:
     """out = x @ w^T on the tcgen05 tensor cores (bfloat16 operands, 32-bit
     accumulation in TMEM).  splits > 1: out is float32 [splits, M, N] partial
-    sums.  dual_up_offset >= 0: out[m, f] = act(x . w[f]) * (x . w[dual_up_offset + f])."""
+    sums.  gated: w holds, per group of 32 rows, 16 gate rows then the 16 up
+    rows of the same features (see ``interleave_gate_up``); out[m, f] =
+    act(x . gate_f) * (x . up_f), N = rows / 2.  n_acc: weight tiles per block
+    (0: chosen from the sizes)."""
     M, K = x.shape
-    dual = dual_up_offset >= 0
-    N = n_features if n_features is not None else w.shape[0]
+    rows = w.shape[0]
+    N = rows // 2 if gated else rows
     if not gemm_tc_supported(x, w, out):
         raise KernelError("gemm_tc: operands must be bfloat16 with dense, 16-byte aligned rows and K % 8 == 0")
     if splits > 1:
@@ -297,12 +300,35 @@ def gemm_tc(out, x, w, cap: float = 0.0, splits: int = 1, dual_up_offset: int = 
         if tuple(out.shape) != (M, N):
             raise KernelError(f"gemm_tc: output shape {tuple(out.shape)}, expected {(M, N)}")
         ldo, part = out.stride(0), 0
+    if n_acc == 0:
+        # two weight tiles per block halve the bytes per flop; worth it once tokens fill the
+        # widest tile and enough blocks remain to fill the GPU
+        blocks2 = ((rows + 255) // 256) * ((M + 255) // 256)
+        n_acc = 2 if (M > 128 and splits == 1 and blocks2 >= 120) else 1
     _check(_lib().af_gemm_tc(_ptr(out), c_int(dtype_code(out.dtype)), c_longlong(ldo), c_longlong(part), _ptr(x),
-                             c_longlong(x.stride(0)), _ptr(w), c_longlong(w.stride(0)), c_longlong(w.shape[0]),
-                             c_int(M), c_int(N), c_int(K), c_int(1 if dual else 0), c_int(max(dual_up_offset, 0)),
-                             c_int(ACTIVATIONS[activation]), c_float(cap), c_int(splits),
+                             c_longlong(x.stride(0)), _ptr(w), c_longlong(w.stride(0)), c_longlong(rows),
+                             c_int(M), c_int(K), c_int(1 if gated else 0), c_int(ACTIVATIONS[activation]),
+                             c_int(n_acc), c_float(cap), c_int(splits),
                              _ptr(error_word(x.device), "err", torch.int32), _stream()))
 
+
+def interleave_gate_up(w_gate, w_up):
+    """The gated product's weight layout: groups of 32 rows, each 16 gate rows
+    followed by the up rows of the same 16 features.  Rows beyond the last
+    whole 16 are padded with zeros (their outputs are never written)."""
+    inter, K = w_gate.shape
+    groups = (inter + 15) // 16
+    out = torch.zeros(groups * 32, K, dtype=w_gate.dtype, device=w_gate.device)
+    v = out.view(groups, 2, 16, K)
+    pad = groups * 16 - inter
+    if pad:
+        g = torch.cat([w_gate, torch.zeros(pad, K, dtype=w_gate.dtype, device=w_gate.device)])
+        u = torch.cat([w_up, torch.zeros(pad, K, dtype=w_up.dtype, device=w_up.device)])
+    else:
+        g, u = w_gate, w_up
+    v[:, 0] = g.view(groups, 16, K)
+    v[:, 1] = u.view(groups, 16, K)
+    return out
 
 def attn_prefill_mma(out, q, k, v, seq_starts, n_seqs: int, max_len: int, nq, nkv, hd, scale, cap, window) -> None:
     """bfloat16 prefill attention on the tensor cores; sequences packed row

@@ -51,15 +51,17 @@ def linear_split(x, w):
     return linear(x, w)
 
 
-def gated_linear(x, w_gu, inter: int, activation: str):
-    """act(x w_gate^T) * (x w_up^T) for w_gu = [gate rows; up rows]: one
-    kernel with the activation in its epilogue where the tensor-core kernel
-    takes the operands, else two steps."""
+def gated_linear(x, w_gu, inter: int, activation: str, interleaved: bool):
+    """act(x w_gate^T) * (x w_up^T).  ``interleaved``: w_gu is in the gated
+    tensor-core layout (``kernels.interleave_gate_up``) and one kernel with the
+    activation in its epilogue does it all; else w_gu = [gate rows; up rows],
+    a product and the activation kernel."""
     M = x.shape[0]
     out = torch.empty(M, inter, dtype=x.dtype, device=x.device)
-    if kernels.gemm_tc_supported(x, w_gu, out):
-        kernels.gemm_tc(out, x, w_gu, dual_up_offset=inter, activation=activation, n_features=inter)
-    else:
-        gu = linear(x, w_gu)
-        kernels.gated_act(out, gu, activation)
+    if interleaved:
+        full = out if w_gu.shape[0] // 2 == inter else torch.empty(M, w_gu.shape[0] // 2, dtype=x.dtype, device=x.device)
+        kernels.gemm_tc(full, x, w_gu, gated=True, activation=activation)
+        return full if full is out else full[:, :inter].contiguous()
+    gu = linear(x, w_gu)
+    kernels.gated_act(out, gu, activation)
     return out

@@ -32,6 +32,7 @@ class GatedMlp(FeedForward):
                               f"(known: {sorted(kernels.ACTIVATIONS)})")
         self.names = [self.param(k) for k in ("gate_weight", "up_weight", "down_weight")]
         self.w_gu = None
+        self.interleaved = False
         self.w_down = None
 
     def weight_decls(self):
@@ -42,9 +43,14 @@ class GatedMlp(FeedForward):
     def load(self, weights):
         g, u, d = self.names
         dt = self.ctx.compute_dtype
-        self.w_gu = torch.cat([weights[g], weights[u]], dim=0).to(dt).contiguous()
+        wg, wu = weights[g].to(dt), weights[u].to(dt)
+        # bfloat16 with a K the tensor-core product takes: gate and up rows interleaved per
+        # tile, activation in the product's epilogue; else [gate; up] and a kernel of its own
+        self.interleaved = dt == torch.bfloat16 and self.hidden % 8 == 0
+        self.w_gu = (kernels.interleave_gate_up(wg, wu) if self.interleaved
+                     else torch.cat([wg, wu], dim=0).contiguous())
         self.w_down = weights[d].to(dt).contiguous()
 
     def forward(self, x, batch):
-        h = gated_linear(x, self.w_gu, self.inter, self.activation)
+        h = gated_linear(x, self.w_gu, self.inter, self.activation, self.interleaved)
         return linear_split(h, self.w_down)

@@ -324,10 +324,11 @@ def test_gemm_tensor_cores(K, M, N, Kd, out_dtype):
     x = torch.randn(M, Kd).to(torch.bfloat16)
     w = (torch.randn(N, Kd) * 0.05).to(torch.bfloat16)
     ref = x.double() @ w.double().T
-    out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
-    K.gemm_tc(out, x.to(DEV), w.to(DEV))
-    K.check_device_errors(DEV)
-    close(out, ref, out_dtype if out_dtype == torch.bfloat16 else torch.float32)
+    for n_acc in (0, 1, 2):
+        out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+        K.gemm_tc(out, x.to(DEV), w.to(DEV), n_acc=n_acc)
+        K.check_device_errors(DEV)
+        close(out, ref, out_dtype if out_dtype == torch.bfloat16 else torch.float32)
     if out_dtype == torch.float32:
         K.gemm_tc(out, x.to(DEV), w.to(DEV), cap=1.5)
         close(out, plain.softcap(ref, 1.5), torch.float32)
@@ -349,17 +350,20 @@ def test_gemm_tensor_cores_split_k(K, M, N, Kd, splits):
 
 
 @pytest.mark.parametrize("M,I,Kd,act", [(8, 256, 128, "gelu_tanh"), (5, 200, 72, "silu"), (130, 448, 192, "gelu_tanh"),
-                                        (300, 9216, 2304, "gelu_tanh")])
+                                        (300, 9216, 2304, "gelu_tanh"), (40, 64, 64, "silu")])
 def test_gemm_tensor_cores_gated(K, M, I, Kd, act):
     x = torch.randn(M, Kd).to(torch.bfloat16)
     w = (torch.randn(2 * I, Kd) * 0.05).to(torch.bfloat16)
     g = x.double() @ w[:I].double().T
     u = x.double() @ w[I:].double().T
     ref = (plain.gelu_tanh(g) if act == "gelu_tanh" else g * torch.sigmoid(g)) * u
-    out = torch.full((M, I), float("nan"), dtype=torch.bfloat16, device=DEV)
-    K.gemm_tc(out, x.to(DEV), w.to(DEV), dual_up_offset=I, activation=act, n_features=I)
-    K.check_device_errors(DEV)
-    close(out, ref, torch.bfloat16)
+    wi = K.interleave_gate_up(w[:I].to(DEV), w[I:].to(DEV))
+    assert wi.shape[0] == (I + 15) // 16 * 32 and torch.equal(wi[16:32].cpu(), w[I: I + 16])
+    for n_acc in (1, 2):
+        out = torch.full((M, wi.shape[0] // 2), float("nan"), dtype=torch.bfloat16, device=DEV)
+        K.gemm_tc(out, x.to(DEV), wi, gated=True, activation=act, n_acc=n_acc)
+        K.check_device_errors(DEV)
+        close(out[:, :I], ref, torch.bfloat16)
 
 
 def test_gemm_tensor_cores_refuses_unaligned(K):
