@@ -92,6 +92,73 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const flo
   }
 }
 
+// The same for bfloat16 rows without partial sums, half-split pairs over the
+// whole head and head_dim % 16 == 0: one block per token, 16-byte loads and
+// stores, eight pairs a thread.
+__global__ void __launch_bounds__(256)
+rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, long long row_stride, const int* __restrict__ positions,
+                      const int* __restrict__ seq_of_token, const int* __restrict__ slots,
+                      const int* __restrict__ len_after, const float* __restrict__ inv_freq, int nq, int nkv, int hd,
+                      __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
+                      const int* __restrict__ page_table, int max_pages, int ring_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int pos = positions[t];
+  __nv_bfloat16* row = qkv + (size_t)t * row_stride;
+  const int half = hd / 2;
+  const int per_head = half / 8;                 // 16-byte pieces of a half head
+  const int n_heads = nq + 2 * nkv;
+  // where this token's k and v rows go in the cache
+  size_t dst_row = 0;
+  bool store = false;
+  if (kcache != nullptr) {
+    const int seq = seq_of_token[t];
+    const int slot = slots[seq];
+    if (slot >= 0 && !(ring_rows > 0 && pos + ring_rows < len_after[seq])) {
+      const int r = ring_rows > 0 ? pos % ring_rows : pos;
+      const int page = page_table[(size_t)slot * max_pages + r / AF_PAGE];
+      dst_row = ((size_t)page * nkv) * AF_PAGE + r % AF_PAGE;   // + h * AF_PAGE rows for kv head h
+      store = true;
+    }
+  }
+  for (int i = threadIdx.x; i < n_heads * per_head; i += blockDim.x) {
+    const int head = i / per_head, c = i - head * per_head;
+    __nv_bfloat16* x = row + (size_t)head * hd + c * 8;
+    uint4 lo = *reinterpret_cast<const uint4*>(x);
+    uint4 hi = *reinterpret_cast<const uint4*>(x + half);
+    if (head < nq + nkv) {
+      uint32_t* lw = reinterpret_cast<uint32_t*>(&lo);
+      uint32_t* hw = reinterpret_cast<uint32_t*>(&hi);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float a[2] = {__uint_as_float(lw[j] << 16), __uint_as_float(lw[j] & 0xffff0000u)};
+        float b[2] = {__uint_as_float(hw[j] << 16), __uint_as_float(hw[j] & 0xffff0000u)};
+        float ra[2], rb[2];
+#pragma unroll
+        for (int e = 0; e < 2; ++e) {
+          float sn, cs;
+          sincosf((float)pos * inv_freq[c * 8 + 2 * j + e], &sn, &cs);
+          ra[e] = a[e] * cs - b[e] * sn;
+          rb[e] = b[e] * cs + a[e] * sn;
+        }
+        __nv_bfloat162 pa = __floats2bfloat162_rn(ra[0], ra[1]), pb = __floats2bfloat162_rn(rb[0], rb[1]);
+        lw[j] = *reinterpret_cast<uint32_t*>(&pa);
+        hw[j] = *reinterpret_cast<uint32_t*>(&pb);
+      }
+      *reinterpret_cast<uint4*>(x) = lo;
+      *reinterpret_cast<uint4*>(x + half) = hi;
+    }
+    if (store && head >= nq) {
+      const bool is_v = head >= nq + nkv;
+      const int h = head - nq - (is_v ? nkv : 0);
+      __nv_bfloat16* d = (is_v ? vcache : kcache) + (dst_row + (size_t)h * AF_PAGE) * hd + c * 8;
+      *reinterpret_cast<uint4*>(d) = lo;
+      *reinterpret_cast<uint4*>(d + half) = hi;
+    }
+  }
+}
+
 // `parts` (optional): float [n_parts, n_tokens, row width] partial sums of the
 // rows, part_stride elements apart; they are added in order into qkv first.
 AF_EXPORT int af_rope_cache_write(void* qkv, int dtype, int row_stride, const float* parts, int n_parts,
@@ -108,6 +175,14 @@ AF_EXPORT int af_rope_cache_write(void* qkv, int dtype, int row_stride, const fl
   AF_REQUIRE(pairing == AF_PAIR_HALF || pairing == AF_PAIR_ADJACENT, "af_rope_cache_write: pairing");
   AF_REQUIRE(ring_rows % AF_PAGE == 0, "af_rope_cache_write: ring rows %d not whole pages", ring_rows);
   AF_REQUIRE((kcache == nullptr) == (vcache == nullptr), "af_rope_cache_write: k and v cache");
+  if (dtype == AF_BF16 && parts == nullptr && pairing == AF_PAIR_HALF && rot_dim == hd && hd % 16 == 0 &&
+      row_stride % 8 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)kcache & 15) == 0 &&
+      ((uintptr_t)vcache & 15) == 0 && n_tokens >= 64) {
+    af_launch(rope_cache_vec_kernel, dim3(n_tokens), dim3(256), 0, stream, (__nv_bfloat16*)qkv, (long long)row_stride,
+              positions, seq_of_token, slots, len_after, inv_freq, nq, nkv, hd, (__nv_bfloat16*)kcache,
+              (__nv_bfloat16*)vcache, page_table, max_pages, ring_rows);
+    AF_CHECK_LAUNCH("af_rope_cache_write");
+  }
   AF_DISPATCH_DTYPE(dtype, T,
                     af_launch(rope_cache_kernel<T>, dim3(dim3(n_tokens, nq + 2 * nkv)), dim3(hd / 2 < 32 ? 32 : (hd / 2 > 256 ? 256 : hd / 2)), 0, stream, 
                         (T*)qkv, row_stride, parts, n_parts, (size_t)part_stride, positions, seq_of_token,

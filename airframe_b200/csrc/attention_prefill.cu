@@ -3,8 +3,8 @@
 // optional window, softcapped scores, grouped heads, sequences of unequal
 // lengths packed row after row.
 //
-// A block of 8 warps owns 128 query rows of one head of one sequence; a warp
-// owns 16 of them.  K and V tiles of 64 keys come through two shared-memory
+// A block owns 64 or 128 query rows of one head of one sequence; a warp owns
+// 16 of them.  K and V tiles of 32 or 64 keys come through two shared-memory
 // stages (cp.async, 16-byte pieces, XOR-swizzled so that ldmatrix is free of
 // bank conflicts).  Scores, the running maximum, the running sum and the output
 // stay in 32-bit registers (online softmax); P is rounded to bfloat16 for the
@@ -13,9 +13,11 @@
 
 namespace {
 
-constexpr int PF_BM = 128;  // query rows per block
-constexpr int PF_BN = 64;   // keys per tile
-constexpr int PF_THREADS = 256;
+// Tile shapes per head size: query rows per block (16 a warp) and keys per
+// tile.  Smaller tiles for head size 256 let two blocks share an SM and spread
+// the triangular work of a causal mask over more blocks.
+template <int HD> struct PfShape { static constexpr int BM = 128, BN = 64; };
+template <> struct PfShape<256> { static constexpr int BM = 64, BN = 32; };
 
 __device__ __forceinline__ float pf_tanh(float x) {
   float y;
@@ -82,7 +84,7 @@ template <int HD, int ROWS>
 __device__ __forceinline__ void pf_load_tile(unsigned char* tile, const __nv_bfloat16* base, long long stride,
                                              int row0, int row_end) {
   constexpr int PIECES = HD / 8;
-  for (int i = threadIdx.x; i < ROWS * PIECES; i += PF_THREADS) {
+  for (int i = threadIdx.x; i < ROWS * PIECES; i += blockDim.x) {
     const int r = i / PIECES, c = i - r * PIECES;
     const bool on = row0 + r < row_end;
     const __nv_bfloat16* src = base + (size_t)(on ? row0 + r : row0) * stride + c * 8;
@@ -91,8 +93,9 @@ __device__ __forceinline__ void pf_load_tile(unsigned char* tile, const __nv_bfl
 }
 
 template <int HD>
-__global__ void __launch_bounds__(PF_THREADS, 1)
+__global__ void __launch_bounds__(PfShape<HD>::BM * 2)
 attn_prefill_mma_kernel(PrefillArgs a) {
+  constexpr int PF_BM = PfShape<HD>::BM, PF_BN = PfShape<HD>::BN;
   pdl_launch_dependents();
   pdl_wait();
   constexpr int KSTEPS = HD / 16;      // k-steps of Q K^T
@@ -258,6 +261,7 @@ attn_prefill_mma_kernel(PrefillArgs a) {
 
 template <int HD>
 int launch_prefill(const PrefillArgs& a, int n_seqs, int max_len, cudaStream_t stream) {
+  constexpr int PF_BM = PfShape<HD>::BM, PF_BN = PfShape<HD>::BN;
   const int smem = PF_BM * HD * 2 + 4 * PF_BN * HD * 2;
   static bool configured = false;
   if (!configured) {
@@ -266,7 +270,7 @@ int launch_prefill(const PrefillArgs& a, int n_seqs, int max_len, cudaStream_t s
     configured = true;
   }
   dim3 grid((max_len + PF_BM - 1) / PF_BM, n_seqs, a.nq);
-  af_launch(attn_prefill_mma_kernel<HD>, dim3(grid), dim3(PF_THREADS), smem, stream, a);
+  af_launch(attn_prefill_mma_kernel<HD>, dim3(grid), dim3(PF_BM * 2), smem, stream, a);
   AF_CHECK_LAUNCH("af_attn_prefill");
 }
 

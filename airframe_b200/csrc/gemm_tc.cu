@@ -109,14 +109,14 @@ struct TcArgs {
   long long part_stride;  // elements between split-K partial results
   int M, N, K;            // N: output features (GATED: half the weight's rows)
   int kb_per_split;       // K blocks handled by one z-slice
-  int act;
   float cap;
   int* err;
 };
 
-template <int BN, int NACC, bool GATED, typename TO>
+template <int BN, int NACC, int ACT, typename TO>  // ACT: -1 plain product, else the gated epilogue's activation
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcArgs a) {
+  constexpr bool GATED = ACT >= 0;
   constexpr int STAGES = tc_stages(BN, NACC);
   constexpr int A_BYTES = TC_BM * TC_BK * 2;
   constexpr int STAGE_BYTES = tc_stage_bytes(BN, NACC);
@@ -220,11 +220,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     // epilogue: warp w reads TMEM lanes [32 * (w % 4), + 32)
     const int quarter = warp & 3;
     pdl_wait();
-    bool done = mbar_wait(&acc_full, 0, give_up);  // (not const: experiments may clear it)
+    const bool done = mbar_wait(&acc_full, 0, give_up);
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-#ifdef AF_EXP_NOEPI
-    done = false;
-#endif
     if (done) {
       TO* out = reinterpret_cast<TO*>(a.out) + (size_t)blockIdx.z * a.part_stride;
       const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
@@ -247,15 +244,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             tmem_ld16(lane_base + acc * BN + c0, v);
           }
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-#ifdef AF_EXP_LDONLY
-          {
-            float accx = 0.f;
-#pragma unroll
-            for (int j = 0; j < CW; ++j) accx += v[j];
-            if (accx == 12345.678f) out[0] = from_f32<TO>(accx);
-            continue;
-          }
-#endif
           if (GATED) {
             // Within a warp lanes 0..15 hold gate rows and lanes 16..31 the up rows of the
             // same 16 features.  Each half keeps one half of the round's tokens and gets
@@ -266,7 +254,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
               const float got = __shfl_xor_sync(0xffffffffu, pick(low, v[j + CW / 2], v[j]), 16);
               // low lanes: g(own) * u(partner) for tokens [0, CW/2); high lanes: g(partner) * u(own) for [CW/2, CW)
               const float g = pick(low, v[j], got), u = pick(low, got, v[j + CW / 2]);
-              v[j] = tc_act(g, a.act) * u;
+              v[j] = tc_act(g, ACT) * u;
             }
           }
           if (a.cap > 0.f) {  // (fully unrolled: v stays in registers)
@@ -278,9 +266,14 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             const int tok0 = m0 + c0 + (lane < 16 ? 0 : CW / 2);
             if (f < a.N) {
               TO* o = out + (size_t)tok0 * a.ldo + f;
+              if (tok0 + CW / 2 <= a.M) {
 #pragma unroll
-              for (int j = 0; j < CW / 2; ++j)
-                if (tok0 + j < a.M) o[(size_t)j * a.ldo] = from_f32<TO>(v[j]);
+                for (int j = 0; j < CW / 2; ++j) o[(size_t)j * a.ldo] = from_f32<TO>(v[j]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < CW / 2; ++j)
+                  if (tok0 + j < a.M) o[(size_t)j * a.ldo] = from_f32<TO>(v[j]);
+              }
             }
           } else if (f < a.N) {
             TO* o = out + (size_t)(m0 + c0) * a.ldo + f;
@@ -307,45 +300,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
 // ---------------------------------------------------------------- host side
 
-template <int BN, int NACC, bool GATED, typename TO>
+template <int BN, int NACC, int ACT, typename TO>
 int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, long long n_w_rows, int splits,
            cudaStream_t stream) {
   constexpr int smem = tc_stages(BN, NACC) * tc_stage_bytes(BN, NACC) + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, NACC, GATED, TO>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, NACC, ACT, TO>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return af_fail((int)e, "gemm_tc: %s", cudaGetErrorString(e));
     configured = true;
   }
   const long long w_tiles = (n_w_rows + TC_BM - 1) / TC_BM;
   dim3 grid((unsigned)((w_tiles + NACC - 1) / NACC), (a.M + BN - 1) / BN, splits);
-  af_launch(gemm_tc_kernel<BN, NACC, GATED, TO>, grid, dim3(TC_THREADS), smem, stream, mw, mx, a);
+  af_launch(gemm_tc_kernel<BN, NACC, ACT, TO>, grid, dim3(TC_THREADS), smem, stream, mw, mx, a);
   AF_CHECK_LAUNCH("af_gemm_tc");
 }
 
-template <int NACC, bool GATED, typename TO>
+template <int NACC, int ACT, typename TO>
 int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, long long rows, int splits,
               cudaStream_t s) {
   switch (bn) {
-    case 16: return launch<16, NACC, GATED, TO>(mw, mx, a, rows, splits, s);
-    case 32: return launch<32, NACC, GATED, TO>(mw, mx, a, rows, splits, s);
-    case 64: return launch<64, NACC, GATED, TO>(mw, mx, a, rows, splits, s);
-    case 128: return launch<128, NACC, GATED, TO>(mw, mx, a, rows, splits, s);
-    case 256: return launch<256, NACC, GATED, TO>(mw, mx, a, rows, splits, s);
+    case 16: return launch<16, NACC, ACT, TO>(mw, mx, a, rows, splits, s);
+    case 32: return launch<32, NACC, ACT, TO>(mw, mx, a, rows, splits, s);
+    case 64: return launch<64, NACC, ACT, TO>(mw, mx, a, rows, splits, s);
+    case 128: return launch<128, NACC, ACT, TO>(mw, mx, a, rows, splits, s);
+    case 256: return launch<256, NACC, ACT, TO>(mw, mx, a, rows, splits, s);
   }
   return af_fail(-1, "gemm_tc: token tile %d", bn);
 }
 
 template <typename TO>
-int launch_variant(int nacc, int gated, int bn, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a,
+int launch_variant(int nacc, int gated, int act, int bn, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a,
                    long long rows, int splits, cudaStream_t s) {
-  if (gated) {
-    if (nacc == 2) return launch_bn<2, true, TO>(bn, mw, mx, a, rows, 1, s);
-    return launch_bn<1, true, TO>(bn, mw, mx, a, rows, 1, s);
+  if (gated && act == AF_ACT_GELU_TANH) {
+    if (nacc == 2) return launch_bn<2, AF_ACT_GELU_TANH, TO>(bn, mw, mx, a, rows, 1, s);
+    return launch_bn<1, AF_ACT_GELU_TANH, TO>(bn, mw, mx, a, rows, 1, s);
   }
-  if (nacc == 2) return launch_bn<2, false, TO>(bn, mw, mx, a, rows, splits, s);
-  return launch_bn<1, false, TO>(bn, mw, mx, a, rows, splits, s);
+  if (gated) {
+    if (nacc == 2) return launch_bn<2, AF_ACT_SILU, TO>(bn, mw, mx, a, rows, 1, s);
+    return launch_bn<1, AF_ACT_SILU, TO>(bn, mw, mx, a, rows, 1, s);
+  }
+  if (nacc == 2) return launch_bn<2, -1, TO>(bn, mw, mx, a, rows, splits, s);
+  return launch_bn<1, -1, TO>(bn, mw, mx, a, rows, splits, s);
 }
 
 }  // namespace
@@ -374,6 +371,7 @@ AF_EXPORT int af_gemm_tc(void* out, int out_dtype, long long ldo, long long part
   AF_REQUIRE(!(gated && splits > 1), "af_gemm_tc: the gated variant does not split K");
   AF_REQUIRE(!gated || n_w_rows % 32 == 0, "af_gemm_tc: a gated weight holds whole groups of 16 + 16 rows");
   AF_REQUIRE(n_acc == 1 || n_acc == 2, "af_gemm_tc: %d accumulators", n_acc);
+  AF_REQUIRE(!gated || act == AF_ACT_GELU_TANH || act == AF_ACT_SILU, "af_gemm_tc: unknown activation %d", act);
   const int total_kb = (K + TC_BK - 1) / TC_BK;
   AF_REQUIRE(splits <= total_kb, "af_gemm_tc: %d splits of %d K blocks", splits, total_kb);
   const int kb_per_split = (total_kb + splits - 1) / splits;
@@ -385,7 +383,7 @@ AF_EXPORT int af_gemm_tc(void* out, int out_dtype, long long ldo, long long part
   rc = af_make_map_bf16(&mx, x, M, K, ldx, bn);
   if (rc) return rc;
   const int N = gated ? (int)(n_w_rows / 2) : (int)n_w_rows;
-  TcArgs a{out, ldo, part_stride, M, N, K, kb_per_split, act, cap, err};
-  if (out_dtype == AF_BF16) return launch_variant<__nv_bfloat16>(n_acc, gated, bn, mw, mx, a, n_w_rows, splits, stream);
-  return launch_variant<float>(n_acc, gated, bn, mw, mx, a, n_w_rows, splits, stream);
+  TcArgs a{out, ldo, part_stride, M, N, K, kb_per_split, cap, err};
+  if (out_dtype == AF_BF16) return launch_variant<__nv_bfloat16>(n_acc, gated, act, bn, mw, mx, a, n_w_rows, splits, stream);
+  return launch_variant<float>(n_acc, gated, act, bn, mw, mx, a, n_w_rows, splits, stream);
 }
