@@ -170,7 +170,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       }
       // few tokens: the product is bound by the weight stream, so the rest of this block's
       // weights is asked into L2 while the kernel before still runs
-      if (BN <= 64) {
+      // (only when all blocks are resident at once: later waves would just ask twice)
+      if (BN <= 64 && gridDim.x * gridDim.y * gridDim.z <= 148) {
         for (int kb = early; kb < kb_count; ++kb) {
 #pragma unroll
           for (int acc = 0; acc < NACC; ++acc) tma_prefetch_2d(&map_w, (kb0 + kb) * TC_BK, n0 + acc * TC_BM);

@@ -36,7 +36,19 @@ TINY_C = {
     "torch_dtype": "bfloat16",
 }
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C}
+# the layer widths of Gemma-2 2B (head size 256, 8 heads in 4 groups) with two layers, a small
+# vocabulary and a small window: the sizes the tensor-core kernels are tuned for
+WIDE_D = {
+    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
+    "num_hidden_layers": 2, "hidden_size": 2304, "num_attention_heads": 8, "num_key_value_heads": 4,
+    "head_dim": 256, "intermediate_size": 9216, "vocab_size": 2048, "rope_theta": 10000.0,
+    "sliding_window": 100, "query_pre_attn_scalar": 256, "attn_logit_softcapping": 50.0,
+    "final_logit_softcapping": 30.0, "max_position_embeddings": 512, "rms_norm_eps": 1e-6,
+    "hidden_activation": "gelu_pytorch_tanh", "tie_word_embeddings": True, "eos_token_id": 1,
+    "torch_dtype": "bfloat16",
+}
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": WIDE_D}
 
 
 def make_folder(cfg_dict, seed=0, store_dtype=None, root=None):
