@@ -342,9 +342,27 @@ def attn_prefill_mma(out, q, k, v, seq_starts, n_seqs: int, max_len: int, nq, nk
         _stream()))
 
 
+def attn_prefill_tc(out, q, k, v, seq_starts, n_seqs: int, max_len: int, nq, nkv, hd, scale, cap, window) -> None:
+    """bfloat16 prefill attention on tcgen05 (S and O in TMEM); sequences packed
+    row after row, ``seq_starts`` int32 [n_seqs + 1]."""
+    if q.dtype != torch.bfloat16 or k.dtype != torch.bfloat16 or v.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+        raise KernelError("attn_prefill_tc: bfloat16 only")
+    if k.shape[0] != q.shape[0] or v.shape[0] != q.shape[0]:
+        raise KernelError("attn_prefill_tc: q, k and v hold the same rows")
+    _check(_lib().af_attn_prefill_tc(
+        _ptr(out), c_longlong(_rows(out, "out")), _ptr(q), c_longlong(_rows(q, "q")), _ptr(k),
+        c_longlong(_rows(k, "k")), _ptr(v), c_longlong(_rows(v, "v")), _ptr(seq_starts, "seq_starts", torch.int32),
+        c_int(n_seqs), c_int(q.shape[0]), c_int(max_len), c_int(nq), c_int(nkv), c_int(hd), c_float(scale),
+        c_float(cap), c_int(window), _ptr(error_word(q.device), "err", torch.int32), _stream()))
+
+
 def attn_prefill(out, q, k, v, batch, nq, nkv, hd, scale, cap, window) -> None:
-    """Attention of a prefill step: the tensor-core kernel for bfloat16 and
-    the head sizes it takes, else the plain kernel."""
+    """Attention of a prefill step: for bfloat16 the tcgen05 kernel (head sizes
+    128, 256) or the mma.sync kernel (64), else the plain kernel."""
+    aligned = all(t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 for t in (q, k, v, out))
+    if q.dtype == torch.bfloat16 and aligned and _lib().af_attn_prefill_tc_supported(c_int(hd)):
+        attn_prefill_tc(out, q, k, v, batch.seq_starts, batch.n_seqs, batch.max_len, nq, nkv, hd, scale, cap, window)
+        return
     if (q.dtype == torch.bfloat16 and _lib().af_attn_prefill_supported(c_int(hd))
             and all(t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 for t in (q, k, v))):
         attn_prefill_mma(out, q, k, v, batch.seq_starts, batch.n_seqs, batch.max_len, nq, nkv, hd, scale, cap, window)

@@ -28,6 +28,9 @@ def tol(dtype):
 
 
 def close(got, ref, dtype, scale=None):
+    """Largest absolute error over ``scale`` (the largest reference magnitude by default;
+    attention outputs use max(1, that): a bfloat16 result is off by up to one unit in its
+    last place, 2^-8 of its own magnitude)."""
     ref = ref.double()
     s = scale if scale is not None else ref.abs().max().clamp_min(1e-30)
     err = float((got.double().cpu() - ref).abs().max() / s)
@@ -416,3 +419,66 @@ def test_attention_prefill_tensor_cores_finds_one_far_key_and_the_window_edge(K)
         visible = window == 0 or (row - far) < window
         near = (out[row].double().cpu().reshape(nq, hd) - v[far].double()).abs().max()
         assert (near < 0.05) == visible, (window, far, float(near))
+
+
+@pytest.mark.parametrize("hd,nq,nkv,window,cap", [(128, 6, 2, 70, 0.0), (256, 4, 2, 300, 30.0), (256, 2, 1, 0, 0.0),
+                                                  (128, 2, 2, 64, 10.0), (256, 8, 4, 0, 50.0), (128, 3, 1, 5, 20.0)])
+def test_attention_prefill_tcgen05(K, hd, nq, nkv, window, cap):
+    torch.manual_seed(hd + window)
+    lens = [37, 1, 200, 128, 129, 64, 513, 1000]
+    T = sum(lens)
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd).to(torch.bfloat16).to(DEV)      # packed rows, as the mixer holds them
+    q, k, v = qkv[:, : nq * hd], qkv[:, nq * hd: (nq + nkv) * hd], qkv[:, (nq + nkv) * hd:]
+    starts = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=torch.int32, device=DEV)
+    out = torch.full((T, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+    scale = 1.1 / math.sqrt(hd)
+    K.attn_prefill_tc(out, q, k, v, starts, len(lens), max(lens), nq, nkv, hd, scale, cap, window)
+    K.check_device_errors(DEV)
+    o = 0
+    for n in lens:
+        ref = plain.attention(q[o:o + n].double().cpu().reshape(n, nq, hd), k[o:o + n].double().cpu().reshape(n, nkv, hd),
+                              v[o:o + n].double().cpu().reshape(n, nkv, hd), scale, cap, window or None)
+        close(out[o:o + n], ref, torch.bfloat16, scale=max(1.0, float(ref.abs().max())))
+        o += n
+    # the twin on the legacy tensor path sees the same inputs
+    twin = torch.empty_like(out)
+    K.attn_prefill_mma(twin, q, k, v, starts, len(lens), max(lens), nq, nkv, hd, scale, cap, window)
+    close(out, twin.double().cpu(), torch.bfloat16, scale=max(1.0, float(twin.float().abs().max())))
+
+
+def test_attention_prefill_tcgen05_finds_one_far_key_the_window_edge_and_a_growing_maximum(K):
+    """One dominant key far back, at and just outside the window's edge; and scores that grow
+    along the sequence, so that the reference maximum has to move and O is rescaled."""
+    hd, nq, nkv, n = 128, 2, 1, 700
+    torch.manual_seed(4)
+    q = (torch.randn(n, nq * hd) * 0.05)
+    base_k = torch.randn(n, nkv * hd) * 0.01
+    v = torch.randn(n, nkv * hd).to(torch.bfloat16)
+    starts = torch.tensor([0, n], dtype=torch.int32, device=DEV)
+    row = n - 1
+    qv = torch.randn(nq, hd)
+    q[row] = qv.reshape(-1)
+    for window, far in [(0, 5), (0, 333), (257, row - 256), (257, row - 257), (64, row - 63), (64, row - 64)]:
+        k = base_k.clone()
+        k[far] = (qv[0] + qv[1]) * 8.0
+        qb, kb = q.to(torch.bfloat16), k.to(torch.bfloat16)
+        out = torch.empty(n, nq * hd, dtype=torch.bfloat16, device=DEV)
+        K.attn_prefill_tc(out, qb.to(DEV), kb.to(DEV), v.to(DEV), starts, 1, n, nq, nkv, hd, 1.0, 0.0, window)
+        ref = plain.attention(qb.double().reshape(n, nq, hd), kb.double().reshape(n, nkv, hd),
+                              v.double().reshape(n, nkv, hd), 1.0, 0.0, window or None)
+        close(out, ref, torch.bfloat16, scale=max(1.0, float(ref.abs().max())))
+        visible = window == 0 or (row - far) < window
+        near = (out[row].double().cpu().reshape(nq, hd) - v[far].double()).abs().max()
+        assert (near < 0.05) == visible, (window, far, float(near))
+    # keys whose score with every query grows by 3 per 64 positions: the maximum moves again and again
+    u = torch.randn(hd)
+    u = u / u.norm()
+    qg = (u * 4.0).repeat(n, nq)
+    kg = torch.stack([u * (0.75 * (j // 64)) for j in range(n)]) + torch.randn(n, hd) * 0.01
+    qb, kb = qg.to(torch.bfloat16), kg.to(torch.bfloat16)
+    out = torch.empty(n, nq * hd, dtype=torch.bfloat16, device=DEV)
+    K.attn_prefill_tc(out, qb.to(DEV), kb.to(DEV), v.to(DEV), starts, 1, n, nq, nkv, hd, 1.0, 0.0, 0)
+    K.check_device_errors(DEV)
+    ref = plain.attention(qb.double().reshape(n, nq, hd), kb.double().reshape(n, nkv, hd),
+                          v.double().reshape(n, nkv, hd), 1.0, 0.0, None)
+    close(out, ref, torch.bfloat16, scale=max(1.0, float(ref.abs().max())))
