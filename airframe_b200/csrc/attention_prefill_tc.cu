@@ -6,17 +6,18 @@
 //   S = Q K^T   tcgen05.mma, Q and the K tile K-major in 128-byte swizzled shared
 //               memory (TMA), S (128 x 64, float) in TMEM, two S buffers so that
 //               the next tile's scores are computed while this tile's softmax runs
-//   softmax     four warps, one query row a thread: tcgen05.ld of its S row,
-//               scale, softcap, mask, running maximum and sum in 32 bits; P is
-//               rounded to bfloat16 and written to swizzled shared memory
+//   softmax     eight warps, two threads a query row (32 keys each): tcgen05.ld of
+//               their part of the S row, scale, softcap, mask, running maximum
+//               (shared through shared memory) and sum in 32 bits; P is rounded
+//               to bfloat16 and written to swizzled shared memory
 //   O += P V    tcgen05.mma, P K-major, the V tile MN-major as TMA wrote it,
 //               O (128 x head_dim, float) in TMEM for the whole block
 // The running maximum only moves when it grows by more than 8 (in base-2
 // exponent units): then O is rescaled in TMEM; otherwise P is computed against
 // the older maximum (bounded by 2^8), which changes no result.
 //
-//   warp 0      TMA producer          warp 1      MMA issue, TMEM allocation
-//   warps 2..5  softmax, O rescale, epilogue
+//   warp 0      TMA producer of Q and K    warp 1      MMA issue, TMEM allocation
+//   warps 2..9  softmax, O rescale, epilogue   warp 10  TMA producer of V
 // Every mbarrier wait is bounded in time; a wait that runs out sets the error
 // word, and the block releases its TMEM and returns.
 #include "umma.cuh"
@@ -25,7 +26,8 @@ namespace {
 
 constexpr int TA_BM = 128;  // query rows per block
 constexpr int TA_BN = 64;   // keys per tile
-constexpr int TA_THREADS = 192;
+constexpr int TA_PARTS = 4;      // threads per query row in the softmax (16 keys each)
+constexpr int TA_THREADS = (2 + 4 * TA_PARTS + 1) * 32;  // Q/K producer, MMA, softmax warps, V producer
 constexpr float TA_LOG2E = 1.4426950408889634f;
 constexpr float TA_RESCALE = 8.f;  // the maximum moves only when it grows by more than this
 
@@ -69,7 +71,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   unsigned char* q_s = sm;
   unsigned char* kv_s = sm + Q_BYTES;                // [stage][K tile | V tile]
   unsigned char* p_s = kv_s + 4 * KV_BYTES;
-  __shared__ uint64_t q_full, kv_full[2], kv_empty[2], s_full[2], s_empty[2], p_full, p_empty, o_full;
+  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, p_empty, o_full, x_full;
+  __shared__ float mx_s[2][TA_PARTS][TA_BM], l_s[TA_PARTS][TA_BM];
   __shared__ uint32_t tmem_base_s;
   __shared__ int give_up_s;
   volatile int* give_up = &give_up_s;
@@ -82,12 +85,15 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&kv_full[s], 1);
-      mbar_init(&kv_empty[s], 1);
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
+      mbar_init(&v_full[s], 1);
+      mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 128);
+      mbar_init(&s_empty[s], 128 * TA_PARTS);
     }
-    mbar_init(&p_full, 128);
+    mbar_init(&p_full, 128 * TA_PARTS);
+    mbar_init(&x_full, 128 * TA_PARTS);
     mbar_init(&p_empty, 1);
     mbar_init(&o_full, 1);
     give_up_s = 0;
@@ -115,21 +121,33 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const int nb = active ? kb_hi - kb_lo + 1 : 0;     // key tiles of this block
 
   if (warp == 0) {
+    // Q, then the K tiles: a K slot is free as soon as its scores are computed,
+    // well before the tile's V slot, so K and V have producers of their own
     if (lane == 0 && active) {
       mbar_expect_tx(&q_full, Q_BYTES);
 #pragma unroll
       for (int c = 0; c < SUB; ++c) tma_load_2d(q_s + c * Q_SUB, &map_q, head * HD + c * 64, row0 + m0, &q_full);
       for (int j = 0; j < nb; ++j) {
         const int s = j & 1;
-        if (!mbar_wait(&kv_empty[s], ((j >> 1) & 1) ^ 1, give_up)) break;
+        if (!mbar_wait(&k_empty[s], ((j >> 1) & 1) ^ 1, give_up)) break;
         unsigned char* st = kv_s + (size_t)s * 2 * KV_BYTES;
-        mbar_expect_tx(&kv_full[s], 2 * KV_BYTES);
+        mbar_expect_tx(&k_full[s], KV_BYTES);
         const int r = row0 + (kb_lo + j) * TA_BN;
 #pragma unroll
-        for (int c = 0; c < SUB; ++c) {
-          tma_load_2d(st + c * KV_SUB, &map_k, kvh * HD + c * 64, r, &kv_full[s]);
-          tma_load_2d(st + KV_BYTES + c * KV_SUB, &map_v, kvh * HD + c * 64, r, &kv_full[s]);
-        }
+        for (int c = 0; c < SUB; ++c) tma_load_2d(st + c * KV_SUB, &map_k, kvh * HD + c * 64, r, &k_full[s]);
+      }
+      if (*give_up) grace_period();
+    }
+  } else if (warp == 2 + 4 * TA_PARTS) {
+    if (lane == 0 && active) {
+      for (int j = 0; j < nb; ++j) {
+        const int s = j & 1;
+        if (!mbar_wait(&v_empty[s], ((j >> 1) & 1) ^ 1, give_up)) break;
+        unsigned char* st = kv_s + (size_t)s * 2 * KV_BYTES + KV_BYTES;
+        mbar_expect_tx(&v_full[s], KV_BYTES);
+        const int r = row0 + (kb_lo + j) * TA_BN;
+#pragma unroll
+        for (int c = 0; c < SUB; ++c) tma_load_2d(st + c * KV_SUB, &map_v, kvh * HD + c * 64, r, &v_full[s]);
       }
       if (*give_up) grace_period();
     }
@@ -144,9 +162,10 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           umma_f16(tmem + (j & 1) * TA_BN, umma_desc(qt + (ks >> 2) * Q_SUB) + 2 * (ks & 3),
                    umma_desc(kt + (ks >> 2) * KV_SUB) + 2 * (ks & 3), IDESC_S, ks > 0 ? 1u : 0u);
         umma_commit(&s_full[j & 1]);
+        umma_commit(&k_empty[j & 1]);    // the K tile is consumed
       };
       if (ok && nb > 0) {
-        ok = mbar_wait(&kv_full[0], 0, give_up);
+        ok = mbar_wait(&k_full[0], 0, give_up);
         if (ok) {
           tc_fence_after();
           issue_s(0);
@@ -155,13 +174,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       for (int j = 0; j < nb && ok; ++j) {
         if (j + 1 < nb) {  // the next tile's scores, while this tile's softmax runs
           const int s = (j + 1) & 1;
-          ok = mbar_wait(&kv_full[s], ((j + 1) >> 1) & 1, give_up);
+          ok = mbar_wait(&k_full[s], ((j + 1) >> 1) & 1, give_up);
           if (ok && j + 1 >= 2) ok = mbar_wait(&s_empty[s], (((j + 1) >> 1) & 1) ^ 1, give_up);
           if (!ok) break;
           tc_fence_after();
           issue_s(j + 1);
         }
-        ok = mbar_wait(&p_full, j & 1, give_up);
+        ok = mbar_wait(&v_full[j & 1], (j >> 1) & 1, give_up) && mbar_wait(&p_full, j & 1, give_up);
         if (!ok) break;
         tc_fence_after();
         // O += P(j) V(j): P K-major [128 x 64 keys], V MN-major [64 keys x HD]
@@ -172,18 +191,22 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           umma_f16(tmem + O_COL, umma_desc(pt) + 2 * kk, umma_desc_mn(vt + kk * 2048, KV_SUB), IDESC_O,
                    (j > 0 || kk > 0) ? 1u : 0u);
         umma_commit(&p_empty);           // P consumed, O updated
-        umma_commit(&kv_empty[j & 1]);   // K and V of this stage consumed
+        umma_commit(&v_empty[j & 1]);    // the V tile is consumed
       }
       if (ok) umma_commit(&o_full);
     }
-  } else if (active) {
-    // ---- softmax warps: thread = query row
+  } else if (active && warp < 2 + 4 * TA_PARTS) {
+    // ---- softmax warps: a thread owns a part (16 keys) of a query row's scores; the warps
+    // w, w + 4, ... share the rows of TMEM lane quarter w % 4
     const int quarter = warp & 3;
+    const int half = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
     const int i = m0 + row;                                   // this thread's query position
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
     const float cs = a.cap > 0.f ? a.scale / a.cap : a.scale * TA_LOG2E;
     const float cap2 = a.cap * TA_LOG2E;
+    constexpr int W = TA_BN / TA_PARTS;                       // scores per thread and tile
+    constexpr int OW = HD / TA_PARTS;                         // O columns per thread
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < nb; ++j) {
@@ -192,17 +215,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         break;
       }
       tc_fence_after();
-      float s[TA_BN];
-      tmem_ld32(lane_addr + (j & 1) * TA_BN, s);
-      tmem_ld32(lane_addr + (j & 1) * TA_BN + 32, s + 32);
+      float s[W];
+      tmem_ld16(lane_addr + (j & 1) * TA_BN + half * W, s);
       tmem_wait_ld();
       tc_fence_before();
       mbar_arrive(&s_empty[j & 1]);                           // the S buffer may be overwritten
-      const int j0 = (kb_lo + j) * TA_BN;
-      const bool edge = (j0 + TA_BN - 1 > i) || (j0 + TA_BN > len) || (a.window > 0 && i - j0 >= a.window);
-      float mx = -INFINITY;
+      const int j0 = (kb_lo + j) * TA_BN + half * W;
+      const bool edge = (j0 + W - 1 > i) || (j0 + W > len) || (a.window > 0 && i - j0 >= a.window);
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < TA_BN; ++c) {
+      for (int c = 0; c < W; ++c) {
         float v = s[c] * cs;
         if (a.cap > 0.f) v = cap2 * ta_tanh(v);
         if (edge) {
@@ -210,8 +232,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           v = (jj <= i && jj < len && (a.window <= 0 || i - jj < a.window)) ? v : -INFINITY;
         }
         s[c] = v;
-        mx = fmaxf(mx, v);
+        mx4[c & 3] = fmaxf(mx4[c & 3], v);
       }
+      // the row's maximum over both halves
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      mx_s[j & 1][half][row] = mx;
+      mbar_arrive(&x_full);
+      if (!mbar_wait(&x_full, j & 1, give_up)) {
+        ok = false;
+        break;
+      }
+#pragma unroll
+      for (int h = 0; h < TA_PARTS; ++h) mx = fmaxf(mx, mx_s[j & 1][h][row]);
       // the reference maximum moves only when it has to
       float corr = 1.f;
       if (mx > m_ref + TA_RESCALE || m_ref == -INFINITY) {
@@ -220,17 +252,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         m_ref = m_new;
       }
       const float ref = m_ref == -INFINITY ? 0.f : m_ref;
-      float sum = 0.f;
-      uint32_t packed[TA_BN / 2];
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t packed[W / 2];
 #pragma unroll
-      for (int c = 0; c < TA_BN; c += 2) {
+      for (int c = 0; c < W; c += 2) {
         const float p0 = ta_exp2(s[c] - ref), p1 = ta_exp2(s[c + 1] - ref);
         __nv_bfloat162 pb = __floats2bfloat162_rn(p0, p1);
         // the sum uses the rounded values that the product will see
-        sum += __low2float(pb) + __high2float(pb);
+        sum4[(c >> 1) & 3] += __low2float(pb) + __high2float(pb);
         packed[c / 2] = *reinterpret_cast<uint32_t*>(&pb);
       }
-      l = l * corr + sum;
+      l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
       // P(j-1) V(j-1) must be done before O is rescaled and P's memory reused
       if (j > 0 && !mbar_wait(&p_empty, (j - 1) & 1, give_up)) {
         ok = false;
@@ -239,36 +271,44 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       tc_fence_after();
       if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
 #pragma unroll 1
-        for (int c0 = 0; c0 < HD; c0 += 32) {
+        for (int c0 = 0; c0 < OW; c0 += 32) {
           float o[32];
-          tmem_ld32(lane_addr + O_COL + c0, o);
+          tmem_ld32(lane_addr + O_COL + half * OW + c0, o);
           tmem_wait_ld();
 #pragma unroll
           for (int c = 0; c < 32; ++c) o[c] *= corr;
-          tmem_st32(lane_addr + O_COL + c0, o);
+          tmem_st32(lane_addr + O_COL + half * OW + c0, o);
         }
         tmem_wait_st();
       }
-      // P row into the swizzled [128 x 128 B] tile: 16-byte piece c lands at piece c ^ (row & 7)
+      // P half row into the swizzled [128 x 128 B] tile: 16-byte piece c lands at piece c ^ (row & 7)
       unsigned char* prow = p_s + row * 128;
 #pragma unroll
-      for (int c = 0; c < 8; ++c)
-        *reinterpret_cast<uint4*>(prow + ((c ^ (row & 7)) << 4)) =
+      for (int c = 0; c < W / 8; ++c)
+        *reinterpret_cast<uint4*>(prow + (((half * (W / 8) + c) ^ (row & 7)) << 4)) =
             make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA
       tc_fence_before();
       mbar_arrive(&p_full);
     }
-    // ---- epilogue: O / l -> bfloat16
+    // ---- epilogue: O / l -> bfloat16 (l is the sum of both halves' sums)
     if (ok && nb > 0) ok = mbar_wait(&o_full, 0, give_up);
+    l_s[half][row] = l;
+    if (ok && nb > 0) {
+      mbar_arrive(&x_full);
+      ok = mbar_wait(&x_full, nb & 1, give_up);
+    }
     if (ok && nb > 0) {
       tc_fence_after();
-      const float inv = l > 0.f ? 1.f / l : 0.f;
-      __nv_bfloat16* dst = a.out + (size_t)(row0 + i) * a.out_stride + (size_t)head * HD;
+      float lt = 0.f;
+#pragma unroll
+      for (int h = 0; h < TA_PARTS; ++h) lt += l_s[h][row];
+      const float inv = lt > 0.f ? 1.f / lt : 0.f;
+      __nv_bfloat16* dst = a.out + (size_t)(row0 + i) * a.out_stride + (size_t)head * HD + half * OW;
 #pragma unroll 1
-      for (int c0 = 0; c0 < HD; c0 += 32) {
+      for (int c0 = 0; c0 < OW; c0 += 32) {
         float o[32];
-        tmem_ld32(lane_addr + O_COL + c0, o);
+        tmem_ld32(lane_addr + O_COL + half * OW + c0, o);
         tmem_wait_ld();
         if (i < len) {
 #pragma unroll

@@ -39,6 +39,8 @@ constexpr unsigned long long AF_WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 // limit ran out (then *give_up is set) or another thread gave up already.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* give_up) {
   if (mbar_try_wait(bar, parity)) return true;
+  // try_wait itself suspends the thread for a while; the timer read between two polls
+  // keeps waiting threads from crowding out working ones
   const unsigned long long t0 = now_ns();
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
