@@ -12,6 +12,11 @@
 // output) in scratch memory.  Waits on the copies are bounded in time.
 // Pass 2, grid (sequence, head): merges the splits and writes bfloat16.
 //
+// The cache rows of earlier tokens do not depend on the kernels before this
+// one in the stream, nor do slots, lengths and page table (they are step
+// inputs), so a block starts its first page copies before it waits for its
+// predecessor; only the page that holds the new token waits.
+//
 // Scores are 32-bit; softcap uses tanh.approx and the softmax ex2.approx, which
 // is what the bfloat16 path allows; the 32-bit path uses the plain kernel.
 #include <mutex>
@@ -50,6 +55,8 @@ struct DecodeArgs {
   float* part_o;   // [batch, nq, splits, HD]
   float* part_ml;  // [batch, nq, splits, 2]
   int* err;        // set to 1 when a bounded wait ran out
+  __nv_bfloat16* out;  // [batch, nq * HD], rows out_stride apart
+  long long out_stride;
 };
 
 __device__ __forceinline__ void da_ldm4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
@@ -117,15 +124,15 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     give_up_s = 0;
     mbar_fence_init();
   }
-  pdl_wait();
   const int slot = a.slots[b];
   const int len = slot >= 0 ? a.lens[b] : 0;
   const int pos = len - 1;
   const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
 
   int pp_begin = 0, pp_end = 0;
+  const int last_pp = pos / AF_PAGE;  // the page of the new token, which the kernel before wrote
   if (len > 0) {
-    const int first_pp = lo / AF_PAGE, last_pp = pos / AF_PAGE;
+    const int first_pp = lo / AF_PAGE;
     const int n_pp = last_pp - first_pp + 1;
     const int per = (n_pp + a.n_splits - 1) / a.n_splits;
     pp_begin = first_pp + z * per;
@@ -149,8 +156,12 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       tma_load_2d(st + TILE_BYTES + c * 8192, &map_v, c * 64, row, bar);
     }
   };
+  int issued = 0;
   if (tid == 0)
-    for (int i = 0; i < STAGES && i < n_pages; ++i) issue(i);
+    for (; issued < STAGES && issued < n_pages && pp_begin + issued != last_pp; ++issued) issue(issued);
+  pdl_wait();
+  if (tid == 0)
+    for (; issued < STAGES && issued < n_pages; ++issued) issue(issued);
 
   // the query heads as A fragments: rows g and g + 8 of the tile
   uint32_t qf[KSTEPS][4];
@@ -315,8 +326,7 @@ __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long l
 }
 
 template <int HD>
-int launch_decode(const DecodeArgs& a, __nv_bfloat16* out, long long out_stride, int batch, long long n_pages,
-                  cudaStream_t stream) {
+int launch_decode(DecodeArgs a, int batch, long long n_pages, cudaStream_t stream) {
   const size_t stage_bytes = (size_t)da_stages<HD>() * 2 * AF_PAGE * HD * 2;
   const size_t merge_bytes = (size_t)4 * 16 * HD * sizeof(float);
   const size_t smem = (stage_bytes > merge_bytes ? stage_bytes : merge_bytes) + 1024;
@@ -337,8 +347,8 @@ int launch_decode(const DecodeArgs& a, __nv_bfloat16* out, long long out_stride,
   dim3 grid(batch, a.nkv * ((group + 15) / 16), a.n_splits);
   af_launch(attn_decode_split_kernel<HD>, grid, dim3(DA_THREADS), smem, stream, mk, mv, a);
   AF_COUNT_LAUNCH("af_attn_decode (split)");
-  af_launch(attn_decode_merge_kernel<HD>, dim3(batch, a.nq), dim3(HD < 128 ? HD : 128), 0, stream, out, out_stride,
-            a.part_o, a.part_ml, a.nq, a.n_splits);
+  af_launch(attn_decode_merge_kernel<HD>, dim3(batch, a.nq), dim3(HD < 128 ? HD : 128), 0, stream, a.out,
+            a.out_stride, a.part_o, a.part_ml, a.nq, a.n_splits);
   AF_CHECK_LAUNCH("af_attn_decode (merge)");
 }
 
@@ -387,11 +397,12 @@ AF_EXPORT int af_attn_decode(void* out, long long out_stride, const void* q, lon
   a.part_o = scratch;
   a.part_ml = scratch + (size_t)batch * nq * n_splits * hd;
   a.err = err;
-  __nv_bfloat16* o = (__nv_bfloat16*)out;
+  a.out = (__nv_bfloat16*)out;
+  a.out_stride = out_stride;
   AF_REQUIRE(n_pages > 0 && n_pages * nkv * AF_PAGE < (1ll << 31), "af_attn_decode: %lld cache pages", n_pages);
-  if (hd == 64) return launch_decode<64>(a, o, out_stride, batch, n_pages, stream);
-  if (hd == 128) return launch_decode<128>(a, o, out_stride, batch, n_pages, stream);
-  return launch_decode<256>(a, o, out_stride, batch, n_pages, stream);
+  if (hd == 64) return launch_decode<64>(a, batch, n_pages, stream);
+  if (hd == 128) return launch_decode<128>(a, batch, n_pages, stream);
+  return launch_decode<256>(a, batch, n_pages, stream);
 }
 
 // ---------------------------------------------------------------- no allocation

@@ -29,13 +29,15 @@ namespace {
 constexpr int TC_BM = 128;  // features per CTA = UMMA M
 constexpr int TC_BK = 64;   // K per stage: 128 bytes of bfloat16 = one swizzle row
 constexpr int TC_THREADS = 192;
-constexpr int TC_SMEM_BUDGET = 192 * 1024;
+constexpr int TC_SMS = 148;
+constexpr int TC_SMEM_BUDGET = 192 * 1024;    // of one block alone on its SM
+constexpr int TC_SMEM_BUDGET_2 = 108 * 1024;  // of each of two blocks that share an SM
 
 __host__ __device__ constexpr int tc_stage_bytes(int bn, int nacc) {
   return nacc * TC_BM * TC_BK * 2 + bn * TC_BK * 2;
 }
-__host__ __device__ constexpr int tc_stages(int bn, int nacc) {
-  int s = TC_SMEM_BUDGET / tc_stage_bytes(bn, nacc);
+__host__ __device__ constexpr int tc_stages(int bn, int nacc, int per_sm) {
+  int s = (per_sm == 2 ? TC_SMEM_BUDGET_2 : TC_SMEM_BUDGET) / tc_stage_bytes(bn, nacc);
   return s > 8 ? 8 : s;
 }
 __host__ __device__ constexpr int tc_tmem_cols(int bn, int nacc) {
@@ -65,11 +67,13 @@ struct TcArgs {
   int* err;
 };
 
-template <int BN, int NACC, int ACT, typename TO>  // ACT: -1 plain product, else the gated epilogue's activation
-__global__ void __launch_bounds__(TC_THREADS, 1)
+// ACT: -1 plain product, else the gated epilogue's activation.  PER_SM: 2 halves the stages so that
+// two blocks share an SM (grids of several waves: one block's fill and drain hide behind the other).
+template <int BN, int NACC, int ACT, typename TO, int PER_SM>
+__global__ void __launch_bounds__(TC_THREADS, PER_SM)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcArgs a) {
   constexpr bool GATED = ACT >= 0;
-  constexpr int STAGES = tc_stages(BN, NACC);
+  constexpr int STAGES = tc_stages(BN, NACC, PER_SM);
   constexpr int A_BYTES = TC_BM * TC_BK * 2;
   constexpr int STAGE_BYTES = tc_stage_bytes(BN, NACC);
   constexpr int COLS = tc_tmem_cols(BN, NACC);
@@ -119,15 +123,6 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         const int k = (kb0 + kb) * TC_BK;
 #pragma unroll
         for (int acc = 0; acc < NACC; ++acc) tma_load_2d(st + acc * A_BYTES, &map_w, k, n0 + acc * TC_BM, &full[kb]);
-      }
-      // few tokens: the product is bound by the weight stream, so the rest of this block's
-      // weights is asked into L2 while the kernel before still runs
-      // (only when all blocks are resident at once: later waves would just ask twice)
-      if (BN <= 64 && gridDim.x * gridDim.y * gridDim.z <= 148) {
-        for (int kb = early; kb < kb_count; ++kb) {
-#pragma unroll
-          for (int acc = 0; acc < NACC; ++acc) tma_prefetch_2d(&map_w, (kb0 + kb) * TC_BK, n0 + acc * TC_BM);
-        }
       }
       pdl_wait();
       for (int kb = 0; kb < early; ++kb)
@@ -253,21 +248,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
 // ---------------------------------------------------------------- host side
 
-template <int BN, int NACC, int ACT, typename TO>
-int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, long long n_w_rows, int splits,
-           cudaStream_t stream) {
-  constexpr int smem = tc_stages(BN, NACC) * tc_stage_bytes(BN, NACC) + 1024;
+template <int BN, int NACC, int ACT, typename TO, int PER_SM>
+int launch_on(dim3 grid, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, cudaStream_t stream) {
+  constexpr int smem = tc_stages(BN, NACC, PER_SM) * tc_stage_bytes(BN, NACC) + 1024;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, NACC, ACT, TO>,
+    cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, NACC, ACT, TO, PER_SM>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return af_fail((int)e, "gemm_tc: %s", cudaGetErrorString(e));
     configured = true;
   }
+  af_launch(gemm_tc_kernel<BN, NACC, ACT, TO, PER_SM>, grid, dim3(TC_THREADS), smem, stream, mw, mx, a);
+  AF_CHECK_LAUNCH("af_gemm_tc");
+}
+
+template <int BN, int NACC, int ACT, typename TO>
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, long long n_w_rows, int splits,
+           cudaStream_t stream) {
   const long long w_tiles = (n_w_rows + TC_BM - 1) / TC_BM;
   dim3 grid((unsigned)((w_tiles + NACC - 1) / NACC), (a.M + BN - 1) / BN, splits);
-  af_launch(gemm_tc_kernel<BN, NACC, ACT, TO>, grid, dim3(TC_THREADS), smem, stream, mw, mx, a);
-  AF_CHECK_LAUNCH("af_gemm_tc");
+  const long long blocks = (long long)grid.x * grid.y * grid.z;
+  if constexpr (BN <= 64 && NACC == 1) {
+    // bound by the weight stream
+    if (blocks > 2 * TC_SMS) return launch_on<BN, NACC, ACT, TO, 2>(grid, mw, mx, a, stream);
+  }
+  return launch_on<BN, NACC, ACT, TO, 1>(grid, mw, mx, a, stream);
 }
 
 template <int NACC, int ACT, typename TO>
