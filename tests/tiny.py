@@ -48,7 +48,14 @@ WIDE_D = {
     "torch_dtype": "bfloat16",
 }
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": WIDE_D}
+# the layer widths of Gemma-2 9B (16 heads in 8 groups, head size 256) and of Gemma-2 27B (32 heads
+# in 16 groups, head size 128, a score scale that is not head_dim^-0.5), two layers each
+WIDE_E = dict(WIDE_D, hidden_size=3584, num_attention_heads=16, num_key_value_heads=8, intermediate_size=14336,
+              vocab_size=1536, sliding_window=72)
+WIDE_F = dict(WIDE_D, hidden_size=4608, num_attention_heads=32, num_key_value_heads=16, head_dim=128,
+              intermediate_size=36864, query_pre_attn_scalar=144, vocab_size=1024, sliding_window=90)
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": WIDE_D, "E": WIDE_E, "F": WIDE_F}
 
 
 def make_folder(cfg_dict, seed=0, store_dtype=None, root=None):
