@@ -40,7 +40,9 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const flo
                                   T* __restrict__ kcache, T* __restrict__ vcache,
                                   const int* __restrict__ page_table, int max_pages, int ring_rows) {
   pdl_launch_dependents();
-  pdl_wait();
+  // Positions, slots, lengths, the page table and the frequencies are inputs of the step, not
+  // results of the kernel before: the row's place in the cache and the first pair's sine and
+  // cosine are worked out before the wait for that kernel.
   const int t = blockIdx.x, head = blockIdx.y;
   const int pos = positions[t];
   T* row = qkv + (size_t)t * row_stride + (size_t)head * hd;
@@ -61,6 +63,9 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const flo
     }
   }
   const bool rotate = head < nq + nkv;
+  float s0 = 0.f, c0 = 1.f;
+  if (rotate && threadIdx.x < half) sincosf((float)pos * inv_freq[threadIdx.x], &s0, &c0);
+  pdl_wait();
   // rotary pairs
   for (int p = threadIdx.x; p < half; p += blockDim.x) {
     const int i0 = pairing == AF_PAIR_HALF ? p : 2 * p;
@@ -68,8 +73,8 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const flo
     float a = rope_src(row, pr, n_parts, part_stride, i0);
     float b = rope_src(row, pr, n_parts, part_stride, i1);
     if (rotate) {
-      float s, c;
-      sincosf((float)pos * inv_freq[p], &s, &c);
+      float s = s0, c = c0;
+      if (p != threadIdx.x) sincosf((float)pos * inv_freq[p], &s, &c);
       const float ra = a * c - b * s, rb = b * c + a * s;
       a = ra;
       b = rb;
