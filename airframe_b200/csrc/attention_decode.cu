@@ -2,13 +2,15 @@
 // a step of few sequences still fills the GPU (it is bound by the bytes of K
 // and V it reads; every byte is read once).
 //
-// Pass 1, grid (sequence, kv head, split): a block of 4 warps walks its share
-// of the sequence's cache pages.  One thread brings the K and V tiles of a page
+// Pass 1, grid (sequence, kv head, split): a block of two groups of 4 warps
+// walks its share of the sequence's cache pages, the groups taking alternate
+// pages (one warp per scheduler cannot hide the latency of its own chain of
+// shared-memory loads and mma).  One thread brings the K and V tiles of a page
 // in by TMA (128-byte swizzled boxes, mbarrier-tracked) through a ring of
 // shared-memory stages.  The query heads of the kv group are the rows of an
 // m16n8k16 tile (mma.sync, 32-bit accumulators): Q K^T, online softmax in
 // registers (32-bit max, sum, output), P V.  Each warp takes 16 of a page's 64
-// keys; the four warps are merged through shared memory and leave (max, sum,
+// keys; all warps are merged through shared memory and leave (max, sum,
 // output) in scratch memory.  Waits on the copies are bounded in time.
 // Pass 2, grid (sequence, head): merges the splits and writes bfloat16.
 //
@@ -26,7 +28,10 @@
 
 namespace {
 
-constexpr int DA_THREADS = 128;
+constexpr int DA_GROUPS = 2;    // warp groups of a block; a group of four warps works on one page at a time
+constexpr int DA_THREADS = DA_GROUPS * 128;
+constexpr int DA_WARPS = DA_THREADS / 32;
+constexpr int DA_SCH = 2;  // chains of score accumulators
 
 __device__ __forceinline__ float fast_tanh(float x) {
   float y;
@@ -100,12 +105,16 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   constexpr int KSTEPS = HD / 16;
   constexpr int ONT = HD / 8;
   constexpr int STAGES = da_stages<HD>();
+  constexpr int SCH = DA_SCH;
   constexpr uint32_t TILE_BYTES = AF_PAGE * HD * 2;
   constexpr float LOG2E = 1.4426950408889634f;
   extern __shared__ unsigned char da_smem_raw[];
   unsigned char* da_smem = (unsigned char*)(((uintptr_t)da_smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ float m_s[4 * 16], l_s[4 * 16];
-  __shared__ uint64_t full[STAGES];
+  __shared__ float m_s[DA_WARPS * 16], l_s[DA_WARPS * 16];
+  // a barrier per page modulo 2 * STAGES: the two groups run ahead of one another, and a page and the
+  // page STAGES later (the other group's, in the same stage) must not share a barrier's phases
+  constexpr int NBAR = 2 * STAGES;
+  __shared__ uint64_t full[NBAR];
   __shared__ int give_up_s;
   volatile int* give_up = &give_up_s;
 
@@ -118,9 +127,10 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   const int n_rows = min(16, kvh * group + group - row_head0);           // heads in this tile
   const int z = blockIdx.z;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int grp = warp >> 2, wq = warp & 3;   // warp group; this warp's quarter of a page's keys
   const int g = lane >> 2, t = lane & 3;
   if (tid == 0) {
-    for (int s = 0; s < STAGES; ++s) mbar_init(&full[s], 1);
+    for (int s = 0; s < NBAR; ++s) mbar_init(&full[s], 1);
     give_up_s = 0;
     mbar_fence_init();
   }
@@ -148,7 +158,7 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     const int page = pt[ring_pages > 0 ? pp % ring_pages : pp];
     const int row = (page * a.nkv + kvh) * AF_PAGE;
     unsigned char* st = da_smem + (size_t)(i % STAGES) * 2 * TILE_BYTES;
-    uint64_t* bar = &full[i % STAGES];
+    uint64_t* bar = &full[i % NBAR];
     mbar_expect_tx(bar, 2 * TILE_BYTES);
 #pragma unroll
     for (int c = 0; c < HD / 64; ++c) {
@@ -184,25 +194,48 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   float mx[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f};
   const float cs = a.cap > 0.f ? a.scale / a.cap : a.scale * LOG2E;
   const float cap2 = a.cap * LOG2E;
-
-  for (int i = 0; i < n_pages; ++i) {
+  for (int i = grp; i < n_pages; i += DA_GROUPS) {
     const int s = i % STAGES;
-    if (!mbar_wait(&full[s], (i / STAGES) & 1, give_up)) break;
+    const int ok = mbar_wait(&full[i % NBAR], (i / NBAR) & 1, give_up) ? 1 : 0;
+    // the four warps of the group go on or give up together
+    int all_ok;
+    asm volatile(
+        "{\n\t.reg .pred p, q;\n\t"
+        "setp.ne.b32 q, %1, 0;\n\t"
+        "barrier.red.and.pred.aligned p, %2, 128, q;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(all_ok)
+        : "r"(ok), "r"(1 + grp)
+        : "memory");
+    if (!all_ok) break;
     const uint32_t k_t = smem_u32(da_smem + (size_t)s * 2 * TILE_BYTES);
     const uint32_t v_t = k_t + TILE_BYTES;
     // ---- S = Q K^T for this warp's 16 keys
-    float sc[2][4];
+    // (SCH chains of accumulators: an mma waits for the one before it on the same accumulator)
+    float scp[SCH][2][4];
 #pragma unroll
-    for (int n = 0; n < 2; ++n) sc[n][0] = sc[n][1] = sc[n][2] = sc[n][3] = 0.f;
+    for (int c = 0; c < SCH; ++c)
+#pragma unroll
+      for (int n = 0; n < 2; ++n) scp[c][n][0] = scp[c][n][1] = scp[c][n][2] = scp[c][n][3] = 0.f;
 #pragma unroll
     for (int ks = 0; ks < KSTEPS; ++ks) {
       uint32_t b0, b1, b2, b3;
-      da_ldm4(da_piece(k_t, warp * 16 + (lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
-      da_mma(sc[0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
-      da_mma(sc[1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+      da_ldm4(da_piece(k_t, wq * 16 + (lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
+      da_mma(scp[ks % SCH][0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
+      da_mma(scp[ks % SCH][1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
     }
+    float sc[2][4];
+#pragma unroll
+    for (int n = 0; n < 2; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        float v = scp[0][n][e];
+#pragma unroll
+        for (int c = 1; c < SCH; ++c) v += scp[c][n][e];
+        sc[n][e] = v;
+      }
     // ---- scale, softcap, mask, online softmax (base 2)
-    const int j0 = (pp_begin + i) * AF_PAGE + warp * 16;
+    const int j0 = (pp_begin + i) * AF_PAGE + wq * 16;
     float new_max[2] = {mx[0], mx[1]};
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
@@ -251,19 +284,20 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
 #pragma unroll
       for (int np = 0; np < ONT / 2; ++np) {
         uint32_t b0, b1, b2, b3;
-        da_ldm4t(da_piece(v_t, warp * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, np * 2 + (lane >> 4)), b0, b1, b2, b3);
+        da_ldm4t(da_piece(v_t, wq * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, np * 2 + (lane >> 4)), b0, b1, b2, b3);
         da_mma(o[2 * np], a0, a1, a2, a3, b0, b1);
         da_mma(o[2 * np + 1], a0, a1, a2, a3, b2, b3);
       }
     }
-    __syncthreads();  // everyone is done with stage s
-    if (tid == 0 && i + STAGES < n_pages && !*give_up) issue(i + STAGES);
+    // the group is done with stage s (a barrier of its own four warps): its first thread refills it
+    asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory");
+    if ((tid & 127) == 0 && i + STAGES < n_pages && !*give_up) issue(i + STAGES);
   }
   if (*give_up && tid == 0) grace_period();
   __syncthreads();
 
   // ---- merge the four warps (each saw a quarter of the keys); the stage memory is the buffer
-  float* o_s = reinterpret_cast<float*>(da_smem);  // [warp][16 rows][HD]
+  float* o_s = reinterpret_cast<float*>(da_smem);  // [warp][rows of real heads][HD]
 #pragma unroll
   for (int r = 0; r < 2; ++r) {
     sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
@@ -273,11 +307,13 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       m_s[warp * 16 + row] = mx[r];
       l_s[warp * 16 + row] = sum[r];
     }
+    if (row < n_rows) {
 #pragma unroll
-    for (int n = 0; n < ONT; ++n) {
-      float* dst = o_s + ((size_t)(warp * 16 + row)) * HD + n * 8 + 2 * t;
-      dst[0] = o[n][2 * r];
-      dst[1] = o[n][2 * r + 1];
+      for (int n = 0; n < ONT; ++n) {
+        float* dst = o_s + ((size_t)(warp * n_rows + row)) * HD + n * 8 + 2 * t;
+        dst[0] = o[n][2 * r];
+        dst[1] = o[n][2 * r + 1];
+      }
     }
   }
   __syncthreads();
@@ -285,14 +321,14 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     const int row = i / HD, d = i - row * HD;
     float M = -INFINITY;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) M = fmaxf(M, m_s[w * 16 + row]);
+    for (int w = 0; w < DA_WARPS; ++w) M = fmaxf(M, m_s[w * 16 + row]);
     const float ref = M == -INFINITY ? 0.f : M;
     float L = 0.f, O = 0.f;
 #pragma unroll
-    for (int w = 0; w < 4; ++w) {
+    for (int w = 0; w < DA_WARPS; ++w) {
       const float f = fast_exp2(m_s[w * 16 + row] - ref);
       L += l_s[w * 16 + row] * f;
-      O += o_s[((size_t)(w * 16 + row)) * HD + d] * f;
+      O += o_s[((size_t)(w * n_rows + row)) * HD + d] * f;
     }
     const size_t pidx = ((size_t)b * a.nq + row_head0 + row) * a.n_splits + z;
     a.part_o[pidx * HD + d] = O;
@@ -328,7 +364,7 @@ __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long l
 template <int HD>
 int launch_decode(DecodeArgs a, int batch, long long n_pages, cudaStream_t stream) {
   const size_t stage_bytes = (size_t)da_stages<HD>() * 2 * AF_PAGE * HD * 2;
-  const size_t merge_bytes = (size_t)4 * 16 * HD * sizeof(float);
+  const size_t merge_bytes = (size_t)DA_WARPS * 16 * HD * sizeof(float);
   const size_t smem = (stage_bytes > merge_bytes ? stage_bytes : merge_bytes) + 1024;
   static bool configured = false;
   if (!configured) {
