@@ -2,22 +2,26 @@
 // causal with an optional window, softcapped scores, grouped heads, sequences
 // of unequal lengths packed row after row.
 //
-// A block owns 128 query rows of one head of one sequence (the 128 TMEM lanes).
-//   S = Q K^T   tcgen05.mma, Q and the K tile K-major in 128-byte swizzled shared
-//               memory (TMA), S (128 x 64, float) in TMEM, two S buffers so that
-//               the next tile's scores are computed while this tile's softmax runs
-//   softmax     eight warps, two threads a query row (32 keys each): tcgen05.ld of
-//               their part of the S row, scale, softcap, mask, running maximum
-//               (shared through shared memory) and sum in 32 bits; P is rounded
-//               to bfloat16 and written to swizzled shared memory
-//   O += P V    tcgen05.mma, P K-major, the V tile MN-major as TMA wrote it,
+// A block owns 128 query rows of one head of one sequence (the 128 TMEM lanes)
+// and walks the keys 128 at a time (two TMA tiles of 64 keys).
+//   S = Q K^T   tcgen05.mma with N = 128: Q and the pair of K tiles K-major in
+//               128-byte swizzled shared memory, S (128 x 128, float) in TMEM,
+//               two S buffers so that the next pair's scores are computed
+//               while this pair's softmax runs.  (An mma costs some 70 cycles
+//               whatever its N, so few wide instructions beat many narrow ones.)
+//   softmax     sixteen warps, four threads a query row (32 keys each):
+//               tcgen05.ld of their part of the S row, scale, softcap, mask,
+//               running maximum (shared through shared memory) and sum in 32
+//               bits; P is rounded to bfloat16 and written to swizzled shared memory
+//   O += P V    tcgen05.mma, P K-major, the V tiles MN-major as TMA wrote them,
 //               O (128 x head_dim, float) in TMEM for the whole block
 // The running maximum only moves when it grows by more than 8 (in base-2
 // exponent units): then O is rescaled in TMEM; otherwise P is computed against
 // the older maximum (bounded by 2^8), which changes no result.
 //
-//   warp 0      TMA producer of Q and K    warp 1      MMA issue, TMEM allocation
-//   warps 2..9  softmax, O rescale, epilogue   warp 10  TMA producer of V
+//   warp 0       TMA producer of Q and K      warp 1    issue of S = Q K^T, TMEM allocation
+//   warps 2..17  softmax, O rescale, epilogue
+//   warp 18      TMA producer of V            warp 19   issue of O += P V
 // Every mbarrier wait is bounded in time; a wait that runs out sets the error
 // word, and the block releases its TMEM and returns.
 #include "umma.cuh"
@@ -25,9 +29,10 @@
 namespace {
 
 constexpr int TA_BM = 128;  // query rows per block
-constexpr int TA_BN = 64;   // keys per tile
-constexpr int TA_PARTS = 4;      // threads per query row in the softmax (16 keys each)
-constexpr int TA_THREADS = (2 + 4 * TA_PARTS + 1) * 32;  // Q/K producer, MMA, softmax warps, V producer
+constexpr int TA_KT = 64;   // keys per TMA tile (a 128-byte swizzled row holds 64 of P's keys, too)
+constexpr int TA_BN = 128;  // keys per step: one S product, two tiles
+constexpr int TA_PARTS = 4;      // threads per query row in the softmax (32 keys each)
+constexpr int TA_THREADS = (2 + 4 * TA_PARTS + 2) * 32;
 constexpr float TA_LOG2E = 1.4426950408889634f;
 constexpr float TA_RESCALE = 8.f;  // the maximum moves only when it grows by more than this
 
@@ -58,21 +63,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const __grid_constant__ CUtensorMap map_v, TaArgs a) {
   constexpr int SUB = HD / 64;                       // 64-column sub-tiles of a head
   constexpr int Q_SUB = TA_BM * 128;                 // bytes of one Q sub-tile [128 rows][128 B]
-  constexpr int KV_SUB = TA_BN * 128;                // bytes of one K or V sub-tile [64 rows][128 B]
-  constexpr int Q_BYTES = SUB * Q_SUB, KV_BYTES = SUB * KV_SUB;
-  constexpr int P_BYTES = TA_BM * TA_BN * 2;         // [128 rows][64 keys] bfloat16 = one swizzled sub-tile
-  constexpr int O_COL = 2 * TA_BN;                   // TMEM columns: S0 [0,64) S1 [64,128) O [128, 128 + HD)
+  constexpr int K_SUB = TA_BN * 128;                 // one K sub-tile of a pair [128 keys][128 B]
+  constexpr int V_SUB = TA_KT * 128;                 // one V sub-tile [64 keys][128 B]
+  constexpr int Q_BYTES = SUB * Q_SUB, K_BYTES = SUB * K_SUB, V_BYTES = SUB * V_SUB;
+  constexpr int P_SUB = TA_BM * 128;                 // P of 64 keys [128 rows][128 B]
+  constexpr int O_COL = 2 * TA_BN;                   // TMEM columns: S0 [0,128) S1 [128,256) O [256, 256 + HD)
   constexpr int COLS = 512;
   constexpr uint32_t IDESC_S = umma_idesc(TA_BN, false);
   constexpr uint32_t IDESC_O = umma_idesc(HD, true);
 
-  extern __shared__ unsigned char ta_raw[];
-  unsigned char* sm = (unsigned char*)(((uintptr_t)ta_raw + 1023) & ~(uintptr_t)1023);
+  extern __shared__ __align__(1024) unsigned char sm[];
   unsigned char* q_s = sm;
-  unsigned char* kv_s = sm + Q_BYTES;                // [stage][K tile | V tile]
-  unsigned char* p_s = kv_s + 4 * KV_BYTES;
-  __shared__ uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, p_empty, o_full, x_full;
-  __shared__ float mx_s[2][TA_PARTS][TA_BM], l_s[TA_PARTS][TA_BM];
+  unsigned char* k_s = q_s + Q_BYTES;                // [sub-tile][128 keys of the pair][128 B]
+  unsigned char* v_s = k_s + K_BYTES;                // [tile slot 0, 1][sub-tile][64 keys][128 B]
+  unsigned char* p_s = v_s + 2 * V_BYTES;            // [64-key half][128 rows][128 B]
+  __shared__ uint64_t q_full, k_full, k_empty, v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, p_empty, o_full,
+      x_full;
+  // the parts' maxima of a row, rounded up to bfloat16 (the reference maximum may sit a little above the true one)
+  __shared__ __nv_bfloat16 mx_s[2][TA_PARTS][TA_BM];
   __shared__ uint32_t tmem_base_s;
   __shared__ int give_up_s;
   volatile int* give_up = &give_up_s;
@@ -84,16 +92,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
+    mbar_init(&k_full, 1);
+    mbar_init(&k_empty, 1);
     for (int s = 0; s < 2; ++s) {
-      mbar_init(&k_full[s], 1);
-      mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 128 * TA_PARTS);
+      mbar_init(&s_empty[s], 4 * TA_PARTS);  // one arrival a softmax warp
     }
-    mbar_init(&p_full, 128 * TA_PARTS);
-    mbar_init(&x_full, 128 * TA_PARTS);
+    mbar_init(&p_full, 4 * TA_PARTS);
+    mbar_init(&x_full, 4 * TA_PARTS);
     mbar_init(&p_empty, 1);
     mbar_init(&o_full, 1);
     give_up_s = 0;
@@ -117,110 +125,113 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   const bool active = m0 < len;
   const int m_last = min(m0 + TA_BM, len) - 1;
   const int j_lo = a.window > 0 ? max(0, m0 - a.window + 1) : 0;
-  const int kb_lo = j_lo / TA_BN, kb_hi = active ? m_last / TA_BN : -1;
-  const int nb = active ? kb_hi - kb_lo + 1 : 0;     // key tiles of this block
+  const int kt_lo = j_lo / TA_KT, kt_hi = active ? m_last / TA_KT : -1;
+  const int n_tiles = active ? kt_hi - kt_lo + 1 : 0;   // 64-key tiles this block needs
+  const int np = (n_tiles + 1) / 2;                     // steps: pairs of tiles (the last may hold one masked tile)
 
   if (warp == 0) {
-    // Q, then the K tiles: a K slot is free as soon as its scores are computed,
-    // well before the tile's V slot, so K and V have producers of their own
+    // Q, then the pairs of K tiles (one buffer: the next pair is fetched as soon as this pair's scores are computed)
     if (lane == 0 && active) {
       mbar_expect_tx(&q_full, Q_BYTES);
 #pragma unroll
       for (int c = 0; c < SUB; ++c) tma_load_2d(q_s + c * Q_SUB, &map_q, head * HD + c * 64, row0 + m0, &q_full);
-      for (int j = 0; j < nb; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(&k_empty[s], ((j >> 1) & 1) ^ 1, give_up)) break;
-        unsigned char* st = kv_s + (size_t)s * 2 * KV_BYTES;
-        mbar_expect_tx(&k_full[s], KV_BYTES);
-        const int r = row0 + (kb_lo + j) * TA_BN;
+      for (int j = 0; j < np; ++j) {
+        if (!mbar_wait(&k_empty, (j & 1) ^ 1, give_up)) break;
+        mbar_expect_tx(&k_full, K_BYTES);
+        const int r = row0 + (kt_lo + 2 * j) * TA_KT;
 #pragma unroll
-        for (int c = 0; c < SUB; ++c) tma_load_2d(st + c * KV_SUB, &map_k, kvh * HD + c * 64, r, &k_full[s]);
+        for (int c = 0; c < SUB; ++c) {
+          // rows past the packed rows read as zeros; rows of the next sequence are masked by position
+          tma_load_2d(k_s + c * K_SUB, &map_k, kvh * HD + c * 64, r, &k_full);
+          tma_load_2d(k_s + c * K_SUB + TA_KT * 128, &map_k, kvh * HD + c * 64, r + TA_KT, &k_full);
+        }
       }
       if (*give_up) grace_period();
     }
   } else if (warp == 2 + 4 * TA_PARTS) {
     if (lane == 0 && active) {
-      for (int j = 0; j < nb; ++j) {
-        const int s = j & 1;
-        if (!mbar_wait(&v_empty[s], ((j >> 1) & 1) ^ 1, give_up)) break;
-        unsigned char* st = kv_s + (size_t)s * 2 * KV_BYTES + KV_BYTES;
-        mbar_expect_tx(&v_full[s], KV_BYTES);
-        const int r = row0 + (kb_lo + j) * TA_BN;
+      for (int t = 0; t < 2 * np; ++t) {
+        const int s = t & 1;
+        if (!mbar_wait(&v_empty[s], ((t >> 1) & 1) ^ 1, give_up)) break;
+        unsigned char* st = v_s + (size_t)s * V_BYTES;
+        mbar_expect_tx(&v_full[s], V_BYTES);
+        const int r = row0 + (kt_lo + t) * TA_KT;
 #pragma unroll
-        for (int c = 0; c < SUB; ++c) tma_load_2d(st + c * KV_SUB, &map_v, kvh * HD + c * 64, r, &v_full[s]);
+        for (int c = 0; c < SUB; ++c) tma_load_2d(st + c * V_SUB, &map_v, kvh * HD + c * 64, r, &v_full[s]);
       }
       if (*give_up) grace_period();
     }
   } else if (warp == 1) {
     if (lane == 0 && active) {
       bool ok = mbar_wait(&q_full, 0, give_up);
-      auto issue_s = [&](int j) {  // S(j) = Q K(j)^T into S buffer j % 2
-        const uint32_t kt = smem_u32(kv_s + (size_t)(j & 1) * 2 * KV_BYTES);
-        const uint32_t qt = smem_u32(q_s);
+      for (int j = 0; j < np && ok; ++j) {  // S(j) = Q K(j)^T into S buffer j % 2, ahead of the softmax
+        ok = mbar_wait(&k_full, j & 1, give_up);
+        if (ok && j >= 2) ok = mbar_wait(&s_empty[j & 1], ((j >> 1) & 1) ^ 1, give_up);
+        if (!ok) break;
+        tc_fence_after();
+        const uint32_t kt = smem_u32(k_s), qt = smem_u32(q_s);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
           umma_f16(tmem + (j & 1) * TA_BN, umma_desc(qt + (ks >> 2) * Q_SUB) + 2 * (ks & 3),
-                   umma_desc(kt + (ks >> 2) * KV_SUB) + 2 * (ks & 3), IDESC_S, ks > 0 ? 1u : 0u);
+                   umma_desc(kt + (ks >> 2) * K_SUB) + 2 * (ks & 3), IDESC_S, ks > 0 ? 1u : 0u);
         umma_commit(&s_full[j & 1]);
-        umma_commit(&k_empty[j & 1]);    // the K tile is consumed
-      };
-      if (ok && nb > 0) {
-        ok = mbar_wait(&k_full[0], 0, give_up);
-        if (ok) {
-          tc_fence_after();
-          issue_s(0);
-        }
+        umma_commit(&k_empty);             // the pair of K tiles is consumed
       }
-      for (int j = 0; j < nb && ok; ++j) {
-        if (j + 1 < nb) {  // the next tile's scores, while this tile's softmax runs
-          const int s = (j + 1) & 1;
-          ok = mbar_wait(&k_full[s], ((j + 1) >> 1) & 1, give_up);
-          if (ok && j + 1 >= 2) ok = mbar_wait(&s_empty[s], (((j + 1) >> 1) & 1) ^ 1, give_up);
+    }
+  } else if (warp == 3 + 4 * TA_PARTS) {
+    // ---- O += P(j) V(j), issued by a thread of its own: the tensor pipe takes the
+    // instructions of both issuing threads as they come
+    if (lane == 0 && active) {
+      bool ok = true;
+      for (int j = 0; j < np && ok; ++j) {
+        ok = mbar_wait(&p_full, j & 1, give_up);
+#pragma unroll
+        for (int h = 0; h < 2 && ok; ++h) {
+          const int t = 2 * j + h;
+          ok = mbar_wait(&v_full[t & 1], (t >> 1) & 1, give_up);
           if (!ok) break;
           tc_fence_after();
-          issue_s(j + 1);
-        }
-        ok = mbar_wait(&v_full[j & 1], (j >> 1) & 1, give_up) && mbar_wait(&p_full, j & 1, give_up);
-        if (!ok) break;
-        tc_fence_after();
-        // O += P(j) V(j): P K-major [128 x 64 keys], V MN-major [64 keys x HD]
-        const uint32_t vt = smem_u32(kv_s + (size_t)(j & 1) * 2 * KV_BYTES + KV_BYTES);
-        const uint32_t pt = smem_u32(p_s);
+          // P K-major [128 x 64 keys], V MN-major [64 keys x HD]
+          const uint32_t vt = smem_u32(v_s + (size_t)(t & 1) * V_BYTES);
+          const uint32_t pt = smem_u32(p_s + h * P_SUB);
 #pragma unroll
-        for (int kk = 0; kk < TA_BN / 16; ++kk)
-          umma_f16(tmem + O_COL, umma_desc(pt) + 2 * kk, umma_desc_mn(vt + kk * 2048, KV_SUB), IDESC_O,
-                   (j > 0 || kk > 0) ? 1u : 0u);
-        umma_commit(&p_empty);           // P consumed, O updated
-        umma_commit(&v_empty[j & 1]);    // the V tile is consumed
+          for (int kk = 0; kk < TA_KT / 16; ++kk)
+            umma_f16(tmem + O_COL, umma_desc(pt) + 2 * kk, umma_desc_mn(vt + kk * 2048, V_SUB), IDESC_O,
+                     (t > 0 || kk > 0) ? 1u : 0u);
+          umma_commit(&v_empty[t & 1]);    // the V tile is consumed
+        }
+        if (ok) umma_commit(&p_empty);     // P consumed, O updated
       }
       if (ok) umma_commit(&o_full);
     }
   } else if (active && warp < 2 + 4 * TA_PARTS) {
-    // ---- softmax warps: a thread owns a part (16 keys) of a query row's scores; the warps
+    // ---- softmax warps: a thread owns a part (32 keys) of a query row's scores; the warps
     // w, w + 4, ... share the rows of TMEM lane quarter w % 4
     const int quarter = warp & 3;
-    const int half = (warp - 2) >> 2;
+    const int part = (warp - 2) >> 2;
     const int row = quarter * 32 + lane;
     const int i = m0 + row;                                   // this thread's query position
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
     const float cs = a.cap > 0.f ? a.scale / a.cap : a.scale * TA_LOG2E;
     const float cap2 = a.cap * TA_LOG2E;
-    constexpr int W = TA_BN / TA_PARTS;                       // scores per thread and tile
+    constexpr int W = TA_BN / TA_PARTS;                       // scores per thread and step
     constexpr int OW = HD / TA_PARTS;                         // O columns per thread
+    static_assert(W == 32, "a thread reads its scores with one 32-column load");
     float m_ref = -INFINITY, l = 0.f;
     bool ok = true;
-    for (int j = 0; j < nb; ++j) {
+    for (int j = 0; j < np; ++j) {
       if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, give_up)) {
         ok = false;
         break;
       }
       tc_fence_after();
       float s[W];
-      tmem_ld16(lane_addr + (j & 1) * TA_BN + half * W, s);
+      tmem_ld32(lane_addr + (j & 1) * TA_BN + part * W, s);
       tmem_wait_ld();
       tc_fence_before();
-      mbar_arrive(&s_empty[j & 1]);                           // the S buffer may be overwritten
-      const int j0 = (kb_lo + j) * TA_BN + half * W;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_empty[j & 1]);            // the S buffer may be overwritten
+      const int j0 = (kt_lo + 2 * j) * TA_KT + part * W;
       const bool edge = (j0 + W - 1 > i) || (j0 + W > len) || (a.window > 0 && i - j0 >= a.window);
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -234,16 +245,18 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         s[c] = v;
         mx4[c & 3] = fmaxf(mx4[c & 3], v);
       }
-      // the row's maximum over both halves
+      // the row's maximum over the parts
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      mx_s[j & 1][half][row] = mx;
-      mbar_arrive(&x_full);
+      mx_s[j & 1][part][row] = __float2bfloat16_ru(mx);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&x_full);
       if (!mbar_wait(&x_full, j & 1, give_up)) {
         ok = false;
         break;
       }
+      mx = -INFINITY;
 #pragma unroll
-      for (int h = 0; h < TA_PARTS; ++h) mx = fmaxf(mx, mx_s[j & 1][h][row]);
+      for (int h = 0; h < TA_PARTS; ++h) mx = fmaxf(mx, __bfloat162float(mx_s[j & 1][h][row]));
       // the reference maximum moves only when it has to
       float corr = 1.f;
       if (mx > m_ref + TA_RESCALE || m_ref == -INFINITY) {
@@ -273,42 +286,46 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll 1
         for (int c0 = 0; c0 < OW; c0 += 32) {
           float o[32];
-          tmem_ld32(lane_addr + O_COL + half * OW + c0, o);
+          tmem_ld32(lane_addr + O_COL + part * OW + c0, o);
           tmem_wait_ld();
 #pragma unroll
           for (int c = 0; c < 32; ++c) o[c] *= corr;
-          tmem_st32(lane_addr + O_COL + half * OW + c0, o);
+          tmem_st32(lane_addr + O_COL + part * OW + c0, o);
         }
         tmem_wait_st();
       }
-      // P half row into the swizzled [128 x 128 B] tile: 16-byte piece c lands at piece c ^ (row & 7)
-      unsigned char* prow = p_s + row * 128;
+      // The thread's 32 keys are half a row of the swizzled [128 x 128 B] tile of their 64-key half:
+      // 16-byte piece c of the row lands at piece c ^ (row & 7)
+      unsigned char* prow = p_s + (part >> 1) * P_SUB + row * 128;
 #pragma unroll
       for (int c = 0; c < W / 8; ++c)
-        *reinterpret_cast<uint4*>(prow + (((half * (W / 8) + c) ^ (row & 7)) << 4)) =
+        *reinterpret_cast<uint4*>(prow + ((((part & 1) * (W / 8) + c) ^ (row & 7)) << 4)) =
             make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA
       tc_fence_before();
-      mbar_arrive(&p_full);
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&p_full);
     }
-    // ---- epilogue: O / l -> bfloat16 (l is the sum of both halves' sums)
-    if (ok && nb > 0) ok = mbar_wait(&o_full, 0, give_up);
-    l_s[half][row] = l;
-    if (ok && nb > 0) {
-      mbar_arrive(&x_full);
-      ok = mbar_wait(&x_full, nb & 1, give_up);
+    // ---- epilogue: O / l -> bfloat16 (l is the sum of the parts' sums)
+    if (ok && np > 0) ok = mbar_wait(&o_full, 0, give_up);
+    float* l_s = reinterpret_cast<float*>(p_s);               // [part][row]: the P tiles are free once O is complete
+    if (ok && np > 0) {
+      l_s[part * TA_BM + row] = l;
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&x_full);
+      ok = mbar_wait(&x_full, np & 1, give_up);
     }
-    if (ok && nb > 0) {
+    if (ok && np > 0) {
       tc_fence_after();
       float lt = 0.f;
 #pragma unroll
-      for (int h = 0; h < TA_PARTS; ++h) lt += l_s[h][row];
+      for (int h = 0; h < TA_PARTS; ++h) lt += l_s[h * TA_BM + row];
       const float inv = lt > 0.f ? 1.f / lt : 0.f;
-      __nv_bfloat16* dst = a.out + (size_t)(row0 + i) * a.out_stride + (size_t)head * HD + half * OW;
+      __nv_bfloat16* dst = a.out + (size_t)(row0 + i) * a.out_stride + (size_t)head * HD + part * OW;
 #pragma unroll 1
       for (int c0 = 0; c0 < OW; c0 += 32) {
         float o[32];
-        tmem_ld32(lane_addr + O_COL + half * OW + c0, o);
+        tmem_ld32(lane_addr + O_COL + part * OW + c0, o);
         tmem_wait_ld();
         if (i < len) {
 #pragma unroll
@@ -336,7 +353,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 template <int HD>
 int launch_ta(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TaArgs& a, int n_seqs,
               int max_len, cudaStream_t stream) {
-  constexpr int smem = TA_BM * HD * 2 + 4 * TA_BN * HD * 2 + TA_BM * TA_BN * 2 + 1024;
+  constexpr int smem = TA_BM * HD * 2 + TA_BN * HD * 2 + 2 * TA_KT * HD * 2 + TA_BM * TA_BN * 2;  // Q, K pair, two V tiles, P
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
@@ -372,9 +389,9 @@ AF_EXPORT int af_attn_prefill_tc(void* out, long long out_stride, const void* q,
   CUtensorMap mq, mk, mv;
   int rc = af_make_map_bf16(&mq, q, n_tokens, (long long)nq * hd, q_stride, TA_BM);
   if (rc) return rc;
-  rc = af_make_map_bf16(&mk, k, n_tokens, (long long)nkv * hd, k_stride, TA_BN);
+  rc = af_make_map_bf16(&mk, k, n_tokens, (long long)nkv * hd, k_stride, TA_KT);
   if (rc) return rc;
-  rc = af_make_map_bf16(&mv, v, n_tokens, (long long)nkv * hd, v_stride, TA_BN);
+  rc = af_make_map_bf16(&mv, v, n_tokens, (long long)nkv * hd, v_stride, TA_KT);
   if (rc) return rc;
   TaArgs a{(__nv_bfloat16*)out, out_stride, seq_starts, nq, nkv, scale, cap, window, err};
   if (hd == 128) return launch_ta<128>(mq, mk, mv, a, n_seqs, max_len, stream);
