@@ -9,10 +9,14 @@
 //               two S buffers so that the next pair's scores are computed
 //               while this pair's softmax runs.  (An mma costs some 70 cycles
 //               whatever its N, so few wide instructions beat many narrow ones.)
-//   softmax     sixteen warps, four threads a query row (32 keys each):
-//               tcgen05.ld of their part of the S row, scale, softcap, mask,
-//               running maximum (shared through shared memory) and sum in 32
-//               bits; P is rounded to bfloat16 and written to swizzled shared memory
+//   softmax     two groups of eight warps, one for each 64-key half of a step,
+//               two threads a query row in each (32 keys a thread): tcgen05.ld
+//               of their part of the S row, scale, softcap, mask, maximum and
+//               sum in 32 bits; P is rounded to bfloat16 and written to
+//               swizzled shared memory.  The halves are steps of the online
+//               softmax in turn: a group takes the running maximum that the
+//               other group published for the half before, so that one
+//               group's exponentials and stores overlap the other's maxima.
 //   O += P V    tcgen05.mma, P K-major, the V tiles MN-major as TMA wrote them,
 //               O (128 x head_dim, float) in TMEM for the whole block
 // The running maximum only moves when it grows by more than 8 (in base-2
@@ -31,8 +35,9 @@ namespace {
 constexpr int TA_BM = 128;  // query rows per block
 constexpr int TA_KT = 64;   // keys per TMA tile (a 128-byte swizzled row holds 64 of P's keys, too)
 constexpr int TA_BN = 128;  // keys per step: one S product, two tiles
-constexpr int TA_PARTS = 4;      // threads per query row in the softmax (32 keys each)
-constexpr int TA_THREADS = (2 + 4 * TA_PARTS + 2) * 32;
+constexpr int TA_PARTS = 2;      // threads per query row in a softmax group (32 keys each)
+constexpr int TA_SM_WARPS = 2 * 4 * TA_PARTS;   // softmax warps: two groups
+constexpr int TA_THREADS = (2 + TA_SM_WARPS + 2) * 32;
 constexpr float TA_LOG2E = 1.4426950408889634f;
 constexpr float TA_RESCALE = 8.f;  // the maximum moves only when it grows by more than this
 
@@ -77,10 +82,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   unsigned char* k_s = q_s + Q_BYTES;                // [sub-tile][128 keys of the pair][128 B]
   unsigned char* v_s = k_s + K_BYTES;                // [tile slot 0, 1][sub-tile][64 keys][128 B]
   unsigned char* p_s = v_s + 2 * V_BYTES;            // [64-key half][128 rows][128 B]
-  __shared__ uint64_t q_full, k_full, k_empty, v_full[2], v_empty[2], s_full[2], s_empty[2], p_full, p_empty, o_full,
-      x_full;
-  // the parts' maxima of a row, rounded up to bfloat16 (the reference maximum may sit a little above the true one)
-  __shared__ __nv_bfloat16 mx_s[2][TA_PARTS][TA_BM];
+  __shared__ uint64_t q_full, k_full, k_empty, v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2], p_empty[2],
+      o_full, x_full[2], m_ready[2], l_full;
+  // the parts' maxima of a row [group][step parity][part][row] and the running maximum that a group
+  // publishes [group][row]; rounded up to bfloat16 (the reference maximum may sit a little above the true one)
+  __shared__ __nv_bfloat16 mx_s[2][2][TA_PARTS][TA_BM];
+  __shared__ __nv_bfloat16 mref_s[2][TA_BM];
   __shared__ uint32_t tmem_base_s;
   __shared__ int give_up_s;
   volatile int* give_up = &give_up_s;
@@ -98,11 +105,13 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
       mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], 4 * TA_PARTS);  // one arrival a softmax warp
+      mbar_init(&s_empty[s], TA_SM_WARPS);   // one arrival a softmax warp
+      mbar_init(&p_full[s], 4 * TA_PARTS);   // the warps of one group
+      mbar_init(&x_full[s], 4 * TA_PARTS);
+      mbar_init(&m_ready[s], 4 * TA_PARTS);
+      mbar_init(&p_empty[s], 1);
     }
-    mbar_init(&p_full, 4 * TA_PARTS);
-    mbar_init(&x_full, 4 * TA_PARTS);
-    mbar_init(&p_empty, 1);
+    mbar_init(&l_full, TA_SM_WARPS);
     mbar_init(&o_full, 1);
     give_up_s = 0;
     mbar_fence_init();
@@ -148,7 +157,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       if (*give_up) grace_period();
     }
-  } else if (warp == 2 + 4 * TA_PARTS) {
+  } else if (warp == 2 + TA_SM_WARPS) {
     if (lane == 0 && active) {
       for (int t = 0; t < 2 * np; ++t) {
         const int s = t & 1;
@@ -178,17 +187,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         umma_commit(&k_empty);             // the pair of K tiles is consumed
       }
     }
-  } else if (warp == 3 + 4 * TA_PARTS) {
+  } else if (warp == 3 + TA_SM_WARPS) {
     // ---- O += P(j) V(j), issued by a thread of its own: the tensor pipe takes the
     // instructions of both issuing threads as they come
     if (lane == 0 && active) {
       bool ok = true;
       for (int j = 0; j < np && ok; ++j) {
-        ok = mbar_wait(&p_full, j & 1, give_up);
 #pragma unroll
         for (int h = 0; h < 2 && ok; ++h) {
           const int t = 2 * j + h;
-          ok = mbar_wait(&v_full[t & 1], (t >> 1) & 1, give_up);
+          ok = mbar_wait(&p_full[h], j & 1, give_up) && mbar_wait(&v_full[t & 1], (t >> 1) & 1, give_up);
           if (!ok) break;
           tc_fence_after();
           // P K-major [128 x 64 keys], V MN-major [64 keys x HD]
@@ -199,25 +207,27 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             umma_f16(tmem + O_COL, umma_desc(pt) + 2 * kk, umma_desc_mn(vt + kk * 2048, V_SUB), IDESC_O,
                      (t > 0 || kk > 0) ? 1u : 0u);
           umma_commit(&v_empty[t & 1]);    // the V tile is consumed
+          umma_commit(&p_empty[h]);        // this half's P is consumed, O updated
         }
-        if (ok) umma_commit(&p_empty);     // P consumed, O updated
       }
       if (ok) umma_commit(&o_full);
     }
-  } else if (active && warp < 2 + 4 * TA_PARTS) {
-    // ---- softmax warps: a thread owns a part (32 keys) of a query row's scores; the warps
-    // w, w + 4, ... share the rows of TMEM lane quarter w % 4
+  } else if (active && warp < 2 + TA_SM_WARPS) {
+    // ---- softmax warps.  Group g (warps 2 + 8 g ..) owns the keys [64 g, 64 g + 64) of every step; in a
+    // group a thread owns 32 keys of a query row; the warps w, w + 4, ... share the rows of TMEM lane
+    // quarter w % 4.  The half-steps (j, 0), (j, 1), (j + 1, 0), ... are the steps of the online softmax.
     const int quarter = warp & 3;
-    const int part = (warp - 2) >> 2;
+    const int grp = (warp - 2) >> 3;
+    const int part = ((warp - 2) >> 2) & 1;
     const int row = quarter * 32 + lane;
     const int i = m0 + row;                                   // this thread's query position
     const uint32_t lane_addr = tmem + ((uint32_t)(quarter * 32) << 16);
     const float cs = a.cap > 0.f ? a.scale / a.cap : a.scale * TA_LOG2E;
     const float cap2 = a.cap * TA_LOG2E;
-    constexpr int W = TA_BN / TA_PARTS;                       // scores per thread and step
-    constexpr int OW = HD / TA_PARTS;                         // O columns per thread
+    constexpr int W = TA_KT / TA_PARTS;                       // scores per thread and step
     static_assert(W == 32, "a thread reads its scores with one 32-column load");
-    float m_ref = -INFINITY, l = 0.f;
+    constexpr int RW = HD / TA_PARTS;                         // O columns a thread rescales (its group alone)
+    float m_known = -INFINITY, l = 0.f;                       // this thread's sum is relative to m_known
     bool ok = true;
     for (int j = 0; j < np; ++j) {
       if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, give_up)) {
@@ -226,12 +236,12 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       }
       tc_fence_after();
       float s[W];
-      tmem_ld32(lane_addr + (j & 1) * TA_BN + part * W, s);
+      tmem_ld32(lane_addr + (j & 1) * TA_BN + grp * TA_KT + part * W, s);
       tmem_wait_ld();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(&s_empty[j & 1]);            // the S buffer may be overwritten
-      const int j0 = (kt_lo + 2 * j) * TA_KT + part * W;
+      const int j0 = (kt_lo + 2 * j + grp) * TA_KT + part * W;
       const bool edge = (j0 + W - 1 > i) || (j0 + W > len) || (a.window > 0 && i - j0 >= a.window);
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
@@ -245,26 +255,32 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         s[c] = v;
         mx4[c & 3] = fmaxf(mx4[c & 3], v);
       }
-      // the row's maximum over the parts
+      // the row's maximum over this half's parts
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      mx_s[j & 1][part][row] = __float2bfloat16_ru(mx);
+      mx_s[grp][j & 1][part][row] = __float2bfloat16_ru(mx);
       __syncwarp();
-      if (lane == 0) mbar_arrive(&x_full);
-      if (!mbar_wait(&x_full, j & 1, give_up)) {
+      if (lane == 0) mbar_arrive(&x_full[grp]);
+      if (!mbar_wait(&x_full[grp], j & 1, give_up)) {
         ok = false;
         break;
       }
-      mx = -INFINITY;
-#pragma unroll
-      for (int h = 0; h < TA_PARTS; ++h) mx = fmaxf(mx, __bfloat162float(mx_s[j & 1][h][row]));
-      // the reference maximum moves only when it has to
-      float corr = 1.f;
-      if (mx > m_ref + TA_RESCALE || m_ref == -INFINITY) {
-        const float m_new = fmaxf(m_ref, mx);
-        corr = m_ref == -INFINITY ? 0.f : ta_exp2(m_ref - m_new);
-        m_ref = m_new;
+      mx = fmaxf(__bfloat162float(mx_s[grp][j & 1][0][row]), __bfloat162float(mx_s[grp][j & 1][1][row]));
+      // the running maximum after the half-step before this one, published by the other group
+      float m_prev = -INFINITY;
+      if (grp == 1 || j > 0) {
+        if (!mbar_wait(&m_ready[grp ^ 1], grp == 1 ? (j & 1) : ((j - 1) & 1), give_up)) {
+          ok = false;
+          break;
+        }
+        m_prev = __bfloat162float(mref_s[grp ^ 1][row]);
       }
-      const float ref = m_ref == -INFINITY ? 0.f : m_ref;
+      // it moves only when it has to
+      float m_new = m_prev;
+      if (mx > m_prev + TA_RESCALE || m_prev == -INFINITY) m_new = fmaxf(m_prev, mx);
+      if (part == 0) mref_s[grp][row] = __float2bfloat16_ru(m_new);   // (exact: both are bfloat16 values)
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&m_ready[grp]);              // read the other group's, wrote ours
+      const float ref = m_new == -INFINITY ? 0.f : m_new;
       float sum4[4] = {0.f, 0.f, 0.f, 0.f};
       uint32_t packed[W / 2];
 #pragma unroll
@@ -275,57 +291,72 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
         sum4[(c >> 1) & 3] += __low2float(pb) + __high2float(pb);
         packed[c / 2] = *reinterpret_cast<uint32_t*>(&pb);
       }
-      l = l * corr + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
-      // P(j-1) V(j-1) must be done before O is rescaled and P's memory reused
-      if (j > 0 && !mbar_wait(&p_empty, (j - 1) & 1, give_up)) {
+      l = l * (m_known == -INFINITY ? 0.f : ta_exp2(m_known - ref)) + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      m_known = m_new;
+      // This group's P of the step before must be consumed before its memory is reused.  (Waited for
+      // here, ahead of the wait below: it also pins the phase that wait looks at.)
+      if (j > 0 && !mbar_wait(&p_empty[grp], (j - 1) & 1, give_up)) {
         ok = false;
         break;
       }
-      tc_fence_after();
-      if (j > 0 && __any_sync(0xffffffffu, corr != 1.f)) {
+      const bool first = j == 0 && grp == 0;                  // no product has been issued yet
+      if (!first && __any_sync(0xffffffffu, m_new != m_prev)) {
+        // O is rescaled by this group alone, once the product of the half-step before is complete
+        // (products complete in order; the next one waits for this group's P)
+        if (!mbar_wait(&p_empty[grp ^ 1], grp == 1 ? (j & 1) : ((j - 1) & 1), give_up)) {
+          ok = false;
+          break;
+        }
+        tc_fence_after();
+        const float corr = m_prev == -INFINITY ? 0.f : ta_exp2(m_prev - ref);
 #pragma unroll 1
-        for (int c0 = 0; c0 < OW; c0 += 32) {
+        for (int c0 = 0; c0 < RW; c0 += 32) {
           float o[32];
-          tmem_ld32(lane_addr + O_COL + part * OW + c0, o);
+          tmem_ld32(lane_addr + O_COL + part * RW + c0, o);
           tmem_wait_ld();
 #pragma unroll
           for (int c = 0; c < 32; ++c) o[c] *= corr;
-          tmem_st32(lane_addr + O_COL + part * OW + c0, o);
+          tmem_st32(lane_addr + O_COL + part * RW + c0, o);
         }
         tmem_wait_st();
       }
-      // The thread's 32 keys are half a row of the swizzled [128 x 128 B] tile of their 64-key half:
+      // The thread's 32 keys are half a row of the swizzled [128 x 128 B] tile of its group's 64 keys:
       // 16-byte piece c of the row lands at piece c ^ (row & 7)
-      unsigned char* prow = p_s + (part >> 1) * P_SUB + row * 128;
+      unsigned char* prow = p_s + grp * P_SUB + row * 128;
 #pragma unroll
       for (int c = 0; c < W / 8; ++c)
-        *reinterpret_cast<uint4*>(prow + ((((part & 1) * (W / 8) + c) ^ (row & 7)) << 4)) =
+        *reinterpret_cast<uint4*>(prow + (((part * (W / 8) + c) ^ (row & 7)) << 4)) =
             make_uint4(packed[4 * c], packed[4 * c + 1], packed[4 * c + 2], packed[4 * c + 3]);
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");  // generic writes -> visible to the MMA
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&p_full);
+      if (lane == 0) mbar_arrive(&p_full[grp]);
     }
-    // ---- epilogue: O / l -> bfloat16 (l is the sum of the parts' sums)
+    // ---- epilogue: O / l -> bfloat16; l is the sum of the four threads' sums, brought to the last maximum
+    if (ok && np > 0) ok = mbar_wait(&m_ready[1], (np - 1) & 1, give_up);
     if (ok && np > 0) ok = mbar_wait(&o_full, 0, give_up);
-    float* l_s = reinterpret_cast<float*>(p_s);               // [part][row]: the P tiles are free once O is complete
+    float* l_s = reinterpret_cast<float*>(p_s);               // [thread of the row][row]: P is free once O is complete
+    const int quad = grp * TA_PARTS + part;                   // this thread among the row's four
     if (ok && np > 0) {
-      l_s[part * TA_BM + row] = l;
+      const float m_fin = __bfloat162float(mref_s[1][row]);
+      l_s[quad * TA_BM + row] =
+          (m_known == -INFINITY || m_fin == -INFINITY) ? 0.f : l * ta_exp2(m_known - m_fin);
       __syncwarp();
-      if (lane == 0) mbar_arrive(&x_full);
-      ok = mbar_wait(&x_full, np & 1, give_up);
+      if (lane == 0) mbar_arrive(&l_full);
+      ok = mbar_wait(&l_full, 0, give_up);
     }
     if (ok && np > 0) {
       tc_fence_after();
+      constexpr int OW = HD / (2 * TA_PARTS);                 // O columns a thread writes out
       float lt = 0.f;
 #pragma unroll
-      for (int h = 0; h < TA_PARTS; ++h) lt += l_s[h * TA_BM + row];
+      for (int h = 0; h < 2 * TA_PARTS; ++h) lt += l_s[h * TA_BM + row];
       const float inv = lt > 0.f ? 1.f / lt : 0.f;
-      __nv_bfloat16* dst = a.out + (size_t)(row0 + i) * a.out_stride + (size_t)head * HD + part * OW;
+      __nv_bfloat16* dst = a.out + (size_t)(row0 + i) * a.out_stride + (size_t)head * HD + quad * OW;
 #pragma unroll 1
       for (int c0 = 0; c0 < OW; c0 += 32) {
         float o[32];
-        tmem_ld32(lane_addr + O_COL + part * OW + c0, o);
+        tmem_ld32(lane_addr + O_COL + quad * OW + c0, o);
         tmem_wait_ld();
         if (i < len) {
 #pragma unroll
