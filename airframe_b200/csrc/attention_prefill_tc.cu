@@ -4,11 +4,14 @@
 //
 // A block owns 128 query rows of one head of one sequence (the 128 TMEM lanes)
 // and walks the keys 128 at a time (two TMA tiles of 64 keys).
-//   S = Q K^T   tcgen05.mma with N = 128: Q and the pair of K tiles K-major in
-//               128-byte swizzled shared memory, S (128 x 128, float) in TMEM,
-//               two S buffers so that the next pair's scores are computed
-//               while this pair's softmax runs.  (An mma costs some 70 cycles
-//               whatever its N, so few wide instructions beat many narrow ones.)
+//   S = Q K^T   tcgen05.mma with N = 128.  Q is copied once from shared memory
+//               into TMEM and is the product's A operand there (operands in
+//               shared memory are fetched at some 64 bytes a cycle, and Q would
+//               be half of the score product's operand bytes, step after
+//               step); the pair of K tiles is K-major in 128-byte swizzled
+//               shared memory, two buffers (the second is where Q arrived); S
+//               (128 x 128, float) in TMEM.  The next pair's scores are computed
+//               as soon as the softmax warps hold this pair's in registers.
 //   softmax     two groups of eight warps, one for each 64-key half of a step,
 //               two threads a query row in each (32 keys a thread): tcgen05.ld
 //               of their part of the S row, scale, softcap, mask, maximum and
@@ -72,18 +75,20 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
   constexpr int V_SUB = TA_KT * 128;                 // one V sub-tile [64 keys][128 B]
   constexpr int Q_BYTES = SUB * Q_SUB, K_BYTES = SUB * K_SUB, V_BYTES = SUB * V_SUB;
   constexpr int P_SUB = TA_BM * 128;                 // P of 64 keys [128 rows][128 B]
-  constexpr int O_COL = 2 * TA_BN;                   // TMEM columns: S0 [0,128) S1 [128,256) O [256, 256 + HD)
+  constexpr int Q_COL = TA_BN;                       // TMEM columns: S [0,128) Q [128, 128 + HD/2) O [256, 256 + HD)
+  constexpr int O_COL = 256;
   constexpr int COLS = 512;
   constexpr uint32_t IDESC_S = umma_idesc(TA_BN, false);
   constexpr uint32_t IDESC_O = umma_idesc(HD, true);
 
   extern __shared__ __align__(1024) unsigned char sm[];
-  unsigned char* q_s = sm;
-  unsigned char* k_s = q_s + Q_BYTES;                // [sub-tile][128 keys of the pair][128 B]
-  unsigned char* v_s = k_s + K_BYTES;                // [tile slot 0, 1][sub-tile][64 keys][128 B]
+  static_assert(Q_BYTES == K_BYTES, "Q's memory becomes the second K buffer");
+  unsigned char* q_s = sm;                           // Q until it is in TMEM, then K buffer 0
+  unsigned char* k_s = sm;                           // [buffer][sub-tile][128 keys of the pair][128 B]: pair j in buffer (j + 1) % 2
+  unsigned char* v_s = k_s + 2 * K_BYTES;            // [tile slot 0, 1][sub-tile][64 keys][128 B]
   unsigned char* p_s = v_s + 2 * V_BYTES;            // [64-key half][128 rows][128 B]
-  __shared__ uint64_t q_full, k_full, k_empty, v_full[2], v_empty[2], s_full[2], s_empty[2], p_full[2], p_empty[2],
-      o_full, x_full[2], m_ready[2], l_full;
+  __shared__ uint64_t q_full, q_moved, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full, s_empty, p_full[2],
+      p_empty[2], o_full, x_full[2], m_ready[2], l_full;
   // the parts' maxima of a row [group][step parity][part][row] and the running maximum that a group
   // publishes [group][row]; rounded up to bfloat16 (the reference maximum may sit a little above the true one)
   __shared__ __nv_bfloat16 mx_s[2][2][TA_PARTS][TA_BM];
@@ -99,13 +104,14 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 
   if (threadIdx.x == 0) {
     mbar_init(&q_full, 1);
-    mbar_init(&k_full, 1);
-    mbar_init(&k_empty, 1);
+    mbar_init(&q_moved, TA_SM_WARPS);        // one arrival a softmax warp
+    mbar_init(&s_full, 1);
+    mbar_init(&s_empty, TA_SM_WARPS);
     for (int s = 0; s < 2; ++s) {
+      mbar_init(&k_full[s], 1);
+      mbar_init(&k_empty[s], 1);
       mbar_init(&v_full[s], 1);
       mbar_init(&v_empty[s], 1);
-      mbar_init(&s_full[s], 1);
-      mbar_init(&s_empty[s], TA_SM_WARPS);   // one arrival a softmax warp
       mbar_init(&p_full[s], 4 * TA_PARTS);   // the warps of one group
       mbar_init(&x_full[s], 4 * TA_PARTS);
       mbar_init(&m_ready[s], 4 * TA_PARTS);
@@ -145,14 +151,17 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #pragma unroll
       for (int c = 0; c < SUB; ++c) tma_load_2d(q_s + c * Q_SUB, &map_q, head * HD + c * 64, row0 + m0, &q_full);
       for (int j = 0; j < np; ++j) {
-        if (!mbar_wait(&k_empty, (j & 1) ^ 1, give_up)) break;
-        mbar_expect_tx(&k_full, K_BYTES);
+        const int b = (j + 1) & 1;           // pair 0 goes beside Q, pair 1 where Q was
+        if (j == 1 && !mbar_wait(&q_moved, 0, give_up)) break;
+        if (j >= 2 && !mbar_wait(&k_empty[b], ((j >> 1) & 1) ^ 1, give_up)) break;
+        unsigned char* kb = k_s + (size_t)b * K_BYTES;
+        mbar_expect_tx(&k_full[b], K_BYTES);
         const int r = row0 + (kt_lo + 2 * j) * TA_KT;
 #pragma unroll
         for (int c = 0; c < SUB; ++c) {
           // rows past the packed rows read as zeros; rows of the next sequence are masked by position
-          tma_load_2d(k_s + c * K_SUB, &map_k, kvh * HD + c * 64, r, &k_full);
-          tma_load_2d(k_s + c * K_SUB + TA_KT * 128, &map_k, kvh * HD + c * 64, r + TA_KT, &k_full);
+          tma_load_2d(kb + c * K_SUB, &map_k, kvh * HD + c * 64, r, &k_full[b]);
+          tma_load_2d(kb + c * K_SUB + TA_KT * 128, &map_k, kvh * HD + c * 64, r + TA_KT, &k_full[b]);
         }
       }
       if (*give_up) grace_period();
@@ -172,19 +181,21 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     }
   } else if (warp == 1) {
     if (lane == 0 && active) {
-      bool ok = mbar_wait(&q_full, 0, give_up);
-      for (int j = 0; j < np && ok; ++j) {  // S(j) = Q K(j)^T into S buffer j % 2, ahead of the softmax
-        ok = mbar_wait(&k_full, j & 1, give_up);
-        if (ok && j >= 2) ok = mbar_wait(&s_empty[j & 1], ((j >> 1) & 1) ^ 1, give_up);
+      bool ok = mbar_wait(&q_moved, 0, give_up);
+      for (int j = 0; j < np && ok; ++j) {  // S(j) = Q K(j)^T
+        const int b = (j + 1) & 1;
+        ok = mbar_wait(&k_full[b], (j >> 1) & 1, give_up);
+        // once the softmax warps hold the scores of the step before in registers
+        if (ok && j >= 1) ok = mbar_wait(&s_empty, (j - 1) & 1, give_up);
         if (!ok) break;
         tc_fence_after();
-        const uint32_t kt = smem_u32(k_s), qt = smem_u32(q_s);
+        const uint32_t kt = smem_u32(k_s + (size_t)b * K_BYTES);
 #pragma unroll
         for (int ks = 0; ks < HD / 16; ++ks)
-          umma_f16(tmem + (j & 1) * TA_BN, umma_desc(qt + (ks >> 2) * Q_SUB) + 2 * (ks & 3),
-                   umma_desc(kt + (ks >> 2) * K_SUB) + 2 * (ks & 3), IDESC_S, ks > 0 ? 1u : 0u);
-        umma_commit(&s_full[j & 1]);
-        umma_commit(&k_empty);             // the pair of K tiles is consumed
+          umma_f16_ts(tmem, tmem + Q_COL + ks * 8, umma_desc(kt + (ks >> 2) * K_SUB) + 2 * (ks & 3), IDESC_S,
+                      ks > 0 ? 1u : 0u);
+        umma_commit(&s_full);
+        umma_commit(&k_empty[b]);          // the pair of K tiles is consumed
       }
     }
   } else if (warp == 3 + TA_SM_WARPS) {
@@ -228,19 +239,43 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     static_assert(W == 32, "a thread reads its scores with one 32-column load");
     constexpr int RW = HD / TA_PARTS;                         // O columns a thread rescales (its group alone)
     float m_known = -INFINITY, l = 0.f;                       // this thread's sum is relative to m_known
-    bool ok = true;
-    for (int j = 0; j < np; ++j) {
-      if (!mbar_wait(&s_full[j & 1], (j >> 1) & 1, give_up)) {
+    const int quad = grp * TA_PARTS + part;                   // this thread among the row's four
+    bool ok = mbar_wait(&q_full, 0, give_up);
+    if (ok) {
+      // ---- Q from shared memory into TMEM: this thread's quarter of its row, 16-byte pieces
+      // un-swizzled, two elements a column
+      constexpr int QW = HD / 8;                              // 32-bit columns per thread
+      const int e0 = quad * (HD / 4);                         // first element of this thread's share
+      const unsigned char* qrow = q_s + (e0 >> 6) * Q_SUB + row * 128;
+      const int p0 = (e0 & 63) >> 3;                          // first 16-byte piece within the 128-byte row
+      uint32_t w[QW];
+#pragma unroll
+      for (int c = 0; c < QW / 4; ++c) {
+        const uint4 v = *reinterpret_cast<const uint4*>(qrow + (((p0 + c) ^ (row & 7)) << 4));
+        w[4 * c] = v.x, w[4 * c + 1] = v.y, w[4 * c + 2] = v.z, w[4 * c + 3] = v.w;
+      }
+      if constexpr (QW == 32) {
+        tmem_st32(lane_addr + Q_COL + quad * QW, reinterpret_cast<const float*>(w));
+      } else {
+        tmem_st16(lane_addr + Q_COL + quad * QW, reinterpret_cast<const float*>(w));
+      }
+      tmem_wait_st();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&q_moved);
+    }
+    for (int j = 0; j < np && ok; ++j) {
+      if (!mbar_wait(&s_full, j & 1, give_up)) {
         ok = false;
         break;
       }
       tc_fence_after();
       float s[W];
-      tmem_ld32(lane_addr + (j & 1) * TA_BN + grp * TA_KT + part * W, s);
+      tmem_ld32(lane_addr + grp * TA_KT + part * W, s);
       tmem_wait_ld();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&s_empty[j & 1]);            // the S buffer may be overwritten
+      if (lane == 0) mbar_arrive(&s_empty);                   // the S buffer may be overwritten
       const int j0 = (kt_lo + 2 * j + grp) * TA_KT + part * W;
       const bool edge = (j0 + W - 1 > i) || (j0 + W > len) || (a.window > 0 && i - j0 >= a.window);
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -336,7 +371,6 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     if (ok && np > 0) ok = mbar_wait(&m_ready[1], (np - 1) & 1, give_up);
     if (ok && np > 0) ok = mbar_wait(&o_full, 0, give_up);
     float* l_s = reinterpret_cast<float*>(p_s);               // [thread of the row][row]: P is free once O is complete
-    const int quad = grp * TA_PARTS + part;                   // this thread among the row's four
     if (ok && np > 0) {
       const float m_fin = __bfloat162float(mref_s[1][row]);
       l_s[quad * TA_BM + row] =
@@ -384,7 +418,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 template <int HD>
 int launch_ta(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TaArgs& a, int n_seqs,
               int max_len, cudaStream_t stream) {
-  constexpr int smem = TA_BM * HD * 2 + TA_BN * HD * 2 + 2 * TA_KT * HD * 2 + TA_BM * TA_BN * 2;  // Q, K pair, two V tiles, P
+  constexpr int smem = 2 * TA_BN * HD * 2 + 2 * TA_KT * HD * 2 + TA_BM * TA_BN * 2;  // two K pairs (Q arrives in one), two V tiles, P
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
