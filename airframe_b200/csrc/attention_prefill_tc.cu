@@ -278,18 +278,24 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       if (lane == 0) mbar_arrive(&s_empty);                   // the S buffer may be overwritten
       const int j0 = (kt_lo + 2 * j + grp) * TA_KT + part * W;
       const bool edge = (j0 + W - 1 > i) || (j0 + W > len) || (a.window > 0 && i - j0 >= a.window);
+      // (the tests on the cap and on the edge stand outside the loops: inside, the compiler kept
+      // them as a branch per element)
+      if (a.cap > 0.f) {
+#pragma unroll
+        for (int c = 0; c < W; ++c) s[c] = cap2 * ta_tanh(s[c] * cs);
+      } else {
+#pragma unroll
+        for (int c = 0; c < W; ++c) s[c] *= cs;
+      }
+      if (edge) {
+        const int hi = min(i, len - 1) - j0;                       // last visible key of this part
+        const int lo = a.window > 0 ? i - a.window + 1 - j0 : -1;  // first visible key
+#pragma unroll
+        for (int c = 0; c < W; ++c) s[c] = (c <= hi && c >= lo) ? s[c] : -INFINITY;
+      }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-      for (int c = 0; c < W; ++c) {
-        float v = s[c] * cs;
-        if (a.cap > 0.f) v = cap2 * ta_tanh(v);
-        if (edge) {
-          const int jj = j0 + c;
-          v = (jj <= i && jj < len && (a.window <= 0 || i - jj < a.window)) ? v : -INFINITY;
-        }
-        s[c] = v;
-        mx4[c & 3] = fmaxf(mx4[c & 3], v);
-      }
+      for (int c = 0; c < W; ++c) mx4[c & 3] = fmaxf(mx4[c & 3], s[c]);
       // the row's maximum over this half's parts
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       mx_s[grp][j & 1][part][row] = __float2bfloat16_ru(mx);

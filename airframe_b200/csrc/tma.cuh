@@ -21,6 +21,9 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes)
                : "memory");
 }
+#ifndef AF_TRY_WAIT_HINT_NS
+#define AF_TRY_WAIT_HINT_NS 200000
+#endif
 // One try: the thread is suspended by the hardware until the phase completes
 // or a time limit (the hint, in nanoseconds) passes; it wakes as soon as the
 // barrier flips, without polling traffic.
@@ -31,7 +34,7 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
       "selp.u32 %0, 1, 0, p;\n\t}"
       : "=r"(ok)
-      : "r"(smem_u32(bar)), "r"(parity), "r"(200000u)
+      : "r"(smem_u32(bar)), "r"(parity), "r"((uint32_t)AF_TRY_WAIT_HINT_NS)
       : "memory");
   return ok != 0;
 }
