@@ -237,14 +237,24 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     // ---- scale, softcap, mask, online softmax (base 2)
     const int j0 = (pp_begin + i) * AF_PAGE + wq * 16;
     float new_max[2] = {mx[0], mx[1]};
+    // (the test on the cap stands outside the loops: inside it stays a branch per score)
+    if (a.cap > 0.f) {
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[n][e] = cap2 * fast_tanh(sc[n][e] * cs);
+    } else {
+#pragma unroll
+      for (int n = 0; n < 2; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) sc[n][e] *= cs;
+    }
 #pragma unroll
     for (int n = 0; n < 2; ++n) {
 #pragma unroll
       for (int e = 0; e < 4; ++e) {
-        float v = sc[n][e] * cs;
-        if (a.cap > 0.f) v = cap2 * fast_tanh(v);
         const int j = j0 + n * 8 + 2 * t + (e & 1);
-        v = (j >= lo && j <= pos) ? v : -INFINITY;
+        const float v = (j >= lo && j <= pos) ? sc[n][e] : -INFINITY;
         sc[n][e] = v;
         new_max[e >> 1] = fmaxf(new_max[e >> 1], v);
       }

@@ -178,22 +178,34 @@ attn_prefill_mma_kernel(PrefillArgs a) {
     const bool edge = (j0 + PF_BN - 1 > m0 + warp * 16) || (j0 + PF_BN > len) ||
                       (a.window > 0 && (m0 + warp * 16 + 15) - j0 >= a.window);
     float new_max[2] = {mx[0], mx[1]};
+    // (the tests on the cap and on the edge stand outside the loops: inside they stay a branch per score)
+    if (a.cap > 0.f) {
 #pragma unroll
-    for (int n = 0; n < SNT; ++n) {
+      for (int n = 0; n < SNT; ++n)
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float v = s[n][e] * cs;
-        if (a.cap > 0.f) v = cap2 * pf_tanh(v);
-        if (edge) {
+        for (int e = 0; e < 4; ++e) s[n][e] = cap2 * pf_tanh(s[n][e] * cs);
+    } else {
+#pragma unroll
+      for (int n = 0; n < SNT; ++n)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) s[n][e] *= cs;
+    }
+    if (edge) {
+#pragma unroll
+      for (int n = 0; n < SNT; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
           const int j = j0 + n * 8 + 2 * t + (e & 1);
           const int i = qrow[e >> 1];
           const bool ok = j <= i && j < len && (a.window <= 0 || i - j < a.window);
-          v = ok ? v : -INFINITY;
+          s[n][e] = ok ? s[n][e] : -INFINITY;
         }
-        s[n][e] = v;
-        new_max[e >> 1] = fmaxf(new_max[e >> 1], v);
       }
     }
+#pragma unroll
+    for (int n = 0; n < SNT; ++n)
+#pragma unroll
+      for (int e = 0; e < 4; ++e) new_max[e >> 1] = fmaxf(new_max[e >> 1], s[n][e]);
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
       new_max[r] = fmaxf(new_max[r], __shfl_xor_sync(0xffffffffu, new_max[r], 1));
