@@ -132,8 +132,13 @@ class Engine:
         positions = list(lens) + [0] * (Bp - B)
         slots = [e.slot for e in entries] + [-1] * (Bp - B)
         len_after = [n + 1 for n in lens] + [0] * (Bp - B)
-        host = torch.tensor(tokens + positions + slots + len_after, dtype=torch.int32).pin_memory()
+        # two pinned staging buffers in turn: one may still be in flight when the next step is laid out
+        k = g["turn"] = g["turn"] ^ 1
+        host, sent = g["host"][k], g["sent"][k]
+        sent.synchronize()
+        host.copy_(torch.tensor(tokens + positions + slots + len_after, dtype=torch.int32))
         g["dynamic"].copy_(host, non_blocking=True)
+        sent.record()
         g["graph"].replay()
         self.replayed_launches += g["launches"]
         return g["logits"][:B]
@@ -164,4 +169,6 @@ class Engine:
         with torch.cuda.graph(graph):
             logits = self.model.forward(batch, self.cache)
         return {"graph": graph, "dynamic": dynamic, "logits": logits, "batch": batch, "fixed": fixed,
-                "launches": kernels.launch_count() - n0}
+                "launches": kernels.launch_count() - n0, "turn": 0,
+                "host": [torch.empty(4 * Bp, dtype=torch.int32).pin_memory() for _ in range(2)],
+                "sent": [torch.cuda.Event() for _ in range(2)]}

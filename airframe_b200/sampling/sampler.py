@@ -32,6 +32,7 @@ class Sampler:
     def __init__(self, vocab_size: int, device):
         self.vocab_size = vocab_size
         self.device = torch.device(device)
+        self._host_out = None
 
     def new_state(self, params: SamplingParams, request_index: int) -> SequenceSamplingState:
         return SequenceSamplingState(params, request_index)
@@ -44,23 +45,32 @@ class Sampler:
         if R != len(states):
             raise ValueError("one sampling state per row of logits")
         use_penalty = params.repetition_penalty != 1.0
-        n_extra = (RECENT_WINDOW + 1) if use_penalty else 0
-        host = torch.zeros(R, 1 + n_extra, dtype=torch.int32)
-        hv = host.view(torch.float32)
-        for r, st in enumerate(states):
-            if not params.greedy:
-                hv[r, 0] = st.rng.next_f32()
-            if use_penalty:
-                host[r, 1] = len(st.recent)
-                if st.recent:
-                    host[r, 2:2 + len(st.recent)] = torch.tensor(st.recent, dtype=torch.int32)
-        dev = host.pin_memory().to(self.device, non_blocking=True)
+        dev = None
+        if use_penalty or not params.greedy:
+            # what the kernel needs from the host: the draw and the recent tokens of every row
+            n_extra = (RECENT_WINDOW + 1) if use_penalty else 0
+            host = torch.zeros(R, 1 + n_extra, dtype=torch.int32)
+            hv = host.view(torch.float32)
+            for r, st in enumerate(states):
+                if not params.greedy:
+                    hv[r, 0] = st.rng.next_f32()
+                if use_penalty:
+                    host[r, 1] = len(st.recent)
+                    if st.recent:
+                        host[r, 2:2 + len(st.recent)] = torch.tensor(st.recent, dtype=torch.int32)
+            dev = host.pin_memory().to(self.device, non_blocking=True)
         out = torch.empty(R, dtype=torch.int32, device=self.device)
         kernels.sample(logits, out, params.temperature, params.top_p, params.repetition_penalty,
                        uniform=dev.view(torch.float32)[:, 0] if not params.greedy else None,
                        recent=dev[:, 2:] if use_penalty else None,
                        n_recent=dev[:, 1] if use_penalty else None)
-        tokens = out.tolist()
+        # the tokens come back through pinned memory kept for the purpose
+        if self._host_out is None or self._host_out.numel() < R:
+            self._host_out = torch.empty(max(R, 64), dtype=torch.int32).pin_memory()
+        back = self._host_out[:R]
+        back.copy_(out, non_blocking=True)
+        torch.cuda.current_stream(self.device).synchronize()
+        tokens = back.tolist()
         for st, t in zip(states, tokens):
             st.note(t)
         return tokens
