@@ -131,10 +131,11 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
     yr[i] = from_f32<TY>(row[i] * inv2 * (offset + w_next[i]));
 }
 
-// The same for rows of up to 4096 elements with hidden % 4 == 0: one thread per
-// four elements, every load issued before the first reduction (the rows are
-// short; what costs is the chain of memory latencies, not the bytes).
-template <typename TA, typename TY>
+// The same for rows of up to 8192 elements with hidden % 4 == 0: a thread owns NV groups of four
+// elements (group v of thread t at element 4 (t + v * threads)), every load issued before the first
+// reduction.  Few rows (decode): NV = 1, many threads per row, what costs is the chain of memory
+// latencies; many rows (prefill): NV = 2, smaller blocks, more rows in flight on an SM.
+template <typename TA, typename TY, int NV>
 __global__ void __launch_bounds__(1024)
 add_rmsnorm_row_kernel(float* __restrict__ x, const TA* __restrict__ a, int n_parts, size_t part_stride,
                        const float* __restrict__ w_post, TY* __restrict__ y, const float* __restrict__ w_next,
@@ -143,11 +144,15 @@ add_rmsnorm_row_kernel(float* __restrict__ x, const TA* __restrict__ a, int n_pa
   pdl_wait();
   __shared__ float scratch[33];
   const int r = blockIdx.x;
-  const int i = threadIdx.x * 4;
-  const bool on = i < hidden;
-  float av[4] = {0.f, 0.f, 0.f, 0.f}, xv[4] = {0.f, 0.f, 0.f, 0.f}, wp[4] = {0.f, 0.f, 0.f, 0.f},
-        wn[4] = {0.f, 0.f, 0.f, 0.f};
-  if (on) {
+  float av[NV][4], xv[NV][4], wp[NV][4], wn[NV][4];
+  bool on[NV];
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int i = (threadIdx.x + v * blockDim.x) * 4;
+    on[v] = i < hidden;
+#pragma unroll
+    for (int u = 0; u < 4; ++u) av[v][u] = xv[v][u] = wp[v][u] = wn[v][u] = 0.f;
+    if (!on[v]) continue;
     const size_t at = (size_t)r * hidden + i;
     if constexpr (sizeof(TA) == 4) {
       const float* ap = reinterpret_cast<const float*>(a) + at;
@@ -159,45 +164,60 @@ add_rmsnorm_row_kernel(float* __restrict__ x, const TA* __restrict__ a, int n_pa
                                   : make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll
         for (int u = 0; u < 8; ++u) {
-          av[0] += t[u].x;
-          av[1] += t[u].y;
-          av[2] += t[u].z;
-          av[3] += t[u].w;
+          av[v][0] += t[u].x;
+          av[v][1] += t[u].y;
+          av[v][2] += t[u].z;
+          av[v][3] += t[u].w;
         }
       }
     } else {
       const uint2 raw = *reinterpret_cast<const uint2*>(a + at);
-      av[0] = __uint_as_float(raw.x << 16);
-      av[1] = __uint_as_float(raw.x & 0xffff0000u);
-      av[2] = __uint_as_float(raw.y << 16);
-      av[3] = __uint_as_float(raw.y & 0xffff0000u);
+      av[v][0] = __uint_as_float(raw.x << 16);
+      av[v][1] = __uint_as_float(raw.x & 0xffff0000u);
+      av[v][2] = __uint_as_float(raw.y << 16);
+      av[v][3] = __uint_as_float(raw.y & 0xffff0000u);
     }
     const float4 xt = *reinterpret_cast<const float4*>(x + at);
     const float4 pt = *reinterpret_cast<const float4*>(w_post + i);
-    xv[0] = xt.x, xv[1] = xt.y, xv[2] = xt.z, xv[3] = xt.w;
-    wp[0] = pt.x, wp[1] = pt.y, wp[2] = pt.z, wp[3] = pt.w;
+    xv[v][0] = xt.x, xv[v][1] = xt.y, xv[v][2] = xt.z, xv[v][3] = xt.w;
+    wp[v][0] = pt.x, wp[v][1] = pt.y, wp[v][2] = pt.z, wp[v][3] = pt.w;
     if (y != nullptr) {
       const float4 nt = *reinterpret_cast<const float4*>(w_next + i);
-      wn[0] = nt.x, wn[1] = nt.y, wn[2] = nt.z, wn[3] = nt.w;
+      wn[v][0] = nt.x, wn[v][1] = nt.y, wn[v][2] = nt.z, wn[v][3] = nt.w;
     }
   }
-  float ss = av[0] * av[0] + av[1] * av[1] + av[2] * av[2] + av[3] * av[3];
+  float ss = 0.f;
+#pragma unroll
+  for (int v = 0; v < NV; ++v) ss += av[v][0] * av[v][0] + av[v][1] * av[v][1] + av[v][2] * av[v][2] + av[v][3] * av[v][3];
   ss = block_sum(ss, scratch);
   const float inv = rsqrtf(ss / (float)hidden + eps_post);
   float ss2 = 0.f;
 #pragma unroll
-  for (int u = 0; u < 4; ++u) {
-    xv[u] = xv[u] + av[u] * inv * (offset + wp[u]);
-    ss2 += on ? xv[u] * xv[u] : 0.f;
+  for (int v = 0; v < NV; ++v) {
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      xv[v][u] = xv[v][u] + av[v][u] * inv * (offset + wp[v][u]);
+      ss2 += on[v] ? xv[v][u] * xv[v][u] : 0.f;
+    }
+    if (on[v])
+      *reinterpret_cast<float4*>(x + (size_t)r * hidden + (threadIdx.x + v * blockDim.x) * 4) =
+          make_float4(xv[v][0], xv[v][1], xv[v][2], xv[v][3]);
   }
-  if (on) *reinterpret_cast<float4*>(x + (size_t)r * hidden + i) = make_float4(xv[0], xv[1], xv[2], xv[3]);
   if (y == nullptr) return;
   ss2 = block_sum(ss2, scratch);
   const float inv2 = rsqrtf(ss2 / (float)hidden + eps_next);
-  if (on) {
-    TY* yr = y + (size_t)r * hidden + i;
 #pragma unroll
-    for (int u = 0; u < 4; ++u) yr[u] = from_f32<TY>(xv[u] * inv2 * (offset + wn[u]));
+  for (int v = 0; v < NV; ++v) {
+    if (!on[v]) continue;
+    TY* yr = y + (size_t)r * hidden + (threadIdx.x + v * blockDim.x) * 4;
+    if constexpr (sizeof(TY) == 2) {
+      __nv_bfloat162 lo = __floats2bfloat162_rn(xv[v][0] * inv2 * (offset + wn[v][0]), xv[v][1] * inv2 * (offset + wn[v][1]));
+      __nv_bfloat162 hi = __floats2bfloat162_rn(xv[v][2] * inv2 * (offset + wn[v][2]), xv[v][3] * inv2 * (offset + wn[v][3]));
+      *reinterpret_cast<uint2*>(yr) = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+    } else {
+#pragma unroll
+      for (int u = 0; u < 4; ++u) yr[u] = from_f32<TY>(xv[v][u] * inv2 * (offset + wn[v][u]));
+    }
   }
 }
 
@@ -211,12 +231,18 @@ AF_EXPORT int af_add_rmsnorm(float* x, const void* a, int a_dtype, int n_parts, 
   AF_REQUIRE(n_parts == 1 || a_dtype == AF_F32, "af_add_rmsnorm: partial sums must be float");
   const bool aligned = (((uintptr_t)x | (uintptr_t)a | (uintptr_t)w_post | (uintptr_t)w_next) & 15) == 0 &&
                        (part_stride % 4 == 0);
-  if (hidden % 4 == 0 && hidden <= 4096 && aligned) {
-    const int threads = ((hidden / 4 + 31) / 32) * 32;
-#define LAUNCH_ROW(TA, TY)                                                                           \
-  af_launch(add_rmsnorm_row_kernel<TA, TY>, dim3(n_rows), dim3(threads), 0, stream, x, (const TA*)a, n_parts,           \
-                                                                 (size_t)part_stride, w_post, (TY*)y, \
-                                                                 w_next, hidden, eps_post, eps_next, offset)
+  if (hidden % 4 == 0 && hidden <= 8192 && aligned && ((uintptr_t)y & 7) == 0) {
+    const int nv = (n_rows >= 256 && hidden >= 1024) || hidden > 4096 ? 2 : 1;
+    const int threads = ((hidden / (4 * nv) + 31) / 32) * 32;
+#define LAUNCH_ROW(TA, TY)                                                                                  \
+  do {                                                                                                      \
+    if (nv == 2)                                                                                            \
+      af_launch(add_rmsnorm_row_kernel<TA, TY, 2>, dim3(n_rows), dim3(threads), 0, stream, x, (const TA*)a, \
+                n_parts, (size_t)part_stride, w_post, (TY*)y, w_next, hidden, eps_post, eps_next, offset);  \
+    else                                                                                                    \
+      af_launch(add_rmsnorm_row_kernel<TA, TY, 1>, dim3(n_rows), dim3(threads), 0, stream, x, (const TA*)a, \
+                n_parts, (size_t)part_stride, w_post, (TY*)y, w_next, hidden, eps_post, eps_next, offset);  \
+  } while (0)
     AF_DISPATCH_DTYPE(a_dtype, TA, AF_DISPATCH_DTYPE(y_dtype, TY, LAUNCH_ROW(TA, TY)));
 #undef LAUNCH_ROW
     AF_CHECK_LAUNCH("af_add_rmsnorm");
