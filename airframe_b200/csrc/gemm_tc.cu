@@ -1,10 +1,12 @@
 // bfloat16 matrix product on the 5th-generation tensor cores:
 //   out[M, N] = x[M, K] * w[N, K]^T      (tokens x features, weights [out, in])
 //
-// The weight is the tcgen05 "A" operand: a CTA owns 128 output features (the
-// 128 TMEM lanes) and BN tokens (TMEM columns), so the same kernel serves
-// decode (BN = 16 .. 64, bandwidth bound: the weights stream through once) and
-// prefill (BN = 256).  Both operands are K-major, staged by TMA into 128-byte
+// The weight is the tcgen05 "A" operand: a tile is 128 output features (the
+// 128 TMEM lanes) by BN tokens (TMEM columns), so the same kernel serves
+// decode (BN = 16 .. 64, bandwidth bound: the weights stream through once, a
+// block per tile) and prefill (BN = 256: one block per SM walks the tiles,
+// token tile fastest so that blocks running together share weight tiles in L2,
+// and fetches the next tile's operands while this tile's accumulators are read back).  Both operands are K-major, staged by TMA into 128-byte
 // swizzled shared memory; one elected thread issues tcgen05.mma with the
 // accumulator in TMEM; four warps read it back with tcgen05.ld for the epilogue.
 //
@@ -63,6 +65,8 @@ struct TcArgs {
   long long part_stride;  // elements between split-K partial results
   int M, N, K;            // N: output features (GATED: half the weight's rows)
   int kb_per_split;       // K blocks handled by one z-slice
+  int tiles_w, tiles_m;   // tiles along the weight rows and along the tokens; a block walks the tiles
+                          // blockIdx.x, blockIdx.x + gridDim.x, ... (token tile fastest)
   float cap;
   int* err;
 };
@@ -81,17 +85,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 
   extern __shared__ unsigned char smem_raw[];
   unsigned char* tiles = (unsigned char*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
-  __shared__ uint64_t full[STAGES], empty[STAGES], acc_full;
+  __shared__ uint64_t full[STAGES], empty[STAGES], acc_full, acc_empty;
   __shared__ uint32_t tmem_base_s;
   __shared__ int give_up_s;
   volatile int* give_up = &give_up_s;
 
   pdl_launch_dependents();
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int n0 = blockIdx.x * (TC_BM * NACC), m0 = blockIdx.y * BN;  // first weight row, first token
   const int total_kb = (a.K + TC_BK - 1) / TC_BK;
   const int kb0 = blockIdx.z * a.kb_per_split;
   const int kb_count = min(a.kb_per_split, total_kb - kb0);
+  const int n_tiles = a.tiles_w * a.tiles_m;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -99,6 +103,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_init(&empty[s], 1);
     }
     mbar_init(&acc_full, 1);
+    mbar_init(&acc_empty, 4);   // one arrival an epilogue warp
     give_up_s = 0;
     mbar_fence_init();
   }
@@ -112,78 +117,104 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
   const uint32_t tmem_base = tmem_base_s;
 
+  // A block walks its tiles one after another; the K blocks of all its tiles form one sequence
+  // (`it`) through the ring of stages, so the producer is already fetching the next tile while
+  // the accumulators of this one are read back.
   if (warp == 0) {
     if (lane == 0) {
-      // The weights do not depend on earlier kernels: the first stages' weight
-      // tiles are fetched before the wait for them, the activations after it.
-      const int early = min(STAGES, kb_count);
-      for (int kb = 0; kb < early; ++kb) {
-        unsigned char* st = tiles + (size_t)kb * STAGE_BYTES;
-        mbar_expect_tx(&full[kb], STAGE_BYTES);
-        const int k = (kb0 + kb) * TC_BK;
+      int it = 0;
+      bool first = true;
+      for (int tile = blockIdx.x; tile < n_tiles && !*give_up; tile += gridDim.x) {
+        const int n0 = (tile / a.tiles_m) * (TC_BM * NACC), m0 = (tile % a.tiles_m) * BN;
+        int kb = 0;
+        if (first) {
+          // The weights do not depend on earlier kernels: the first stages' weight
+          // tiles are fetched before the wait for them, the activations after it.
+          const int early = min(STAGES, kb_count);
+          for (; kb < early; ++kb) {
+            unsigned char* st = tiles + (size_t)kb * STAGE_BYTES;
+            mbar_expect_tx(&full[kb], STAGE_BYTES);
+            const int k = (kb0 + kb) * TC_BK;
 #pragma unroll
-        for (int acc = 0; acc < NACC; ++acc) tma_load_2d(st + acc * A_BYTES, &map_w, k, n0 + acc * TC_BM, &full[kb]);
-      }
-      pdl_wait();
-      for (int kb = 0; kb < early; ++kb)
-        tma_load_2d(tiles + (size_t)kb * STAGE_BYTES + NACC * A_BYTES, &map_x, (kb0 + kb) * TC_BK, m0, &full[kb]);
-      for (int kb = early; kb < kb_count; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        if (!mbar_wait(&empty[s], ph ^ 1, give_up)) break;
-        unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
-        mbar_expect_tx(&full[s], STAGE_BYTES);
-        const int k = (kb0 + kb) * TC_BK;
+            for (int acc = 0; acc < NACC; ++acc)
+              tma_load_2d(st + acc * A_BYTES, &map_w, k, n0 + acc * TC_BM, &full[kb]);
+          }
+          pdl_wait();
+          for (int e = 0; e < early; ++e)
+            tma_load_2d(tiles + (size_t)e * STAGE_BYTES + NACC * A_BYTES, &map_x, (kb0 + e) * TC_BK, m0, &full[e]);
+          it = early;
+          first = false;
+        }
+        for (; kb < kb_count; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (it >= STAGES && !mbar_wait(&empty[s], ph ^ 1, give_up)) break;
+          unsigned char* st = tiles + (size_t)s * STAGE_BYTES;
+          mbar_expect_tx(&full[s], STAGE_BYTES);
+          const int k = (kb0 + kb) * TC_BK;
 #pragma unroll
-        for (int acc = 0; acc < NACC; ++acc) tma_load_2d(st + acc * A_BYTES, &map_w, k, n0 + acc * TC_BM, &full[s]);
-        tma_load_2d(st + NACC * A_BYTES, &map_x, k, m0, &full[s]);
+          for (int acc = 0; acc < NACC; ++acc) tma_load_2d(st + acc * A_BYTES, &map_w, k, n0 + acc * TC_BM, &full[s]);
+          tma_load_2d(st + NACC * A_BYTES, &map_x, k, m0, &full[s]);
+        }
       }
+      if (first) pdl_wait();
       if (*give_up) grace_period();
     }
   } else if (warp == 1) {
     if (lane == 0) {
       bool ok = true;
-      for (int kb = 0; kb < kb_count && ok; ++kb) {
-        const int s = kb % STAGES;
-        const uint32_t ph = (kb / STAGES) & 1;
-        if (!mbar_wait(&full[s], ph, give_up)) {
+      int it = 0, round = 0;
+      for (int tile = blockIdx.x; tile < n_tiles && ok; tile += gridDim.x, ++round) {
+        // the accumulators are free once the epilogue warps have read the tile before out of them
+        if (round > 0 && !mbar_wait(&acc_empty, (round - 1) & 1, give_up)) {
           ok = false;
           break;
         }
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t st = smem_u32(tiles + (size_t)s * STAGE_BYTES);
-        const uint64_t db = umma_desc(st + NACC * A_BYTES);
+        for (int kb = 0; kb < kb_count; ++kb, ++it) {
+          const int s = it % STAGES;
+          const uint32_t ph = (it / STAGES) & 1;
+          if (!mbar_wait(&full[s], ph, give_up)) {
+            ok = false;
+            break;
+          }
+          asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+          const uint32_t st = smem_u32(tiles + (size_t)s * STAGE_BYTES);
+          const uint64_t db = umma_desc(st + NACC * A_BYTES);
 #pragma unroll
-        for (int k = 0; k < TC_BK / 16; ++k) {
-          const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
+          for (int k = 0; k < TC_BK / 16; ++k) {
+            const uint32_t accum = (kb > 0 || k > 0) ? 1u : 0u;
 #pragma unroll
-          for (int acc = 0; acc < NACC; ++acc)  // 32 bytes of K per step
-            umma_f16(tmem_base + acc * BN, umma_desc(st + acc * A_BYTES) + 2 * k, db + 2 * k, IDESC, accum);
+            for (int acc = 0; acc < NACC; ++acc)  // 32 bytes of K per step
+              umma_f16(tmem_base + acc * BN, umma_desc(st + acc * A_BYTES) + 2 * k, db + 2 * k, IDESC, accum);
+          }
+          umma_commit(&empty[s]);
         }
-        umma_commit(&empty[s]);
+        if (ok) umma_commit(&acc_full);
       }
-      if (ok) umma_commit(&acc_full);
     }
   } else {
     // epilogue: warp w reads TMEM lanes [32 * (w % 4), + 32)
     const int quarter = warp & 3;
     pdl_wait();
-    const bool done = mbar_wait(&acc_full, 0, give_up);
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    if (done) {
+    int round = 0;
+    for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++round) {
+      const int tile_w = tile / a.tiles_m;
+      const int m0 = (tile % a.tiles_m) * BN;
+      if (!mbar_wait(&acc_full, round & 1, give_up)) break;
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       TO* out = reinterpret_cast<TO*>(a.out) + (size_t)blockIdx.z * a.part_stride;
       const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
       // CW columns (tokens) per round: the TMEM loads of a round are issued
       // together and waited for once
       constexpr int CW = BN >= 64 ? 64 : BN;
-      int round = 0;
 #pragma unroll 1
       for (int acc = 0; acc < NACC; ++acc) {
         // the output feature of this lane: a weight row, or for GATED the feature whose gate row it is
-        const int tile = blockIdx.x * NACC + acc;
-        const int f = GATED ? tile * 64 + quarter * 16 + (lane & 15) : tile * TC_BM + quarter * 32 + lane;
+        const int wt = tile_w * NACC + acc;
+        const int f = GATED ? wt * 64 + quarter * 16 + (lane & 15) : wt * TC_BM + quarter * 32 + lane;
 #pragma unroll 1
-        for (int c0 = 0; c0 < BN; c0 += CW, ++round) {
+        for (int c0 = 0; c0 < BN; c0 += CW) {
           float v[CW];
           if constexpr (CW >= 32) {
 #pragma unroll
@@ -192,6 +223,12 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             tmem_ld16(lane_base + acc * BN + c0, v);
           }
           asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+          if (acc == NACC - 1 && c0 + CW >= BN) {
+            // everything of this tile is in registers: the next tile's products may start
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty);
+          }
           if (GATED) {
             // Within a warp lanes 0..15 hold gate rows and lanes 16..31 the up rows of the
             // same 16 features.  Each half keeps one half of the round's tokens and gets
@@ -263,15 +300,20 @@ int launch_on(dim3 grid, const CUtensorMap& mw, const CUtensorMap& mx, const TcA
 }
 
 template <int BN, int NACC, int ACT, typename TO>
-int launch(const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, long long n_w_rows, int splits,
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcArgs a, long long n_w_rows, int splits,
            cudaStream_t stream) {
   const long long w_tiles = (n_w_rows + TC_BM - 1) / TC_BM;
-  dim3 grid((unsigned)((w_tiles + NACC - 1) / NACC), (a.M + BN - 1) / BN, splits);
-  const long long blocks = (long long)grid.x * grid.y * grid.z;
+  a.tiles_w = (int)((w_tiles + NACC - 1) / NACC);
+  a.tiles_m = (a.M + BN - 1) / BN;
+  const long long tiles = (long long)a.tiles_w * a.tiles_m;
   if constexpr (BN <= 64 && NACC == 1) {
-    // bound by the weight stream
-    if (blocks > 2 * TC_SMS) return launch_on<BN, NACC, ACT, TO, 2>(grid, mw, mx, a, stream);
+    // bound by the weight stream: a block per tile; many waves of them run two to an SM
+    dim3 grid((unsigned)tiles, 1, splits);
+    if (tiles * splits > 2 * TC_SMS) return launch_on<BN, NACC, ACT, TO, 2>(grid, mw, mx, a, stream);
+    return launch_on<BN, NACC, ACT, TO, 1>(grid, mw, mx, a, stream);
   }
+  // bound by the products: one block per SM walks the tiles
+  dim3 grid((unsigned)(tiles < TC_SMS ? tiles : TC_SMS), 1, splits);
   return launch_on<BN, NACC, ACT, TO, 1>(grid, mw, mx, a, stream);
 }
 
@@ -341,7 +383,7 @@ AF_EXPORT int af_gemm_tc(void* out, int out_dtype, long long ldo, long long part
   rc = af_make_map_bf16(&mx, x, M, K, ldx, bn);
   if (rc) return rc;
   const int N = gated ? (int)(n_w_rows / 2) : (int)n_w_rows;
-  TcArgs a{out, ldo, part_stride, M, N, K, kb_per_split, cap, err};
+  TcArgs a{out, ldo, part_stride, M, N, K, kb_per_split, 0, 0, cap, err};
   if (out_dtype == AF_BF16) return launch_variant<__nv_bfloat16>(n_acc, gated, act, bn, mw, mx, a, n_w_rows, splits, stream);
   return launch_variant<float>(n_acc, gated, act, bn, mw, mx, a, n_w_rows, splits, stream);
 }
