@@ -23,6 +23,8 @@ from typing import Optional
 
 import torch
 
+from .. import transfers
+
 from ..kernels_const import PAGE
 from ..parts.base import KVNeed, StateNeed
 from .pool import CacheFull, IndexPool, PoolError
@@ -96,6 +98,7 @@ class KVGroup:
             rows[:, 0] = torch.tensor(slots, dtype=torch.int32)
             rows[:, 1:] = self.table_host[slots]
             dev = rows.to(self.table.device, non_blocking=True)
+            transfers.count_h2d(rows)
             self.table.index_copy_(0, dev[:, 0].long(), dev[:, 1:])
         self.dirty.clear()
 

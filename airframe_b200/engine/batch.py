@@ -11,6 +11,8 @@ from typing import Optional
 
 import torch
 
+from .. import transfers
+
 
 @dataclass
 class StepEntry:
@@ -71,6 +73,7 @@ def build_batch(entries, lens_before, device, pad_to: int = 0) -> StepBatch:
     if device.type == "cuda":
         host = host.pin_memory()
     dev = host.to(device, non_blocking=True)
+    transfers.count_h2d(host)
     o = 0
 
     def cut(n):

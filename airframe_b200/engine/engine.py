@@ -12,6 +12,8 @@ from typing import Optional
 
 import torch
 
+from .. import transfers
+
 from ..cache import PoolError, SequenceCache
 from .batch import StepBatch, StepEntry, build_batch
 from .model import Model
@@ -138,6 +140,7 @@ class Engine:
         sent.synchronize()
         host.copy_(torch.tensor(tokens + positions + slots + len_after, dtype=torch.int32))
         g["dynamic"].copy_(host, non_blocking=True)
+        transfers.count_h2d(host)
         sent.record()
         g["graph"].replay()
         self.replayed_launches += g["launches"]

@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import torch
 
-from .. import kernels
+from .. import kernels, transfers
 from .params import RECENT_WINDOW, SamplingParams
 from .rng import XorShift64Star
 
@@ -59,6 +59,7 @@ class Sampler:
                     if st.recent:
                         host[r, 2:2 + len(st.recent)] = torch.tensor(st.recent, dtype=torch.int32)
             dev = host.pin_memory().to(self.device, non_blocking=True)
+            transfers.count_h2d(host)
         out = torch.empty(R, dtype=torch.int32, device=self.device)
         kernels.sample(logits, out, params.temperature, params.top_p, params.repetition_penalty,
                        uniform=dev.view(torch.float32)[:, 0] if not params.greedy else None,
@@ -69,6 +70,7 @@ class Sampler:
             self._host_out = torch.empty(max(R, 64), dtype=torch.int32).pin_memory()
         back = self._host_out[:R]
         back.copy_(out, non_blocking=True)
+        transfers.count_d2h(back)
         torch.cuda.current_stream(self.device).synchronize()
         tokens = back.tolist()
         for st, t in zip(states, tokens):
