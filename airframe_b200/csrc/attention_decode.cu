@@ -358,16 +358,50 @@ __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long l
   pdl_wait();
   const int b = blockIdx.x, h = blockIdx.y;
   const size_t p0 = ((size_t)b * nq + h) * n_splits;
+  constexpr int FEW = 8;
+  const int d = threadIdx.x;   // HD >= 128: threads 0..127 take d and d + 128 (HD 256)
+  if (n_splits <= FEW) {
+    // few splits: every load (outputs, maxima, sums) is issued before the first use, one round trip
+    constexpr int PER = HD > 128 ? HD / 128 : 1;
+    float o[FEW][PER], m[FEW], l[FEW];
+#pragma unroll
+    for (int s = 0; s < FEW; ++s) {
+      const bool on = s < n_splits;
+      m[s] = on ? part_ml[(p0 + s) * 2] : -INFINITY;
+      l[s] = on ? part_ml[(p0 + s) * 2 + 1] : 0.f;
+#pragma unroll
+      for (int e = 0; e < PER; ++e) o[s][e] = on && d + e * 128 < HD ? part_o[(p0 + s) * HD + d + e * 128] : 0.f;
+    }
+    float M = -INFINITY;
+#pragma unroll
+    for (int s = 0; s < FEW; ++s) M = fmaxf(M, m[s]);
+    const float ref = M == -INFINITY ? 0.f : M;
+    float L = 0.f, O[PER];
+#pragma unroll
+    for (int e = 0; e < PER; ++e) O[e] = 0.f;
+#pragma unroll
+    for (int s = 0; s < FEW; ++s) {
+      const float f = fast_exp2(m[s] - ref);
+      L += l[s] * f;
+#pragma unroll
+      for (int e = 0; e < PER; ++e) O[e] += o[s][e] * f;
+    }
+    const float inv = L > 0.f ? 1.f / L : 0.f;
+#pragma unroll
+    for (int e = 0; e < PER; ++e)
+      if (d + e * 128 < HD) out[(size_t)b * out_stride + (size_t)h * HD + d + e * 128] = __float2bfloat16_rn(O[e] * inv);
+    return;
+  }
   float M = -INFINITY;
   for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(p0 + s) * 2]);
   const float ref = M == -INFINITY ? 0.f : M;
   float L = 0.f;
   for (int s = 0; s < n_splits; ++s) L += part_ml[(p0 + s) * 2 + 1] * fast_exp2(part_ml[(p0 + s) * 2] - ref);
   const float inv = L > 0.f ? 1.f / L : 0.f;
-  for (int d = threadIdx.x; d < HD; d += blockDim.x) {
+  for (int dd = threadIdx.x; dd < HD; dd += blockDim.x) {
     float O = 0.f;
-    for (int s = 0; s < n_splits; ++s) O += part_o[(p0 + s) * HD + d] * fast_exp2(part_ml[(p0 + s) * 2] - ref);
-    out[(size_t)b * out_stride + (size_t)h * HD + d] = __float2bfloat16_rn(O * inv);
+    for (int s = 0; s < n_splits; ++s) O += part_o[(p0 + s) * HD + dd] * fast_exp2(part_ml[(p0 + s) * 2] - ref);
+    out[(size_t)b * out_stride + (size_t)h * HD + dd] = __float2bfloat16_rn(O * inv);
   }
 }
 

@@ -141,17 +141,30 @@ add_rmsnorm_row_kernel(float* __restrict__ x, const TA* __restrict__ a, int n_pa
                        const float* __restrict__ w_post, TY* __restrict__ y, const float* __restrict__ w_next,
                        int hidden, float eps_post, float eps_next, float offset) {
   pdl_launch_dependents();
-  pdl_wait();
   __shared__ float scratch[33];
   const int r = blockIdx.x;
   float av[NV][4], xv[NV][4], wp[NV][4], wn[NV][4];
   bool on[NV];
+  // the norms' weights do not depend on the kernel in front (and are cold: the step's other
+  // weights have pushed them out of L2): they are asked for before the wait
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
     const int i = (threadIdx.x + v * blockDim.x) * 4;
     on[v] = i < hidden;
 #pragma unroll
     for (int u = 0; u < 4; ++u) av[v][u] = xv[v][u] = wp[v][u] = wn[v][u] = 0.f;
+    if (!on[v]) continue;
+    const float4 pt = *reinterpret_cast<const float4*>(w_post + i);
+    wp[v][0] = pt.x, wp[v][1] = pt.y, wp[v][2] = pt.z, wp[v][3] = pt.w;
+    if (y != nullptr) {
+      const float4 nt = *reinterpret_cast<const float4*>(w_next + i);
+      wn[v][0] = nt.x, wn[v][1] = nt.y, wn[v][2] = nt.z, wn[v][3] = nt.w;
+    }
+  }
+  pdl_wait();
+#pragma unroll
+  for (int v = 0; v < NV; ++v) {
+    const int i = (threadIdx.x + v * blockDim.x) * 4;
     if (!on[v]) continue;
     const size_t at = (size_t)r * hidden + i;
     if constexpr (sizeof(TA) == 4) {
@@ -178,13 +191,7 @@ add_rmsnorm_row_kernel(float* __restrict__ x, const TA* __restrict__ a, int n_pa
       av[v][3] = __uint_as_float(raw.y & 0xffff0000u);
     }
     const float4 xt = *reinterpret_cast<const float4*>(x + at);
-    const float4 pt = *reinterpret_cast<const float4*>(w_post + i);
     xv[v][0] = xt.x, xv[v][1] = xt.y, xv[v][2] = xt.z, xv[v][3] = xt.w;
-    wp[v][0] = pt.x, wp[v][1] = pt.y, wp[v][2] = pt.z, wp[v][3] = pt.w;
-    if (y != nullptr) {
-      const float4 nt = *reinterpret_cast<const float4*>(w_next + i);
-      wn[v][0] = nt.x, wn[v][1] = nt.y, wn[v][2] = nt.z, wn[v][3] = nt.w;
-    }
   }
   float ss = 0.f;
 #pragma unroll
