@@ -37,7 +37,14 @@ GEMMA2_2B = {
     "final_logit_softcapping": 30.0, "max_position_embeddings": 8192, "rms_norm_eps": 1e-6,
     "hidden_activation": "gelu_pytorch_tanh", "tie_word_embeddings": True, "torch_dtype": "bfloat16",
 }
-FULL_LAYERS = 26
+# the other sizes of the family differ in these keys (--sizes 9b / 27b: not the default run)
+SIZES = {
+    "2b": {},
+    "9b": {"num_hidden_layers": 42, "hidden_size": 3584, "num_attention_heads": 16, "num_key_value_heads": 8,
+           "intermediate_size": 14336},
+    "27b": {"num_hidden_layers": 46, "hidden_size": 4608, "num_attention_heads": 32, "num_key_value_heads": 16,
+            "head_dim": 128, "intermediate_size": 36864, "query_pre_attn_scalar": 144},
+}
 PROMPT_LEN = 2048
 CONTEXT = 8192
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0}
@@ -143,8 +150,10 @@ def run_ours(args) -> dict:
     from airframe_b200.engine import GpuRuntime, StepEntry
     from airframe_b200.sampling import Sampler, SamplingParams
 
-    n_layers = args.layers or FULL_LAYERS
-    cfg_dict = dict(GEMMA2_2B, num_hidden_layers=n_layers)
+    full = dict(GEMMA2_2B, **SIZES[args.sizes])
+    full_layers = full["num_hidden_layers"]
+    n_layers = args.layers or full_layers
+    cfg_dict = dict(full, num_hidden_layers=n_layers)
     cfg = config_from_dict(cfg_dict)
     B, K, W = args.batch, args.steps, max(args.warmup, 3)
     pk = peaks()
@@ -256,15 +265,17 @@ def run_ours(args) -> dict:
            "d2h_bytes_per_step": round((moved[1][1] - moved[0][1]) / (n_new - 1))}
 
     return {
-        "metric": "Gemma-2 2B bf16 decode tokens/s at batch 8 (2,048-token prompts)",
+        "metric": f"Gemma-2 {args.sizes.upper()} bf16 decode tokens/s at batch {B} (2,048-token prompts)",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights N(0, 0.02), uniform random token ids",
-        "config": {"model": "gemma-2-2b sizes", "global_batch": B, "seq_len": PROMPT_LEN, "context": CONTEXT,
-                   "parallelism": "single-gpu", "layers": n_layers, "layers_full": FULL_LAYERS,
-                   "hidden": 2304, "heads": 8, "kv_heads": 4, "head_dim": 256, "intermediate": 9216,
-                   "vocab": 256000, "sliding_window": 4096, "sampling": "greedy on device",
-                   "l2": "inputs larger than L2 (weights 5.2 GB per step)"},
+        "config": {"model": f"gemma-2-{args.sizes} sizes", "global_batch": B, "seq_len": PROMPT_LEN, "context": CONTEXT,
+                   "parallelism": "single-gpu", "layers": n_layers, "layers_full": full_layers,
+                   "hidden": cfg_dict["hidden_size"], "heads": cfg_dict["num_attention_heads"],
+                   "kv_heads": cfg_dict["num_key_value_heads"], "head_dim": cfg_dict["head_dim"],
+                   "intermediate": cfg_dict["intermediate_size"], "vocab": cfg_dict["vocab_size"],
+                   "sliding_window": cfg_dict["sliding_window"], "sampling": "greedy on device",
+                   "l2": f"inputs larger than L2 (weights {model_bytes(cfg_dict, n_layers) / 1e9:.1f} GB per step)"},
         "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
         "gpu_launches": launches, "clocks": clock_info, "impl": "ours",
     }
@@ -279,6 +290,7 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--sizes", default="2b", choices=sorted(SIZES), help="layer sizes of this Gemma-2 model")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
