@@ -46,7 +46,7 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const flo
   const int t = blockIdx.x, head = blockIdx.y;
   const int pos = positions[t];
   T* row = qkv + (size_t)t * row_stride + (size_t)head * hd;
-  const float* pr = parts ? parts + (size_t)t * (nq + 2 * nkv) * hd + (size_t)head * hd : nullptr;
+  const float* pr = parts ? parts + (size_t)t * (nq + 2 * nkv) * hd + (size_t)head * hd : nullptr;  // (read after the wait)
   const int half = rot_dim / 2;
   // where this head's row goes in the cache (k and v heads only)
   T* dst = nullptr;
@@ -66,6 +66,8 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const flo
   float s0 = 0.f, c0 = 1.f;
   if (rotate && threadIdx.x < half) sincosf((float)pos * inv_freq[threadIdx.x], &s0, &c0);
   pdl_wait();
+  pr = pdl_fresh(pr);
+  row = pdl_fresh(row);
   // rotary pairs
   for (int p = threadIdx.x; p < half; p += blockDim.x) {
     const int i0 = pairing == AF_PAIR_HALF ? p : 2 * p;
@@ -107,7 +109,8 @@ rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, long long row_stride, con
                       __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
                       const int* __restrict__ page_table, int max_pages, int ring_rows) {
   pdl_launch_dependents();
-  pdl_wait();
+  // (positions, slots, lengths, page table and frequencies are inputs of the step: the row's place in
+  // the cache and the sines and cosines are worked out before the wait for the kernel in front)
   const int t = blockIdx.x;
   const int pos = positions[t];
   __nv_bfloat16* row = qkv + (size_t)t * row_stride;
@@ -127,6 +130,17 @@ rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, long long row_stride, con
       store = true;
     }
   }
+  // a thread's pieces all have the same place in their heads when the block's size is a multiple of
+  // the pieces of a head (it is for head sizes up to 512 that divide so): its 8 pairs' angles are fixed
+  const bool fixed_c = blockDim.x % per_head == 0;
+  float sn0[8], cs0[8];
+  if (fixed_c) {
+    const int c = threadIdx.x % per_head;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) sincosf((float)pos * inv_freq[c * 8 + e], &sn0[e], &cs0[e]);
+  }
+  pdl_wait();
+  row = pdl_fresh(row);
   for (int i = threadIdx.x; i < n_heads * per_head; i += blockDim.x) {
     const int head = i / per_head, c = i - head * per_head;
     __nv_bfloat16* x = row + (size_t)head * hd + c * 8;
@@ -142,8 +156,8 @@ rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, long long row_stride, con
         float ra[2], rb[2];
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
-          float sn, cs;
-          sincosf((float)pos * inv_freq[c * 8 + 2 * j + e], &sn, &cs);
+          float sn = sn0[2 * j + e], cs = cs0[2 * j + e];
+          if (!fixed_c) sincosf((float)pos * inv_freq[c * 8 + 2 * j + e], &sn, &cs);
           ra[e] = a[e] * cs - b[e] * sn;
           rb[e] = b[e] * cs + a[e] * sn;
         }

@@ -58,6 +58,15 @@ extern int g_af_pdl;
 
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+// A kernel that does work before pdl_wait() passes every pointer to memory that earlier kernels
+// write through this after the wait.  Loads through a `const __restrict__` pointer may be moved by
+// the compiler across the wait (it takes the memory for unchanging while the kernel runs); it
+// cannot move them across the point where the pointer's value becomes known.
+template <typename T>
+__device__ __forceinline__ T* pdl_fresh(T* p) {
+  asm volatile("" : "+l"(p)::"memory");
+  return p;
+}
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t af_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,

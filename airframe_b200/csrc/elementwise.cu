@@ -162,6 +162,8 @@ add_rmsnorm_row_kernel(float* __restrict__ x, const TA* __restrict__ a, int n_pa
     }
   }
   pdl_wait();
+  a = pdl_fresh(a);
+  x = pdl_fresh(x);
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
     const int i = (threadIdx.x + v * blockDim.x) * 4;
