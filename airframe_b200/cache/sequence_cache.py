@@ -69,6 +69,13 @@ class KVGroup:
     def pages_missing(self, slot: int, new_len: int) -> int:
         return max(0, pages_for(self.rows_held(new_len)) - len(self.held[slot]))
 
+    def room(self, slot: int) -> int:
+        """Tokens the sequence may hold before this group needs another page."""
+        held = len(self.held[slot])
+        if self.ring_rows and held * PAGE >= self.ring_rows:
+            return 1 << 62                  # the ring is complete: it never grows again
+        return held * PAGE
+
     def grow(self, slot: int, new_len: int) -> None:
         n = self.pages_missing(slot, new_len)
         if n == 0:
@@ -145,6 +152,7 @@ class SequenceCache:
         self.n_slots = self.total_pages if max_sequences is None else min(max_sequences, self.total_pages)
         self.slots = IndexPool(self.n_slots, "cache slot")
         self.lens = [0] * self.n_slots
+        self.room = [0] * self.n_slots       # tokens that fit into the pages a slot holds in every group
         self.device = device
         self.dtype = dtype
         self.groups: dict = {}
@@ -188,6 +196,7 @@ class SequenceCache:
     def take_slot(self) -> int:
         slot = self.slots.take()
         self.lens[slot] = 0
+        self.room[slot] = 0
         for st in self.states.values():
             if st is not None:
                 st[slot].zero_()
@@ -199,6 +208,7 @@ class SequenceCache:
         for g in self.groups.values():
             g.release(slot)
         self.lens[slot] = 0
+        self.room[slot] = 0
         self.slots.give_back(slot)
 
     def length(self, slot: int) -> int:
@@ -217,14 +227,20 @@ class SequenceCache:
             if new_len > self.max_context:
                 raise ContextOverflow(f"sequence in slot {slot} would hold {new_len} tokens; "
                                       f"the cache is built for {self.max_context}")
+        # most steps add a token that still fits into the pages held: nothing to take
+        short = {s: n for s, n in growth.items() if n > self.room[s]}
+        if not short:
+            return
         for g in self.groups.values():
-            want = sum(g.pages_missing(s, n) for s, n in growth.items())
+            want = sum(g.pages_missing(s, n) for s, n in short.items())
             if want > g.pages.n_free:
                 raise CacheFull(f"{want} more cache pages wanted, {g.pages.n_free} of {g.n_pages} free "
                                 f"(window {g.need.window})")
         for g in self.groups.values():
-            for s, n in growth.items():
+            for s, n in short.items():
                 g.grow(s, n)
+        for s in short:
+            self.room[s] = min((g.room(s) for g in self.groups.values()), default=self.max_context)
 
     def commit(self, growth: dict) -> None:
         for slot, new_len in growth.items():

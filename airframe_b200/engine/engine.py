@@ -130,15 +130,20 @@ class Engine:
         if g is None:
             g = self._capture(Bp)
             self._graphs[Bp] = g
-        tokens = [e.tokens[0] for e in entries] + [0] * (Bp - B)
-        positions = list(lens) + [0] * (Bp - B)
-        slots = [e.slot for e in entries] + [-1] * (Bp - B)
-        len_after = [n + 1 for n in lens] + [0] * (Bp - B)
         # two pinned staging buffers in turn: one may still be in flight when the next step is laid out
         k = g["turn"] = g["turn"] ^ 1
         host, sent = g["host"][k], g["sent"][k]
         sent.synchronize()
-        host.copy_(torch.tensor(tokens + positions + slots + len_after, dtype=torch.int32))
+        lay = g["host_np"][k]                 # [tokens | positions | slots | len_after], Bp each
+        lay[:B] = [e.tokens[0] for e in entries]
+        lay[Bp:Bp + B] = lens
+        lay[2 * Bp:2 * Bp + B] = [e.slot for e in entries]
+        lay[3 * Bp:3 * Bp + B] = [n + 1 for n in lens]
+        if B < Bp:
+            lay[B:Bp] = 0
+            lay[Bp + B:2 * Bp] = 0
+            lay[2 * Bp + B:3 * Bp] = -1
+            lay[3 * Bp + B:] = 0
         g["dynamic"].copy_(host, non_blocking=True)
         transfers.count_h2d(host)
         sent.record()
@@ -173,5 +178,6 @@ class Engine:
             logits = self.model.forward(batch, self.cache)
         return {"graph": graph, "dynamic": dynamic, "logits": logits, "batch": batch, "fixed": fixed,
                 "launches": kernels.launch_count() - n0, "turn": 0,
-                "host": [torch.empty(4 * Bp, dtype=torch.int32).pin_memory() for _ in range(2)],
+                "host": (hosts := [torch.empty(4 * Bp, dtype=torch.int32).pin_memory() for _ in range(2)]),
+                "host_np": [h.numpy() for h in hosts],
                 "sent": [torch.cuda.Event() for _ in range(2)]}
