@@ -133,3 +133,20 @@ def test_schedule_validation():
     s.schedule = [ScheduleEntry(0), ScheduleEntry(1, cache_from=0), ScheduleEntry(0, cache_from=1)]
     with pytest.raises(ConfigError, match="keeps none"):
         s.validate()
+
+
+def test_presets_parse_and_match_the_test_configurations():
+    from airframe_b200.config import config_from_dict
+    from airframe_b200.config.presets import PRESETS, preset
+    import tiny
+    for name in PRESETS:
+        cfg = config_from_dict(preset(name))
+        cfg.model_spec().validate()
+    for name, ref in (("tinyA", tiny.TINY_A), ("tinyB", tiny.TINY_B)):
+        p = preset(name)
+        for key in ("num_hidden_layers", "hidden_size", "num_attention_heads", "num_key_value_heads", "head_dim",
+                    "intermediate_size", "vocab_size", "rope_theta", "sliding_window", "query_pre_attn_scalar",
+                    "attn_logit_softcapping", "final_logit_softcapping", "max_position_embeddings"):
+            assert p[key] == ref[key], (name, key)
+    with pytest.raises(KeyError, match="unknown preset"):
+        preset("70b")

@@ -88,6 +88,24 @@ def test_command_line(case):
     assert out.returncode != 0 and "LIBSHIMMY_MODEL_PATH" in out.stderr
 
 
+def test_command_line_with_a_named_random_model():
+    """--random NAME runs a preset with seeded weights; two --prompt-ids make a batch; the same seed gives
+    the same tokens."""
+    runs = []
+    for _ in range(2):
+        out = subprocess.run([sys.executable, str(ROOT / "bin" / "simple_flight"), "--random", "tinyB", "--seed", "5",
+                              "--dtype", "fp32", "--max-tokens", "6", "--ignore-eos", "--prompt-ids", "3,4,5",
+                              "--prompt-ids", "9"], capture_output=True, text=True, timeout=600)
+        assert out.returncode == 0, out.stderr
+        lines = [ln for ln in out.stdout.splitlines() if ln.startswith("Output ")]
+        assert len(lines) == 2 and all(len(ln.split(":")[1].split()) == 6 for ln in lines)
+        runs.append(lines)
+    assert runs[0] == runs[1]
+    out = subprocess.run([sys.executable, str(ROOT / "bin" / "simple_flight"), "--random", "nope"], capture_output=True,
+                         text=True, timeout=600)
+    assert out.returncode != 0 and "unknown preset" in out.stderr
+
+
 def test_runtime_refuses_the_cpu(case):
     from airframe_b200.engine import GpuRuntime
     with pytest.raises(RuntimeError, match="CUDA device only"):
