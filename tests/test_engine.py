@@ -15,12 +15,12 @@ pytestmark = pytest.mark.gpu
 # request lengths: some cross the window in the prompt, some while decoding,
 # some wrap the ring of the local layers (64 rows for all three windows)
 LENGTHS = {"A": [5, 11, 17, 40, 64, 1, 33], "B": [1, 9, 20, 33, 100, 128, 70], "C": [3, 45, 130, 300, 65, 64, 200],
-           "D": [70, 5, 210, 129, 64, 101, 33], "E": [70, 5, 150, 129, 64, 101, 33], "F": [66, 5, 140, 129, 64, 101, 33]}
+           "D": [70, 5, 210, 129, 64, 101, 33], "E": [70, 5, 150, 129, 64, 101, 33], "F": [66, 5, 140, 129, 64, 101, 33], "G": [3, 45, 130, 200, 65, 64, 100]}
 PROMPTS = {"A": [5, 3, 17, 10, 20, 1, 9], "B": [1, 9, 5, 33, 40, 60, 17], "C": [3, 39, 41, 150, 2, 64, 63],
-           "D": [40, 5, 99, 128, 1, 100, 20], "E": [40, 5, 99, 128, 1, 100, 20], "F": [40, 5, 99, 128, 1, 100, 20]}
+           "D": [40, 5, 99, 128, 1, 100, 20], "E": [40, 5, 99, 128, 1, 100, 20], "F": [40, 5, 99, 128, 1, 100, 20], "G": [3, 39, 41, 150, 2, 64, 63]}
 
 
-@pytest.fixture(scope="module", params=["A", "B", "C", "D", "E", "F"])
+@pytest.fixture(scope="module", params=["A", "B", "C", "D", "E", "F", "G"])
 def case(request, tmp_path_factory):
     name = request.param
     folder = make_folder(CONFIGS[name], seed=11, store_dtype="bfloat16", root=tmp_path_factory.mktemp(name))

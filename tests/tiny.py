@@ -55,7 +55,19 @@ WIDE_E = dict(WIDE_D, hidden_size=3584, num_attention_heads=16, num_key_value_he
 WIDE_F = dict(WIDE_D, hidden_size=4608, num_attention_heads=32, num_key_value_heads=16, head_dim=128,
               intermediate_size=36864, query_pre_attn_scalar=144, vocab_size=1024, sliding_window=90)
 
-CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": WIDE_D, "E": WIDE_E, "F": WIDE_F}
+# sizes that no tensor-core kernel takes: a width that is no multiple of 8, head size 80, five heads
+# without grouping, an odd vocabulary, an odd window, no softcaps
+ODD_G = {
+    "architectures": ["Gemma2ForCausalLM"], "model_type": "gemma2",
+    "num_hidden_layers": 3, "hidden_size": 100, "num_attention_heads": 5, "num_key_value_heads": 5,
+    "head_dim": 80, "intermediate_size": 260, "vocab_size": 777, "rope_theta": 777.0,
+    "sliding_window": 33, "query_pre_attn_scalar": 50, "attn_logit_softcapping": None,
+    "final_logit_softcapping": None, "max_position_embeddings": 256, "rms_norm_eps": 1e-5,
+    "hidden_activation": "gelu_pytorch_tanh", "tie_word_embeddings": True, "eos_token_id": 1,
+    "torch_dtype": "bfloat16",
+}
+
+CONFIGS = {"A": TINY_A, "B": TINY_B, "C": TINY_C, "D": WIDE_D, "E": WIDE_E, "F": WIDE_F, "G": ODD_G}
 
 
 def make_folder(cfg_dict, seed=0, store_dtype=None, root=None):
