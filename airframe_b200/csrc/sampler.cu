@@ -121,7 +121,32 @@ sample_kernel(float* __restrict__ logits, int ld, int V, const int* __restrict__
   // ---- maximum over finite logits, lowest index on ties
   float best = -INFINITY;
   int best_i = 0x7fffffff;
-  for (int i = tid; i < V; i += SM_THREADS) {
+  int done = 0;
+  if ((((uintptr_t)z) & 15) == 0) {
+    // 16-byte loads, four in flight a thread (indices still rise within a thread: the first maximum stays)
+    const float4* z4 = reinterpret_cast<const float4*>(z);
+    const int n4 = V / 4;
+    for (int i0 = tid; i0 < n4; i0 += 4 * SM_THREADS) {
+      float4 q[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        q[u] = i0 + u * SM_THREADS < n4 ? z4[i0 + u * SM_THREADS] : make_float4(-INFINITY, -INFINITY, -INFINITY, -INFINITY);
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        const int i = (i0 + u * SM_THREADS) * 4;
+        const float e[4] = {q[u].x, q[u].y, q[u].z, q[u].w};
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          if (isfinite(e[c]) && e[c] > best) {
+            best = e[c];
+            best_i = i + c;
+          }
+        }
+      }
+    }
+    done = n4 * 4;
+  }
+  for (int i = done + tid; i < V; i += SM_THREADS) {
     const float v = z[i];
     if (isfinite(v) && v > best) {  // indices rise within a thread: first maximum stays
       best = v;
