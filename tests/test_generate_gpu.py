@@ -24,7 +24,7 @@ def case(request, tmp_path_factory):
 
 
 def test_greedy_generation_equals_the_plain_chain(case):
-    """BASELINE workloads: A prompts 5/11/17 then 8 tokens, B prompts 1/9/20/33 then 12."""
+    """The tiny configurations' own workloads: A prompts 5/11/17 then 8 tokens, B prompts 1/9/20/33 then 12."""
     from airframe_b200.engine import GpuRuntime
     from airframe_b200.sampling import SamplingParams
     name, folder, cfg, w = case
