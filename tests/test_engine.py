@@ -104,6 +104,17 @@ def test_results_do_not_depend_on_batch_mates_or_slots(case, dtype):
     assert rel_err(b[0], a[3]) < SPLITS[dtype] and rel_err(b[1], a[1]) < SPLITS[dtype]
 
 
+def test_the_same_work_gives_the_same_bits(case, dtype):
+    """No kernel adds in an order that depends on timing: a request run twice, and the same batch run
+    twice through the captured decode step, give bitwise equal logits."""
+    rt = runtime(case, dtype)
+    ids = case["requests"][2]
+    a, b = replay.run_whole(rt, ids), replay.run_whole(rt, ids)
+    assert torch.equal(a, b)
+    a, b = replay.run_tail(rt, ids, 16), replay.run_tail(rt, ids, 16)
+    assert torch.equal(a, b)
+
+
 def test_step_errors(case):
     from airframe_b200.cache import CacheFull, ContextOverflow
     from airframe_b200.engine import StepEntry, StepError
