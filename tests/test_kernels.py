@@ -320,7 +320,8 @@ def test_kernels_refuse_what_they_cannot_do(K):
 
 
 @pytest.mark.parametrize("M,N,Kd", [(1, 128, 64), (8, 256, 128), (5, 130, 72), (16, 2304, 2304), (33, 384, 200),
-                                    (64, 100, 1000), (100, 640, 328), (300, 384, 264), (700, 130, 2048)])
+                                    (64, 100, 1000), (100, 640, 328), (300, 384, 264), (700, 130, 2048),
+                                    (520, 6400, 136)])      # the last: more tiles than SMs, a block walks several
 @pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
 def test_gemm_tensor_cores(K, M, N, Kd, out_dtype):
     torch.manual_seed(M * N + Kd)
