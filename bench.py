@@ -181,7 +181,22 @@ def run_ours(args) -> dict:
         torch.cuda.synchronize()
         return start.elapsed_time(end)
 
-    def decode_rate(batch, steps, warm, clocks=None):
+    def step_timeline(one):
+        """Start and duration (us, device clock) of every kernel and copy of one decode step, as the
+        CUDA profiler of PyTorch records them (the kernels of a graph replay overlap: a kernel's span
+        includes its wait for the kernel in front)."""
+        from torch.profiler import ProfilerActivity, profile
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            for _ in range(2):
+                one()
+            torch.cuda.synchronize()
+        evs = sorted((e for e in prof.events() if "cuda" in str(e.device_type).lower()),
+                     key=lambda e: e.time_range.start)
+        first = [i for i, e in enumerate(evs) if "embed_kernel" in e.name][-1]
+        t0 = evs[first].time_range.start
+        return [(e.time_range.start - t0, e.time_range.end - e.time_range.start, e.name) for e in evs[first:]]
+
+    def decode_rate(batch, steps, warm, clocks=None, timeline=None):
         """tokens/s, ms/step and launches of `steps` decode steps at `batch` after 2,048-token prompts."""
         sampler = Sampler(V, dev)
         states = [sampler.new_state(greedy, i) for i in range(batch)]
@@ -197,6 +212,8 @@ def run_ours(args) -> dict:
 
             for _ in range(warm):
                 one()
+            if timeline is not None:
+                timeline.extend(step_timeline(one))
             if clocks is not None:
                 clocks.start()
             n0 = kernels.launch_count() + eng.replayed_launches
@@ -224,6 +241,14 @@ def run_ours(args) -> dict:
     pf_flops = prefill_flops(cfg_dict, n_layers, PROMPT_LEN, 1)
     prefill = {"value": PROMPT_LEN / (pf_ms / 1e3), "tokens": PROMPT_LEN, "ms": pf_ms,
                "frac": pf_flops / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+
+    if args.timeline:
+        tl = []
+        decode_rate(B, 4, W, timeline=tl)
+        print(f"# one decode step, batch {B}, {n_layers} layers: start us, duration us, kernel")
+        for start, dur, name in tl:
+            print(f"{start:9.1f} {dur:8.1f}  {name[:100]}")
+        return None
 
     # ---- the headline: decode at batch B
     clocks = ClockSampler()
@@ -290,6 +315,8 @@ def main() -> int:
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
+    ap.add_argument("--timeline", action="store_true",
+                    help="print the kernels of one decode step with their start and duration, then exit")
     ap.add_argument("--sizes", default="2b", choices=sorted(SIZES), help="layer sizes of this Gemma-2 model")
     args = ap.parse_args()
     if args.impl == "reference":
@@ -300,7 +327,9 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
-    print(json.dumps(run_ours(args)))
+    line = run_ours(args)
+    if line is not None:
+        print(json.dumps(line))
     return 0
 
 
