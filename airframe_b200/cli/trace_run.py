@@ -39,6 +39,7 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     stdout = stdout or sys.stdout
 
     import torch
+    from .. import kernels
     from ..config import config_from_folder
     from ..engine import GpuRuntime, StepEntry
 
@@ -73,6 +74,7 @@ def main(argv=None, stdin=None, stdout=None) -> int:
                     tmp.replace(out_dir / f"{step}.f32")
                 else:
                     torch.cuda.synchronize()
+                kernels.check_device_errors(rt.engine.device)     # a kernel that gave up waiting fails the step
         except Exception:
             for rid in taken:
                 rt.engine.free_slot(slots.pop(rid))

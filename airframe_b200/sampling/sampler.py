@@ -66,12 +66,18 @@ class Sampler:
                        recent=dev[:, 2:] if use_penalty else None,
                        n_recent=dev[:, 1] if use_penalty else None)
         # the tokens come back through pinned memory kept for the purpose
-        if self._host_out is None or self._host_out.numel() < R:
-            self._host_out = torch.empty(max(R, 64), dtype=torch.int32).pin_memory()
+        if self._host_out is None or self._host_out.numel() < R + 1:
+            self._host_out = torch.empty(max(R, 64) + 1, dtype=torch.int32).pin_memory()
         back = self._host_out[:R]
         back.copy_(out, non_blocking=True)
         transfers.count_d2h(back)
+        # with the tokens comes the word that a kernel sets when one of its bounded waits ran out
+        gave_up = self._host_out[-1:]
+        gave_up.copy_(kernels.error_word(self.device), non_blocking=True)
+        transfers.count_d2h(gave_up)
         torch.cuda.current_stream(self.device).synchronize()
+        if int(gave_up[0]) != 0:
+            kernels.check_device_errors(self.device)          # clears the word and raises
         tokens = back.tolist()
         for st, t in zip(states, tokens):
             st.note(t)

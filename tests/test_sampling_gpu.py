@@ -119,3 +119,20 @@ def test_a_row_does_not_depend_on_its_batch(K):
     together, _ = _sample(K, rows, 0.8, 0.95, 1.1, u=u, recent=[[1, 2, 3]] * 8)
     alone = [_sample(K, rows[i:i + 1], 0.8, 0.95, 1.1, u=u[i:i + 1], recent=[[1, 2, 3]])[0][0] for i in range(8)]
     assert together == alone
+
+
+def test_the_sampler_reports_a_kernel_that_gave_up_waiting(K):
+    """Kernels with bounded waits set a device word when a wait runs out; the word travels to the host
+    with the sampled tokens, and the step fails instead of returning tokens made from garbage.  (The
+    word is set by hand here: no kernel is made to wait.)"""
+    from airframe_b200.sampling import Sampler, SamplingParams
+    sampler = Sampler(16, DEV)
+    params = SamplingParams(temperature=0.0, repetition_penalty=1.0)
+    logits = torch.zeros(2, 16, device=DEV)
+    logits[:, 3] = 1.0
+    states = [sampler.new_state(params, i) for i in range(2)]
+    assert sampler.sample(logits, states, params) == [3, 3]
+    K.error_word(DEV).fill_(1)
+    with pytest.raises(K.KernelError, match="gave up waiting"):
+        sampler.sample(logits, states, params)
+    assert sampler.sample(logits, states, params) == [3, 3]          # the word was cleared
