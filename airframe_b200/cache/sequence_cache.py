@@ -26,7 +26,7 @@ import torch
 from .. import transfers
 
 from ..kernels_const import PAGE
-from ..parts.base import KVNeed, StateNeed
+from ..parts.base import KVNeed
 from .pool import CacheFull, IndexPool, PoolError
 
 _STATE_DTYPES = {"float32": torch.float32, "bfloat16": torch.bfloat16, "int32": torch.int32}

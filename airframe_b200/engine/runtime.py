@@ -5,7 +5,6 @@ ids: the library starts where the tokenizer ends.
 """
 from __future__ import annotations
 
-from pathlib import Path
 from typing import Optional
 
 import torch
