@@ -100,7 +100,7 @@ class Engine:
         self.cache.reserve(growth)
         self.cache.flush()
         if self.use_graphs and lens[0] > 0 and all(e.want == [0] for e in entries):
-            logits = self._decode_graphed(entries, lens)
+            logits = self._decode_graphed([e.slot for e in entries], lens, tokens=[e.tokens[0] for e in entries])
             if not borrow:
                 logits = logits.clone()
         else:
@@ -120,11 +120,40 @@ class Engine:
                 return b
         return (n + 127) // 128 * 128
 
-    def _decode_graphed(self, entries, lens):
-        """One decode step, every sequence wanting its token's logits, through
-        a CUDA graph.  The result is the graph's own output buffer: it is
-        valid until the next step of the same padded size."""
-        B = len(entries)
+    def decode_rows(self, slots, tokens_dev, borrow: bool = True):
+        """One decode step whose tokens are already on the device (the sampler's
+        output of the step before): row r carries the next token ``tokens_dev[r]``
+        of the sequence in ``slots[r]``; a row with slot None is not used.  Rows keep
+        their places from step to step, so the host can queue this step before it has
+        read the tokens themselves.  Needs CUDA graphs (``use_graphs``).  Returns the
+        logits of all rows [len(slots), vocab]."""
+        if not self.use_graphs:
+            raise StepError("decode_rows needs captured decode steps")
+        live = [s for s in slots if s is not None]
+        if not live or len(set(live)) != len(live):
+            raise StepError("decode_rows needs at least one sequence, each slot once")
+        try:
+            lens = [self.cache.length(s) if s is not None else 0 for s in slots]
+        except PoolError as err:
+            raise StepError(str(err)) from err
+        if any(s is not None and n == 0 for s, n in zip(slots, lens)):
+            raise StepError("sequences that go on have tokens in the cache")
+        if tokens_dev.dtype != torch.int32 or tokens_dev.numel() < len(slots) or not tokens_dev.is_cuda:
+            raise StepError("decode_rows wants one int32 token per row on the device")
+        growth = {s: n + 1 for s, n in zip(slots, lens) if s is not None}
+        self.cache.reserve(growth)
+        self.cache.flush()
+        logits = self._decode_graphed([-1 if s is None else s for s in slots], lens, tokens_dev=tokens_dev)
+        self.cache.commit(growth)
+        return logits if borrow else logits.clone()
+
+    def _decode_graphed(self, slots, lens, tokens=None, tokens_dev=None):
+        """One decode step, every row wanting its token's logits, through a CUDA
+        graph.  Rows with slot -1 are padding.  The tokens come from the host
+        (``tokens``) or lie on the device already (``tokens_dev``).  The result is
+        the graph's own output buffer: it is valid until the next step of the same
+        padded size."""
+        B = len(slots)
         Bp = self.padded_batch(B)
         g = self._graphs.get(Bp)
         if g is None:
@@ -135,10 +164,10 @@ class Engine:
         host, sent = g["host"][k], g["sent"][k]
         sent.synchronize()
         lay = g["host_np"][k]                 # [tokens | positions | slots | len_after], Bp each
-        lay[:B] = [e.tokens[0] for e in entries]
+        lay[:B] = tokens if tokens is not None else 0
         lay[Bp:Bp + B] = lens
-        lay[2 * Bp:2 * Bp + B] = [e.slot for e in entries]
-        lay[3 * Bp:3 * Bp + B] = [n + 1 for n in lens]
+        lay[2 * Bp:2 * Bp + B] = slots
+        lay[3 * Bp:3 * Bp + B] = [n + 1 if s >= 0 else 0 for s, n in zip(slots, lens)]
         if B < Bp:
             lay[B:Bp] = 0
             lay[Bp + B:2 * Bp] = 0
@@ -147,6 +176,8 @@ class Engine:
         g["dynamic"].copy_(host, non_blocking=True)
         transfers.count_h2d(host)
         sent.record()
+        if tokens_dev is not None:
+            g["dynamic"][:B].copy_(tokens_dev[:B], non_blocking=True)
         g["graph"].replay()
         self.replayed_launches += g["launches"]
         return g["logits"][:B]

@@ -13,6 +13,16 @@ The loop needs of its engine: ``take_slot()``, ``free_slot(slot)``,
 ``step(entries) -> logits``, ``max_context``, ``vocab_size`` and
 ``cache.total_pages`` / ``cache.n_slots``; of its sampler:
 ``new_state(params, index)`` and ``sample(logits, states, params) -> tokens``.
+
+With an engine that has ``decode_rows`` (decode steps captured into CUDA
+graphs) and a sampler that has ``sample_async``, and without a repetition
+penalty (it needs the token before the next step), the loop keeps the device
+one step ahead of the host: step k + 1 takes its tokens from the device, where
+the sampler of step k left them, and is queued before the host has read them.
+What the host knows without the tokens (max_tokens, the context limit) it
+applies in time; a stop token it sees one step late: that sequence's next
+step is already queued, its result is dropped and nothing of it is emitted.
+The tokens are the same either way.
 """
 from __future__ import annotations
 
@@ -48,6 +58,7 @@ class GenerationLoop:
         self.sampler = sampler
         self.model_stop_ids = set(stop_token_ids)
         self.max_batch = max_batch
+        self.pipelined = True          # keep the device a step ahead of the host where engine and sampler allow
         self.finish_reasons: list = []
         self.batches_run: list = []
 
@@ -128,6 +139,15 @@ class GenerationLoop:
         s.slot = -1
 
     def _run_batch(self, seqs, params, stops, on_token) -> None:
+        ahead = (self.pipelined and params.repetition_penalty == 1.0 and hasattr(self.engine, "decode_rows")
+                 and hasattr(self.sampler, "sample_async") and getattr(self.engine, "use_graphs", False))
+        if ahead:
+            self._run_batch_ahead(seqs, params, stops, on_token)
+        else:
+            self._run_batch_in_step(seqs, params, stops, on_token)
+
+    def _run_batch_in_step(self, seqs, params, stops, on_token) -> None:
+        """Every step waits for the tokens of the step before."""
         logits = self.engine.step([StepEntry(s.slot, s.prompt, [len(s.prompt) - 1]) for s in seqs])
         for s in seqs:
             s.length = len(s.prompt)
@@ -154,3 +174,48 @@ class GenerationLoop:
             logits = self.engine.step([StepEntry(s.slot, [s.out[-1]], [0]) for s in active], borrow=True)
             for s in active:
                 s.length += 1
+
+    def _run_batch_ahead(self, seqs, params, stops, on_token) -> None:
+        """The device one step ahead of the host.  Row r of every decode step
+        belongs to seqs[r]; a sequence that has ended leaves its row unused."""
+        eng, smp = self.engine, self.sampler
+        logits = eng.step([StepEntry(s.slot, s.prompt, [len(s.prompt) - 1]) for s in seqs])
+        for s in seqs:
+            s.length = len(s.prompt)
+        n = len(seqs)
+        sampled = [1] * n                       # samples asked for per row, the one in flight included
+        pend = smp.sample_async(logits, [s.state for s in seqs], params)
+        pend_rows = list(range(n))              # rows whose tokens `pend` carries
+        while True:
+            # rows that go on whatever their token in flight is, unless it is a stop token
+            go = [r for r in pend_rows
+                  if seqs[r].finish is None and sampled[r] < params.max_tokens
+                  and seqs[r].length + 1 <= eng.max_context]
+            nxt = None
+            if go:
+                on = set(go)
+                logits = eng.decode_rows([seqs[r].slot if r in on else None for r in range(n)], pend.device)
+                nxt = smp.sample_async(logits, [seqs[r].state if r in on else None for r in range(n)], params)
+            # now the tokens in flight (the next step is queued behind them)
+            tokens = pend.result()
+            for r in pend_rows:
+                s = seqs[r]
+                if s.finish is not None:
+                    continue
+                t = tokens[r]
+                if t in stops:
+                    self._end(s, "stop")        # its row of the queued step is wasted
+                    continue
+                s.out.append(t)
+                if on_token is not None:
+                    on_token(s.index, t)
+                if len(s.out) >= params.max_tokens:
+                    self._end(s, "length")
+                elif s.length + 1 > eng.max_context:
+                    self._end(s, "context")
+            if nxt is None:
+                break
+            for r in go:
+                seqs[r].length += 1
+                sampled[r] += 1
+            pend, pend_rows = nxt, go

@@ -28,11 +28,40 @@ class SequenceSamplingState:
             del self.recent[0]
 
 
+class PendingTokens:
+    """Tokens that the sampling kernel has been asked for: on the device at once
+    (``device``, int32 [R], in stream order), on the host after :meth:`result`."""
+
+    def __init__(self, sampler, device_tokens, host, gave_up, event, states):
+        self._sampler = sampler
+        self.device = device_tokens
+        self._host = host
+        self._gave_up = gave_up
+        self._event = event
+        self._states = states
+        self._tokens = None
+
+    def result(self) -> list:
+        """Waits for the step, checks the device's error word that came with the
+        tokens, notes the tokens in the states they belong to (None: no state)."""
+        if self._tokens is None:
+            self._event.synchronize()
+            if int(self._gave_up[0]) != 0:
+                kernels.check_device_errors(self._sampler.device)      # clears the word and raises
+            self._tokens = self._host.tolist()
+            for st, t in zip(self._states, self._tokens):
+                if st is not None:
+                    st.note(t)
+        return self._tokens
+
+
 class Sampler:
     def __init__(self, vocab_size: int, device):
         self.vocab_size = vocab_size
         self.device = torch.device(device)
-        self._host_out = None
+        self._host_out = [None, None]       # pinned buffers in turn: two samples may be in flight
+        self._done = [None, None]
+        self._turn = 0
 
     def new_state(self, params: SamplingParams, request_index: int) -> SequenceSamplingState:
         return SequenceSamplingState(params, request_index)
@@ -41,6 +70,12 @@ class Sampler:
         """One token for each row of ``logits`` (float32 [R, V] on the device;
         changed in place by the penalty).  Advances each state's generator and
         recent-token window."""
+        return self.sample_async(logits, states, params).result()
+
+    def sample_async(self, logits, states, params: SamplingParams) -> PendingTokens:
+        """As :meth:`sample`, without waiting: the kernel and the copy of its
+        tokens to the host are queued.  A row whose state is None takes no draw
+        from any generator and notes nothing (its token is not used)."""
         R = logits.shape[0]
         if R != len(states):
             raise ValueError("one sampling state per row of logits")
@@ -52,6 +87,8 @@ class Sampler:
             host = torch.zeros(R, 1 + n_extra, dtype=torch.int32)
             hv = host.view(torch.float32)
             for r, st in enumerate(states):
+                if st is None:
+                    continue
                 if not params.greedy:
                     hv[r, 0] = st.rng.next_f32()
                 if use_penalty:
@@ -66,19 +103,18 @@ class Sampler:
                        recent=dev[:, 2:] if use_penalty else None,
                        n_recent=dev[:, 1] if use_penalty else None)
         # the tokens come back through pinned memory kept for the purpose
-        if self._host_out is None or self._host_out.numel() < R + 1:
-            self._host_out = torch.empty(max(R, 64) + 1, dtype=torch.int32).pin_memory()
-        back = self._host_out[:R]
+        k = self._turn = self._turn ^ 1
+        if self._done[k] is not None:
+            self._done[k].synchronize()                  # (its last user has long been read)
+        if self._host_out[k] is None or self._host_out[k].numel() < R + 1:
+            self._host_out[k] = torch.empty(max(R, 64) + 1, dtype=torch.int32).pin_memory()
+            self._done[k] = torch.cuda.Event()
+        back = self._host_out[k][:R]
         back.copy_(out, non_blocking=True)
         transfers.count_d2h(back)
         # with the tokens comes the word that a kernel sets when one of its bounded waits ran out
-        gave_up = self._host_out[-1:]
+        gave_up = self._host_out[k][-1:]
         gave_up.copy_(kernels.error_word(self.device), non_blocking=True)
         transfers.count_d2h(gave_up)
-        torch.cuda.current_stream(self.device).synchronize()
-        if int(gave_up[0]) != 0:
-            kernels.check_device_errors(self.device)          # clears the word and raises
-        tokens = back.tolist()
-        for st, t in zip(states, tokens):
-            st.note(t)
-        return tokens
+        self._done[k].record(torch.cuda.current_stream(self.device))
+        return PendingTokens(self, out, back, gave_up, self._done[k], list(states))

@@ -62,6 +62,28 @@ def test_temperature_sampling_is_seeded_and_batch_independent(case):
     assert all(len(x) == 8 and all(0 <= t < cfg["vocab_size"] for t in x) for x in a)
 
 
+def test_the_device_a_step_ahead_of_the_host_gives_the_same_tokens(case):
+    from airframe_b200.engine import GpuRuntime
+    from airframe_b200.sampling import SamplingParams
+    name, folder, cfg, w = case
+    prompts = [replay.random_ids(cfg["vocab_size"], n, 90 + n) for n in (4, 13, 2, 9, 6)]
+    rt = GpuRuntime.load(folder, dtype="bfloat16", max_tokens=64 * 8)
+    free = SamplingParams(max_tokens=10, temperature=0.9, top_p=0.95, repetition_penalty=1.0, ignore_eos=True, seed=5)
+    rt.generate(prompts[0], free)                                         # (makes the loop)
+    runs = {}
+    for ahead in (False, True):
+        rt._loop.pipelined = ahead
+        a = rt.generate(prompts, free)
+        # tokens that some sequences emit midway become stop tokens: those sequences end early, one step late for the host
+        stops = [a[0][4], a[2][7], a[3][0]]
+        b = rt.generate(prompts, SamplingParams(max_tokens=10, temperature=0.9, top_p=0.95, repetition_penalty=1.0,
+                                                ignore_eos=True, seed=5, stop_token_ids=stops))
+        runs[ahead] = (a, b, list(rt._loop.finish_reasons))
+        assert rt.engine.cache.slots.n_held == 0
+    assert runs[False] == runs[True]
+    assert "stop" in runs[True][2] and len(runs[True][1][3]) == 0
+
+
 def test_more_requests_than_fit_one_batch(case):
     from airframe_b200.engine import GpuRuntime
     from airframe_b200.sampling import SamplingParams

@@ -142,3 +142,87 @@ def test_slots_come_back_when_a_step_fails():
     with pytest.raises(RuntimeError, match="boom"):
         loop.generate([[1], [2]], P(max_tokens=5))
     assert eng.pool.n_held == 0
+
+
+# ---------------------------------------------------------------- the device one step ahead of the host
+
+class AheadEngine(FakeEngine):
+    """An engine whose decode steps can take their tokens from 'the device'."""
+    use_graphs = True
+
+    def decode_rows(self, slots, tokens_dev, borrow=True):
+        live = [(r, s) for r, s in enumerate(slots) if s is not None]
+        assert live and len(slots) == len(tokens_dev)
+        for r, s in live:
+            assert self.lens[s] > 0
+            self.lens[s] += 1
+            assert self.lens[s] <= self.max_context
+        self.steps.append([(s, [tokens_dev[r]]) for r, s in live])
+        return list(slots)
+
+
+class Pending:
+    def __init__(self, tokens):
+        self.device = tokens
+        self.read = False
+
+    def result(self):
+        self.read = True
+        return self.device
+
+
+class AheadSampler(ScriptSampler):
+    def sample_async(self, logits, states, params):
+        out = []
+        for st in states:
+            if st is None:
+                out.append(0)
+                continue
+            seq = self.script[st["index"]]
+            out.append(seq[st["k"]] if st["k"] < len(seq) else 0)
+            st["k"] += 1
+        return Pending(out)
+
+
+SCRIPTS = [
+    ({0: [5, 6, 9, 1], 1: [9], 2: [5, 5, 5, 5, 5, 5]}, [[1, 2, 3], [4], [7, 7, 7, 7, 7]], dict(max_tokens=4)),
+    ({0: [9], 1: [9]}, [[1], [2]], dict(max_tokens=3)),
+    ({0: [1, 2, 3, 4, 5, 6, 7, 8], 1: [1, 9]}, [[1] * 28, [2]], dict(max_tokens=8)),       # request 0 meets the context limit
+    ({0: [4], 1: [4, 4], 2: [4, 4, 9]}, [[1], [2], [3]], dict(max_tokens=1)),
+    ({i: [i + 10] * 3 for i in range(5)}, [[1]] * 5, dict(max_tokens=2)),
+]
+
+
+@pytest.mark.parametrize("script,prompts,kw", SCRIPTS)
+def test_a_step_ahead_gives_the_same_tokens_and_reasons(script, prompts, kw):
+    runs = []
+    for ahead in (False, True):
+        eng = AheadEngine(slots=3)
+        loop = GenerationLoop(eng, AheadSampler({k: list(v) for k, v in script.items()}), stop_token_ids=[9])
+        loop.pipelined = ahead
+        seen = {}
+        out = loop.generate(prompts, P(**kw), on_token=lambda i, t: seen.setdefault(i, []).append(t))
+        assert eng.pool.n_held == 0
+        runs.append((out, loop.finish_reasons, seen, eng.steps, loop.batches_run))
+    assert runs[0][0] == runs[1][0] and runs[0][1] == runs[1][1] and runs[0][2] == runs[1][2]
+    assert runs[0][4] == runs[1][4]
+    # one step ahead, a sequence is fed at most one token more than in step: the stop token it ended on
+    fed = [sum(len(t) for step in r[3] for _, t in step) for r in runs]
+    n_stops = sum(1 for reason in runs[0][1] if reason == "stop")
+    assert fed[0] <= fed[1] <= fed[0] + n_stops
+
+
+def test_a_step_ahead_feeds_nothing_after_the_last_allowed_token():
+    eng = AheadEngine()
+    loop = GenerationLoop(eng, AheadSampler({0: [3, 3, 3, 3], 1: [4, 9, 4, 4]}), stop_token_ids=[9])
+    assert loop.generate([[1, 1], [2]], P(max_tokens=3)) == [[3, 3, 3], [4]]
+    assert loop.finish_reasons == ["length", "stop"]
+    # prompts; both rows; both rows (request 1's stop token is in flight); request 0 alone is never fed its third token
+    assert eng.steps == [[(0, [1, 1]), (1, [2])], [(0, [3]), (1, [4])], [(0, [3]), (1, [9])]]
+
+
+def test_a_repetition_penalty_keeps_the_loop_in_step():
+    eng = AheadEngine()
+    loop = GenerationLoop(eng, AheadSampler({0: [3, 9]}), stop_token_ids=[9])
+    out = loop.generate([[1]], SamplingParams(temperature=0.0, repetition_penalty=1.3, max_tokens=4))
+    assert out == [[3]] and eng.steps == [[(0, [1])], [(0, [3])]]
