@@ -5,9 +5,12 @@
 
 A step is one decode step of a batch of 8 sequences that hold 2,048-token
 prompts (context limit 8192): the model's step function plus greedy sampling on
-the device.  ``value`` is decoded tokens a second, timed with CUDA events around
-exactly K steps after W warm-up steps.  ``e2e`` is the same through
-``GpuRuntime.generate`` with host token lists in and out.  The line also carries
+the device, stepped as the generation loop steps it (a step takes its tokens from
+the device and is queued before the host has read them).  ``value`` is decoded
+tokens a second, timed with CUDA events around exactly K steps after W warm-up
+steps (default 32: the first 30 or so steps after a burst of prompts run at
+lowered clocks, about 2.1 ms instead of 1.8).  ``e2e`` is the same through
+``GpuRuntime.generate`` with host token lists in and out, prompts' aftermath included.  The line also carries
 the prefill rate of 2,048 tokens with its fraction of the bf16 peak, the decode
 step's fraction of the HBM roofline, decode at batch 1 and 64, the clocks seen
 during the timed region and the number of this library's kernels launched in it.
@@ -227,11 +230,17 @@ def run_ours(args) -> dict:
         try:
             ps = prompts(batch, 100 + batch)
             logits = eng.step([StepEntry(s, p, [PROMPT_LEN - 1]) for s, p in zip(slots, ps)])
-            state = {"tokens": sampler.sample(logits, states, greedy)}
+            state = {}
+
+            # the product's own way of stepping (GenerationLoop): the step takes its tokens from the device,
+            # where the sampler of the step before left them, and is queued before the host reads those
+            state["pending"] = sampler.sample_async(logits, states, greedy)
 
             def one():
-                lg = eng.step([StepEntry(s, [t], [0]) for s, t in zip(slots, state["tokens"])], borrow=True)
-                state["tokens"] = sampler.sample(lg, states, greedy)
+                lg = eng.decode_rows(slots, state["pending"].device)
+                nxt = sampler.sample_async(lg, states, greedy)
+                state["pending"].result()                     # the tokens of the step before, on the host
+                state["pending"] = nxt
 
             for _ in range(warm):
                 one()
@@ -241,6 +250,7 @@ def run_ours(args) -> dict:
                 clocks.start()
             n0 = kernels.launch_count() + eng.replayed_launches
             ms = timed(one, steps)
+            state["pending"].result()
             launches = kernels.launch_count() + eng.replayed_launches - n0
             lens = [eng.length(s) for s in slots]
             if after is not None:
@@ -296,7 +306,7 @@ def run_ours(args) -> dict:
     points = {}
     if not args.no_points:
         for b in (1, 64):
-            points[f"decode_b{b}"] = decode_rate(b, max(4, K // 2), 3)[0]
+            points[f"decode_b{b}"] = decode_rate(b, max(4, K // 2), W)[0]
 
     # ---- end to end through the public entry point
     n_new = K + 1
@@ -344,8 +354,10 @@ def run_ours(args) -> dict:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=64)
-    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=32,
+                    help="untimed decode steps after the prompts (the first 30 or so after a burst of prompts "
+                         "run at lowered clocks)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
