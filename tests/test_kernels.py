@@ -86,6 +86,34 @@ def test_add_rmsnorm(K, dtype):
     close(xd, x.double() + plain.rms_norm(parts.double().sum(0), w1.double(), 1e-6), torch.float32)
 
 
+@pytest.mark.parametrize("H", [1100, 2304, 4608])
+@pytest.mark.parametrize("n_parts", [1, 3, 9])
+def test_add_rmsnorm_of_a_decode_step(K, H, n_parts):
+    """Few rows of many 32-bit partial sums, as a decode step has them; one row's result does not depend
+    on the others."""
+    M = 7
+    g = torch.Generator().manual_seed(H + n_parts)
+    x = torch.randn(M, H, generator=g)
+    parts = torch.randn(n_parts, M, H, generator=g) * 2
+    parts[:, 3] *= 30.0                                    # a row with another scale
+    w1, w2 = torch.randn(H, generator=g) * 0.1, torch.randn(H, generator=g) * 0.1
+    want_x = x.double() + plain.rms_norm(parts.double().sum(0), w1.double(), 1e-6)
+    want_y = plain.rms_norm(want_x, w2.double(), 1e-5)
+    for ydt in (torch.bfloat16, torch.float32):
+        xd = x.to(DEV)
+        y = torch.empty(M, H, dtype=ydt, device=DEV)
+        K.add_rmsnorm(xd, parts.to(DEV), w1.to(DEV), 1e-6, 1.0, y=y, w_next=w2.to(DEV), eps_next=1e-5, n_parts=n_parts)
+        close(xd, want_x, torch.float32)
+        close(y, want_y, ydt)
+    xd1 = x.to(DEV)
+    K.add_rmsnorm(xd1, parts.to(DEV), w1.to(DEV), 1e-6, 1.0, n_parts=n_parts)     # without a next norm
+    close(xd1, want_x, torch.float32)
+    # rows alone give the same bits as rows together
+    x3 = x[3:4].to(DEV)
+    K.add_rmsnorm(x3, parts[:, 3:4].contiguous().to(DEV), w1.to(DEV), 1e-6, 1.0, n_parts=n_parts)
+    assert torch.equal(x3[0], xd1[3])
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_gated_act(K, dtype):
     M, I = 3, 1111
