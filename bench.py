@@ -11,7 +11,8 @@ tokens a second, timed with CUDA events around exactly K steps after W warm-up
 steps (default 32: the first 30 or so steps after a burst of prompts run at
 lowered clocks, about 2.1 ms instead of 1.8).  ``e2e`` is the same through
 ``GpuRuntime.generate`` with host token lists in and out, prompts' aftermath included.  The line also carries
-the prefill rate of 2,048 tokens with its fraction of the bf16 peak, the decode
+the prefill rate of 2,048 tokens with its fraction of the bf16 peak (and the same for its
+products and its attention kernels apart, from their summed kernel times), the decode
 step's fraction of the HBM roofline, decode at batch 1 and 64, the clocks seen
 during the timed region and the number of this library's kernels launched in it.
 Every decode step reads all weights (5.2 GB), far more than the 126 MB L2, so
@@ -142,6 +143,37 @@ def prefill_flops(cfg, n_layers, T, n_logits):
         pairs = sum(min(t + 1, w) if w else t + 1 for t in range(T))
         attn += 2 * 2 * pairs * q
     return linear + attn + 2 * n_logits * v * h
+
+
+def prefill_shares(prefill_once, cfg, n_layers, pk) -> dict:
+    """The layers' products and the attention kernels of one prefill apart: their summed kernel times
+    (one more prefill under the CUDA profiler of PyTorch) and their flops over the bf16 peak."""
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        prefill_once()
+        torch.cuda.synchronize()
+    gemm_us = attn_us = 0.0
+    for e in prof.events():
+        if "cuda" not in str(e.device_type).lower():
+            continue
+        dur = e.time_range.end - e.time_range.start
+        if "gemm_tc_kernel<256" in e.name or "gemm_tc_kernel<128" in e.name:     # (the head's one row is not among these)
+            gemm_us += dur
+        elif "attn_prefill" in e.name:
+            attn_us += dur
+    h, i = cfg["hidden_size"], cfg["intermediate_size"]
+    q = cfg["num_attention_heads"] * cfg["head_dim"]
+    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
+    linear = 2 * PROMPT_LEN * n_layers * ((q + 2 * kv) * h + h * q + 3 * h * i)
+    attn = prefill_flops(cfg, n_layers, PROMPT_LEN, 0) - linear
+    peak = pk["bf16_tflops"] * 1e12
+    out = {}
+    if gemm_us > 0:
+        out["products"] = {"ms": gemm_us / 1e3, "frac": linear / (gemm_us / 1e6) / peak}
+    if attn_us > 0:
+        out["attention"] = {"ms": attn_us / 1e3, "frac": attn / (attn_us / 1e6) / peak}
+    return out
 
 
 def run_ours(args) -> dict:
@@ -276,6 +308,7 @@ def run_ours(args) -> dict:
     pf_flops = prefill_flops(cfg_dict, n_layers, PROMPT_LEN, 1)
     prefill = {"value": PROMPT_LEN / (pf_ms / 1e3), "tokens": PROMPT_LEN, "ms": pf_ms,
                "frac": pf_flops / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+    prefill.update(prefill_shares(prefill_once, cfg_dict, n_layers, pk))
 
     if args.phase_times:
         out = []
