@@ -115,6 +115,51 @@ def test_the_same_work_gives_the_same_bits(case, dtype):
     assert torch.equal(a, b)
 
 
+def test_decode_steps_fed_from_the_device(case, dtype):
+    """``decode_rows``: the step's tokens lie on the device, rows keep their places and a row may be
+    unused; the logits are those of the same step fed from the host."""
+    from airframe_b200.engine import StepEntry, StepError
+    rt = runtime(case, dtype)
+    eng = rt.engine
+    reqs = [r for r in case["requests"] if len(r) >= 5][:3]
+    outs = {}
+    for way in ("host", "device"):
+        slots = [eng.take_slot() for _ in reqs]
+        try:
+            eng.step([StepEntry(s, r[:-3], []) for s, r in zip(slots, reqs)])
+            got = []
+            for k in (3, 2, 1):                                  # the last three tokens, one step each
+                toks = [r[len(r) - k] for r in reqs]
+                live = [0, 2] if k == 1 else [0, 1, 2]           # the middle row is unused in the last step
+                if way == "host":
+                    lg = eng.step([StepEntry(slots[i], [toks[i]], [0]) for i in live])
+                    got.append(lg.clone())
+                else:
+                    dev = torch.tensor(toks, dtype=torch.int32, device=eng.device)
+                    lg = eng.decode_rows([slots[i] if i in live else None for i in range(3)], dev)
+                    got.append(lg[live].clone())
+            outs[way] = got
+        finally:
+            for s in slots:
+                eng.free_slot(s)
+    for a, b in zip(outs["host"], outs["device"]):
+        assert a.shape == b.shape and rel_err(b, a) < SPLITS[dtype]
+    s = eng.take_slot()
+    try:
+        dev = torch.zeros(2, dtype=torch.int32, device=eng.device)
+        with pytest.raises(StepError, match="tokens in the cache"):
+            eng.decode_rows([s, None], dev)
+        with pytest.raises(StepError, match="at least one sequence"):
+            eng.decode_rows([None, None], dev)
+        eng.step([StepEntry(s, [1, 2], [])])
+        with pytest.raises(StepError, match="int32"):
+            eng.decode_rows([s], dev.float())
+        with pytest.raises(StepError, match="each slot once"):
+            eng.decode_rows([s, s], dev)
+    finally:
+        eng.free_slot(s)
+
+
 def test_step_errors(case):
     from airframe_b200.cache import CacheFull, ContextOverflow
     from airframe_b200.engine import StepEntry, StepError
