@@ -146,22 +146,27 @@ def prefill_flops(cfg, n_layers, T, n_logits):
 
 
 def prefill_shares(prefill_once, cfg, n_layers, pk) -> dict:
-    """The layers' products and the attention kernels of one prefill apart: their summed kernel times
+    """The layers' products and the attention kernels of one prefill apart: the time charged to them
     (one more prefill under the CUDA profiler of PyTorch) and their flops over the bf16 peak."""
     import torch
     from torch.profiler import ProfilerActivity, profile
     with profile(activities=[ProfilerActivity.CUDA]) as prof:
         prefill_once()
         torch.cuda.synchronize()
+    # Kernels overlap (a kernel starts while the one in front still runs and waits for it): a kernel is
+    # charged the time from the end of what ran before it to its own end, so that the shares add up to the
+    # time the device was busy.
+    evs = sorted((e for e in prof.events() if "cuda" in str(e.device_type).lower()), key=lambda e: e.time_range.start)
     gemm_us = attn_us = 0.0
-    for e in prof.events():
-        if "cuda" not in str(e.device_type).lower():
-            continue
-        dur = e.time_range.end - e.time_range.start
+    busy_until = None
+    for e in evs:
+        start, end = e.time_range.start, e.time_range.end
+        own = end - start if busy_until is None else max(0.0, end - max(start, busy_until))
+        busy_until = end if busy_until is None else max(busy_until, end)
         if "gemm_tc_kernel<256" in e.name or "gemm_tc_kernel<128" in e.name:     # (the head's one row is not among these)
-            gemm_us += dur
+            gemm_us += own
         elif "attn_prefill" in e.name:
-            attn_us += dur
+            attn_us += own
     h, i = cfg["hidden_size"], cfg["intermediate_size"]
     q = cfg["num_attention_heads"] * cfg["head_dim"]
     kv = cfg["num_key_value_heads"] * cfg["head_dim"]
