@@ -186,8 +186,11 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ x, const TA* __restrict__
 // elements (group v of thread t at element 4 (t + v * threads)), every load issued before the first
 // reduction.  Few rows (decode): NV = 1, many threads per row, what costs is the chain of memory
 // latencies; many rows (prefill): NV = 2, smaller blocks, more rows in flight on an SM.
-template <typename TA, typename TY, int NV>
-__global__ void __launch_bounds__(1024)
+// MANY (the rows of a prompt): the kernel is bound by how many rows an SM holds at a time, so it keeps to 32
+// registers (seven blocks of a 2304-wide row per SM instead of four) and reads the norms' weights, which
+// every row shares and the L1 holds, where it uses them instead of keeping them from the start.
+template <typename TA, typename TY, int NV, bool MANY = false>
+__global__ void __launch_bounds__(MANY ? 512 : 1024, MANY ? 4 : 1)
 add_rmsnorm_row_kernel(float* __restrict__ x, const TA* __restrict__ a, int n_parts, size_t part_stride,
                        const float* __restrict__ w_post, TY* __restrict__ y, const float* __restrict__ w_next,
                        int hidden, float eps_post, float eps_next, float offset) {
@@ -204,7 +207,7 @@ add_rmsnorm_row_kernel(float* __restrict__ x, const TA* __restrict__ a, int n_pa
     on[v] = i < hidden;
 #pragma unroll
     for (int u = 0; u < 4; ++u) av[v][u] = xv[v][u] = wp[v][u] = wn[v][u] = 0.f;
-    if (!on[v]) continue;
+    if (!on[v] || MANY) continue;
     const float4 pt = *reinterpret_cast<const float4*>(w_post + i);
     wp[v][0] = pt.x, wp[v][1] = pt.y, wp[v][2] = pt.z, wp[v][3] = pt.w;
     if (y != nullptr) {
@@ -254,6 +257,10 @@ add_rmsnorm_row_kernel(float* __restrict__ x, const TA* __restrict__ a, int n_pa
   float ss2 = 0.f;
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
+    if (MANY && on[v]) {
+      const float4 pt = *reinterpret_cast<const float4*>(w_post + (threadIdx.x + v * blockDim.x) * 4);
+      wp[v][0] = pt.x, wp[v][1] = pt.y, wp[v][2] = pt.z, wp[v][3] = pt.w;
+    }
 #pragma unroll
     for (int u = 0; u < 4; ++u) {
       xv[v][u] = xv[v][u] + av[v][u] * inv * (offset + wp[v][u]);
@@ -269,6 +276,10 @@ add_rmsnorm_row_kernel(float* __restrict__ x, const TA* __restrict__ a, int n_pa
 #pragma unroll
   for (int v = 0; v < NV; ++v) {
     if (!on[v]) continue;
+    if (MANY) {
+      const float4 nt = *reinterpret_cast<const float4*>(w_next + (threadIdx.x + v * blockDim.x) * 4);
+      wn[v][0] = nt.x, wn[v][1] = nt.y, wn[v][2] = nt.z, wn[v][3] = nt.w;
+    }
     TY* yr = y + (size_t)r * hidden + (threadIdx.x + v * blockDim.x) * 4;
     if constexpr (sizeof(TY) == 2) {
       __nv_bfloat162 lo = __floats2bfloat162_rn(xv[v][0] * inv2 * (offset + wn[v][0]), xv[v][1] * inv2 * (offset + wn[v][1]));
@@ -296,7 +307,10 @@ AF_EXPORT int af_add_rmsnorm(float* x, const void* a, int a_dtype, int n_parts, 
     const int threads = ((hidden / (4 * nv) + 31) / 32) * 32;
 #define LAUNCH_ROW(TA, TY)                                                                                  \
   do {                                                                                                      \
-    if (nv == 2)                                                                                            \
+    if (nv == 2 && n_rows >= 256 && threads <= 512)                                                         \
+      af_launch(add_rmsnorm_row_kernel<TA, TY, 2, true>, dim3(n_rows), dim3(threads), 0, stream, x, (const TA*)a, \
+                n_parts, (size_t)part_stride, w_post, (TY*)y, w_next, hidden, eps_post, eps_next, offset);  \
+    else if (nv == 2)                                                                                       \
       af_launch(add_rmsnorm_row_kernel<TA, TY, 2>, dim3(n_rows), dim3(threads), 0, stream, x, (const TA*)a, \
                 n_parts, (size_t)part_stride, w_post, (TY*)y, w_next, hidden, eps_post, eps_next, offset);  \
     else                                                                                                    \

@@ -86,6 +86,28 @@ def test_add_rmsnorm(K, dtype):
     close(xd, x.double() + plain.rms_norm(parts.double().sum(0), w1.double(), 1e-6), torch.float32)
 
 
+@pytest.mark.parametrize("H", [1024, 2304, 3584, 4608])
+def test_add_rmsnorm_of_a_prompt(K, H):
+    """Many rows (the variant that keeps few registers and reads the weights where it uses them)."""
+    M = 300
+    g = torch.Generator().manual_seed(H)
+    x = torch.randn(M, H, generator=g)
+    w1, w2 = torch.randn(H, generator=g) * 0.1, torch.randn(H, generator=g) * 0.1
+    for a in ((torch.randn(M, H, generator=g) * 3).to(torch.bfloat16), torch.randn(2, M, H, generator=g)):
+        n_parts = a.shape[0] if a.dim() == 3 else 1
+        summed = a.double().sum(0) if a.dim() == 3 else a.double()
+        want_x = x.double() + plain.rms_norm(summed, w1.double(), 1e-6)
+        want_y = plain.rms_norm(want_x, w2.double(), 1e-5)
+        xd = x.to(DEV)
+        y = torch.empty(M, H, dtype=torch.bfloat16, device=DEV)
+        K.add_rmsnorm(xd, a.to(DEV), w1.to(DEV), 1e-6, 1.0, y=y, w_next=w2.to(DEV), eps_next=1e-5, n_parts=n_parts)
+        close(xd, want_x, torch.float32)
+        close(y, want_y, torch.bfloat16)
+        xd = x.to(DEV)
+        K.add_rmsnorm(xd, a.to(DEV), w1.to(DEV), 1e-6, 1.0, n_parts=n_parts)
+        close(xd, want_x, torch.float32)
+
+
 @pytest.mark.parametrize("H", [1100, 2304, 4608])
 @pytest.mark.parametrize("n_parts", [1, 3, 9])
 def test_add_rmsnorm_of_a_decode_step(K, H, n_parts):
