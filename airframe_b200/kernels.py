@@ -37,7 +37,19 @@ def _lib():
 
 
 def _stream() -> c_void_p:
-    return c_void_p(torch.cuda.current_stream().cuda_stream)
+    # the raw handle of the current stream of the current device (the Stream object of
+    # torch.cuda.current_stream() costs several microseconds a call, once per kernel launched)
+    return c_void_p(_raw_stream(_current_device()))
+
+
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_current_device = getattr(torch._C, "_cuda_getDevice", None)
+if _raw_stream is None or _current_device is None:          # an older or newer torch: the documented way
+    def _raw_stream(_index):                                 # noqa: F811
+        return torch.cuda.current_stream().cuda_stream
+
+    def _current_device():                                   # noqa: F811
+        return 0
 
 
 def _ptr(t, name="tensor", dtype=None, allow_none=False) -> c_void_p:
@@ -280,17 +292,18 @@ def gemm_tc_splits(M: int, N: int, K: int) -> int:
 
 
 def gemm_tc(out, x, w, cap: float = 0.0, splits: int = 1, gated: bool = False, activation: str = "gelu_tanh",
-            n_acc: int = 0) -> None:
+            n_acc: int = 0, checked: bool = False) -> None:
     """out = x @ w^T on the tcgen05 tensor cores (bfloat16 operands, 32-bit
     accumulation in TMEM).  splits > 1: out is float32 [splits, M, N] partial
     sums.  gated: w holds, per group of 32 rows, 16 gate rows then the 16 up
     rows of the same features (see ``interleave_gate_up``); out[m, f] =
     act(x . gate_f) * (x . up_f), N = rows / 2.  n_acc: weight tiles per block
-    (0: chosen from the sizes)."""
+    (0: chosen from the sizes).  ``checked``: the caller has asked
+    :func:`gemm_tc_supported` already."""
     M, K = x.shape
     rows = w.shape[0]
     N = rows // 2 if gated else rows
-    if not gemm_tc_supported(x, w, out):
+    if not checked and not gemm_tc_supported(x, w, out):
         raise KernelError("gemm_tc: operands must be bfloat16 with dense, 16-byte aligned rows and K % 8 == 0")
     if splits > 1:
         if out.dtype != torch.float32 or tuple(out.shape) != (splits, M, N) or not out.is_contiguous():

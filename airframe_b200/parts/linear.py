@@ -19,7 +19,7 @@ def linear(x, w, out_dtype=None, cap: float = 0.0, out=None):
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype or x.dtype, device=x.device)
     if kernels.gemm_tc_supported(x, w, out):
-        kernels.gemm_tc(out, x, w, cap)
+        kernels.gemm_tc(out, x, w, cap, checked=True)
     else:
         kernels.gemm_plain(out, x, w, cap)
     return out
@@ -46,8 +46,11 @@ def linear_split(x, w):
         splits = kernels.gemm_tc_splits(M, N, K)
         if splits > 1:
             parts = torch.empty(splits, M, N, dtype=torch.float32, device=x.device)
-            kernels.gemm_tc(parts, x, w, splits=splits)
+            kernels.gemm_tc(parts, x, w, splits=splits, checked=True)
             return PartialSums(parts)
+        out = torch.empty(M, N, dtype=x.dtype, device=x.device)
+        kernels.gemm_tc(out, x, w, checked=True)
+        return out
     return linear(x, w)
 
 

@@ -182,6 +182,8 @@ def prefill_shares(prefill_once, cfg, n_layers, pk) -> dict:
 
 
 def run_ours(args) -> dict:
+    global PROMPT_LEN
+    PROMPT_LEN = args.prompt_len
     import torch
     sys.path.insert(0, str(ROOT))
     from airframe_b200 import kernels
@@ -377,7 +379,7 @@ def run_ours(args) -> dict:
         prefill["shares_unavailable"] = str(why)[:120]
 
     return {
-        "metric": f"Gemma-2 {args.sizes.upper()} bf16 decode tokens/s at batch {B} (2,048-token prompts)",
+        "metric": f"Gemma-2 {args.sizes.upper()} bf16 decode tokens/s at batch {B} ({PROMPT_LEN:,}-token prompts)",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights N(0, 0.02), uniform random token ids",
@@ -411,6 +413,8 @@ def main() -> int:
                     help="run the layers of a decode step of up to 8 tokens as one kernel (opt-in path)")
     ap.add_argument("--phase-times", action="store_true",
                     help="print the phases of one fused decode step with their times and exit")
+    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
+                    help="tokens of every prompt, and of the prefill that is timed (not the default run)")
     ap.add_argument("--sizes", default="2b", choices=sorted(SIZES), help="layer sizes of this Gemma-2 model")
     args = ap.parse_args()
     if args.impl == "reference":
