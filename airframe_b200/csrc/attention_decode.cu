@@ -2,6 +2,9 @@
 // a step of few sequences still fills the GPU (it is bound by the bytes of K
 // and V it reads; every byte is read once).
 //
+// The sequences of a batch may differ much in length: a sequence's keys are cut into as many splits
+// (up to the grid's) as give every block about the same number of pages; blocks beyond a sequence's
+// splits leave at once.
 // Pass 1, grid (sequence, kv head, split): a block of two groups of 4 warps
 // walks its share of the sequence's cache pages, the groups taking alternate
 // pages (one warp per scheduler cannot hide the latency of its own chain of
@@ -56,7 +59,8 @@ struct DecodeArgs {
   int nq, nkv;
   float scale, cap;
   int window, ring_rows;
-  int n_splits;
+  int n_splits;    // at most this many splits of a sequence's keys (the stride of the partial results)
+  int batch, n_sms;
   float* part_o;   // [batch, nq, splits, HD]
   float* part_ml;  // [batch, nq, splits, 2]
   int* err;        // set to 1 when a bounded wait ran out
@@ -87,6 +91,42 @@ __device__ __forceinline__ uint32_t da_pack(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&v);
 }
 
+// Pages of the cache that sequence b's new token attends to: [first, last].
+__device__ __forceinline__ int da_pages(const int* slots, const int* lens, int b, int window, int* first_pp, int* last_pp) {
+  const int len = slots[b] >= 0 ? lens[b] : 0;
+  if (len <= 0) {
+    *first_pp = 0;
+    *last_pp = -1;
+    return 0;
+  }
+  const int pos = len - 1;
+  const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  *first_pp = lo / AF_PAGE;
+  *last_pp = pos / AF_PAGE;
+  return *last_pp - *first_pp + 1;
+}
+
+// Into how many splits sequence b's pages are cut (1..max_splits).  The sequences of a batch may differ
+// much in length: every block gets about the same number of pages, total pages / (SMs per row of the
+// grid), so a long sequence among short ones is cut into many splits and the short ones into one,
+// instead of the same number for all.  (The split and the merge kernel compute it alike.)
+__device__ __forceinline__ int da_splits_of(int total, int mine, int rows_of_grid, int n_sms, int max_splits) {
+  const int blocks = max(1, n_sms / max(1, rows_of_grid));       // blocks there are for one kv head of all sequences
+  const int target = max(1, (total + blocks - 1) / blocks);      // pages a block should get
+  return max(1, min(max_splits, (mine + target / 2) / target));
+}
+// The pages of all sequences of the batch, summed by the block's first warp into *total_s (shared memory);
+// the caller synchronises the block before it reads it.
+__device__ __forceinline__ void da_total_pages(const int* slots, const int* lens, int batch, int window, int* total_s) {
+  if (threadIdx.x < 32) {
+    int t = 0, f, l;
+    for (int i = threadIdx.x; i < batch; i += 32) t += da_pages(slots, lens, i, window, &f, &l);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
+    if (threadIdx.x == 0) *total_s = t;
+  }
+}
+
 template <int HD>
 __host__ __device__ constexpr int da_stages() { return HD >= 256 ? 3 : 4; }
 
@@ -115,7 +155,7 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   // page STAGES later (the other group's, in the same stage) must not share a barrier's phases
   constexpr int NBAR = 2 * STAGES;
   __shared__ uint64_t full[NBAR];
-  __shared__ int give_up_s;
+  __shared__ int give_up_s, total_pages_s;
   volatile int* give_up = &give_up_s;
 
   pdl_launch_dependents();
@@ -139,12 +179,18 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   const int pos = len - 1;
   const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
 
-  int pp_begin = 0, pp_end = 0;
-  const int last_pp = pos / AF_PAGE;  // the page of the new token, which the kernel before wrote
+  int pp_begin = 0, pp_end = 0, first_pp, last_pp;  // last_pp: the page of the new token, which the kernel before wrote
+  const int my_pages = da_pages(a.slots, a.lens, b, a.window, &first_pp, &last_pp);
+  int splits = 1;
+  if (a.n_splits > 1) {
+    da_total_pages(a.slots, a.lens, a.batch, a.window, &total_pages_s);
+    __syncthreads();
+    splits = da_splits_of(total_pages_s, my_pages, gridDim.y, a.n_sms, a.n_splits);
+  }
+  if (z >= splits) return;                          // (nothing of the block's is in flight yet)
   if (len > 0) {
-    const int first_pp = lo / AF_PAGE;
     const int n_pp = last_pp - first_pp + 1;
-    const int per = (n_pp + a.n_splits - 1) / a.n_splits;
+    const int per = (n_pp + splits - 1) / splits;
     pp_begin = first_pp + z * per;
     pp_end = min(pp_begin + per, last_pp + 1);
   }
@@ -353,11 +399,21 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
 template <int HD>
 __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long long out_stride,
                                          const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         int nq, int n_splits) {
+                                         int nq, int max_splits, const int* __restrict__ slots,
+                                         const int* __restrict__ lens, int window, int rows_of_grid, int n_sms) {
   pdl_launch_dependents();
-  pdl_wait();
   const int b = blockIdx.x, h = blockIdx.y;
-  const size_t p0 = ((size_t)b * nq + h) * n_splits;
+  const size_t p0 = ((size_t)b * nq + h) * max_splits;
+  // (slots and lengths are inputs of the step: the number of splits is worked out before the wait)
+  __shared__ int total_pages_s;
+  int first_pp, last_pp, n_splits = 1;
+  if (max_splits > 1) {
+    const int my_pages = da_pages(slots, lens, b, window, &first_pp, &last_pp);
+    da_total_pages(slots, lens, gridDim.x, window, &total_pages_s);
+    __syncthreads();
+    n_splits = da_splits_of(total_pages_s, my_pages, rows_of_grid, n_sms, max_splits);
+  }
+  pdl_wait();
   constexpr int FEW = 8;
   const int d = threadIdx.x;   // HD >= 128: threads 0..127 take d and d + 128 (HD 256)
   if (n_splits <= FEW) {
@@ -428,7 +484,8 @@ int launch_decode(DecodeArgs a, int batch, long long n_pages, cudaStream_t strea
   af_launch(attn_decode_split_kernel<HD>, grid, dim3(DA_THREADS), smem, stream, mk, mv, a);
   AF_COUNT_LAUNCH("af_attn_decode (split)");
   af_launch(attn_decode_merge_kernel<HD>, dim3(batch, a.nq), dim3(HD < 128 ? HD : 128), 0, stream, a.out,
-            a.out_stride, a.part_o, a.part_ml, a.nq, a.n_splits);
+            a.out_stride, (const float*)a.part_o, (const float*)a.part_ml, a.nq, a.n_splits, a.slots, a.lens, a.window,
+            (int)grid.y, a.n_sms);
   AF_CHECK_LAUNCH("af_attn_decode (merge)");
 }
 
@@ -474,6 +531,16 @@ AF_EXPORT int af_attn_decode(void* out, long long out_stride, const void* q, lon
   a.window = window;
   a.ring_rows = ring_rows;
   a.n_splits = n_splits;
+  a.batch = batch;
+  {
+    static int sms = 0;
+    if (sms == 0) {
+      int dev = 0;
+      cudaGetDevice(&dev);
+      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+    }
+    a.n_sms = sms > 0 ? sms : 148;
+  }
   a.part_o = scratch;
   a.part_ml = scratch + (size_t)batch * nq * n_splits * hd;
   a.err = err;

@@ -391,10 +391,24 @@ def attn_decode_splits(batch: int, nkv: int, max_len: int, window: int, blocks: 
     return max(1, min(want, pages, 64))
 
 
+def attn_decode_max_splits(batch: int, nkv: int, max_len: int, window: int, blocks: int = 148) -> int:
+    """The most splits the split kernel may give one sequence (the third extent
+    of its grid).  With sequences of equal lengths it uses
+    :func:`attn_decode_splits` of them; the room above that is for a long
+    sequence among short ones, up to three blocks an SM in all (a block without
+    a split of its own leaves at once, but the SMs start them one by one)."""
+    rows = min(max_len, window) if window else max_len
+    pages = max(1, (rows + PAGE - 1) // PAGE + (1 if window else 0))
+    units = max(1, batch * nkv)
+    return max(1, min(max(blocks // units, min(16, 3 * blocks // units)), pages, 64))
+
+
 def attn_decode_split(out, q, kcache, vcache, page_table, slots, lens, nq, nkv, hd, scale, cap, window, ring_rows,
                       n_splits: int, scratch=None) -> None:
     """bfloat16 decode attention, split over the keys (two kernels: partial
-    results into ``scratch``, then their merge)."""
+    results into ``scratch``, then their merge).  ``n_splits`` is the most
+    splits a sequence gets: the kernel cuts every sequence so that all blocks
+    get about the same number of cache pages."""
     B = q.shape[0]
     lib = _lib()
     lib.af_attn_decode_scratch.restype = ctypes.c_longlong
@@ -418,7 +432,7 @@ def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window) -> None:
     """Attention of a decode step over the cache: the split kernel for
     bfloat16 and head sizes it takes, else the plain kernel."""
     if q.dtype == torch.bfloat16 and _lib().af_attn_decode_supported(c_int(hd)):
-        n = attn_decode_splits(batch.n_seqs, nkv, batch.max_len_after, window)
+        n = attn_decode_max_splits(batch.n_seqs, nkv, batch.max_len_after, window)
         attn_decode_split(out, q, kv.k, kv.v, kv.page_table, batch.slots, batch.len_after, nq, nkv, hd, scale, cap,
                           window, kv.ring_rows, n)
         return

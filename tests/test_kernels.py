@@ -332,6 +332,31 @@ def test_attention_decode_over_pages(K, dtype, hd, nq, nkv, window, cap):
         close(out[b], ref, dtype, scale=1.0)
 
 
+@pytest.mark.parametrize("hd,nq,nkv,window", [(256, 8, 4, 0), (128, 6, 2, 0), (256, 4, 2, 300), (128, 16, 2, 1000)])
+def test_attention_decode_one_long_sequence_among_short_ones(K, hd, nq, nkv, window):
+    """The split kernel cuts every sequence by its own length: the long one into many splits, the short
+    ones into one; a key far back in the long one has to be found."""
+    dtype = torch.bfloat16
+    torch.manual_seed(hd + window)
+    lens = [3, 2500, 70, 1, 640, 129, 64]
+    scale = 1.0 / math.sqrt(hd)
+    q = torch.randn(len(lens), nq * hd).to(dtype)
+    ks = [(torch.randn(n, nkv, hd) * 0.3).to(dtype) for n in lens]
+    vs = [torch.randn(n, nkv, hd).to(dtype) for n in lens]
+    far = 2500 - 1 - (150 if window else 2100)
+    ks[1][far] = (q[1].float().reshape(nq, hd)[: nq // nkv].sum(0) * 6.0).to(dtype)     # the first kv group's heads score it high
+    out = _decode_case(K, dtype, hd, nq, nkv, window, 30.0, lens, q, ks, vs, scale)
+    for b, n in enumerate(lens):
+        qq = torch.zeros(n, nq, hd, dtype=torch.float64)
+        qq[-1] = q[b].double().reshape(nq, hd)
+        ref = plain.attention(qq, ks[b].double(), vs[b].double(), scale, 30.0, window or None)[-1]
+        close(out[b], ref, dtype, scale=1.0)
+    near = (out[1].double().cpu().reshape(nq, hd)[0] - vs[1][far, 0].double()).abs().max()
+    assert near < 0.1, float(near)
+    assert K.attn_decode_max_splits(7, nkv, 2500, window) >= K.attn_decode_splits(7, nkv, 2500, window)
+    assert K.attn_decode_max_splits(8, 4, 8192, 0) > K.attn_decode_splits(8, 4, 8192, 0)
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_attention_finds_one_far_key_and_the_window_edge(K, dtype):
     """Random keys would hide a lost row among hundreds: one key is made to
