@@ -15,7 +15,8 @@ const char* af_last_error(void);
 long long af_attn_decode_scratch(int batch, int nq, int hd, int n_splits);
 
 // Decode attention over the paged bfloat16 cache (see attention_decode.cu).
-// `scratch` is the caller's: af_attn_decode_scratch(...) floats of device memory.
+// `scratch` is the caller's: af_attn_decode_scratch(...) floats of device memory.  n_splits is the most
+// splits a sequence's keys are cut into (the kernel cuts each sequence by its length).
 int af_attn_decode(void* out, long long out_stride, const void* q, long long q_stride, const void* kcache,
                    const void* vcache, long long n_pages, const int* page_table, int max_pages, const int* slots,
                    const int* lens, int batch, int nq, int nkv, int hd, float scale, float cap, int window,

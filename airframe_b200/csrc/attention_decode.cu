@@ -502,7 +502,8 @@ AF_EXPORT long long af_attn_decode_scratch(int batch, int nq, int hd, int n_spli
 // out [batch, nq * hd] bfloat16 = attention of one new token per sequence over
 // its cache (lens[b] counts the new token, which the cache holds already).
 // The cache of the layer holds n_pages pages [kv heads][64][hd].  scratch:
-// af_attn_decode_scratch(...) floats.  Sequences with slot < 0 give zeros.
+// af_attn_decode_scratch(...) floats.  Sequences with slot < 0 give zeros.  n_splits: the most splits
+// of a sequence's keys (the third extent of the grid).
 AF_EXPORT int af_attn_decode(void* out, long long out_stride, const void* q, long long q_stride,
                              const void* kcache, const void* vcache, long long n_pages, const int* page_table,
                              int max_pages, const int* slots, const int* lens, int batch, int nq, int nkv, int hd,
