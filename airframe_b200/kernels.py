@@ -440,8 +440,6 @@ def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window) -> None:
                       scale, cap, window, kv.ring_rows)
 
 
-__all__ = [n for n in dir() if not n.startswith("_")]
-
 
 # ---------------------------------------------------------------- the layers of a decode step as one kernel
 
@@ -479,3 +477,6 @@ def decode_layers(prog, x, positions, slots, len_after, n_phases=None, trace=Non
         _ptr(prog.part_ml, "part_ml", torch.float32), _ptr(positions, "positions", i32),
         _ptr(slots, "slots", i32), _ptr(len_after, "len_after", i32), _ptr(prog.sync, "sync", i32),
         _ptr(error_word(x.device), "err", i32), _ptr(trace, "trace", torch.int64, allow_none=True), _stream()))
+
+
+__all__ = [n for n in dir() if not n.startswith("_")]
