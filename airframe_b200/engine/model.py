@@ -99,7 +99,9 @@ class Model:
         needs = {cache.views[i].kv.need for i in range(len(sched)) if cache.views[i].kv is not None}
         shape = tuple(sorted(kernels.attn_decode_splits(batch.n_tokens, n.num_kv_heads, batch.max_len_after,
                                                         n.window or 0) for n in needs))
-        key = (batch.n_tokens, id(cache), shape)
+        # (a token of the cache's own stands for it: an id could be used again once a cache is gone, and a
+        # program points into its cache's memory)
+        key = (batch.n_tokens, cache.__dict__.setdefault("_program_key", object()), shape)
         if key not in self._programs:
             prog = None
             try:
