@@ -98,3 +98,19 @@ def test_sizes_the_one_kernel_step_refuses_run_as_a_chain(tmp_path):
     got = replay.run_tail(rt, ids, 8)
     assert rel_err(got, plain.logits(cfg, w, ids)) < VS_PLAIN["bfloat16"]
     assert not fused_programs(rt) and "head_dim" in rt.engine.model.not_fused_because
+
+
+def test_decode_attention_split_counts():
+    """The grid's third extent: the count that equal lengths use, with room above it for a long
+    sequence among short ones, never more than the pages there are."""
+    from airframe_b200 import kernels as K
+    for batch, nkv in ((1, 4), (8, 4), (16, 4), (16, 8), (64, 4), (128, 16)):
+        for ctx, window in ((8192, 0), (2048, 4096), (100, 0), (8192, 512)):
+            equal = K.attn_decode_splits(batch, nkv, ctx, window)
+            most = K.attn_decode_max_splits(batch, nkv, ctx, window)
+            rows = min(ctx, window) if window else ctx
+            pages = (rows + 63) // 64 + (1 if window else 0)
+            assert 1 <= equal <= most <= max(1, min(pages, 64))
+            assert batch * nkv * most <= max(3 * 148, batch * nkv * equal, batch * nkv)
+    assert K.attn_decode_max_splits(8, 4, 8192, 0) == 13 and K.attn_decode_splits(8, 4, 8192, 0) == 4
+    assert K.attn_decode_max_splits(64, 4, 8192, 0) == 1
