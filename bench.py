@@ -11,8 +11,8 @@ tokens a second, timed with CUDA events around exactly K steps after W warm-up
 steps (default 32: the first 30 or so steps after a burst of prompts run at
 lowered clocks, about 2.1 ms instead of 1.8).  ``e2e`` is the same through
 ``GpuRuntime.generate`` with host token lists in and out, prompts' aftermath included.  The line also carries
-the prefill rate of 2,048 tokens with its fraction of the bf16 peak (and the same for its
-products and its attention kernels apart, from their summed kernel times), the decode
+the prefill rate of 2,048 tokens with its fraction of the bf16 peak (and, under ``profiled``,
+the same for its products and its attention kernels apart, from a run under a profiler), the decode
 step's fraction of the HBM roofline, decode at batch 1 and 64, the clocks seen
 during the timed region and the number of this library's kernels launched in it.
 Every decode step reads all weights (5.2 GB), far more than the 126 MB L2, so
@@ -374,9 +374,11 @@ def run_ours(args) -> dict:
 
     # (last, so that the launches before it come in the same order with and without it)
     try:
-        prefill.update(prefill_shares(prefill_once, cfg_dict, n_layers, pk))
-    except Exception as why:        # a profiler that cannot attach (another one is attached already) costs only these two keys
-        prefill["shares_unavailable"] = str(why)[:120]
+        prefill["profiled"] = dict(prefill_shares(prefill_once, cfg_dict, n_layers, pk),
+                                   note="kernel times of one more prefill under the CUDA profiler of PyTorch, "
+                                        "not timed with events like the figures beside it")
+    except Exception as why:        # a profiler that cannot attach (another one is attached already) costs only this key
+        prefill["profiled"] = {"unavailable": str(why)[:120]}
 
     return {
         "metric": f"Gemma-2 {args.sizes.upper()} bf16 decode tokens/s at batch {B} ({PROMPT_LEN:,}-token prompts)",
