@@ -11,10 +11,8 @@ from __future__ import annotations
 
 import torch
 
-import os
-
 from ..config.base import ModelSpec
-from ..parts import BuildContext, NotFusable, build_part
+from ..parts import BuildContext, build_part
 
 
 def _build_layers(spec: ModelSpec, ctx: BuildContext):
@@ -37,11 +35,6 @@ class Model:
         self.final_norm = build_part("norm", spec.final_norm, self.ctx)
         self.head = build_part("head", spec.head, self.ctx)
         self.loaded = False
-        # opt-in (it is slower than the chain of kernels at the sizes measured so far): decode steps of
-        # few tokens run as one kernel when every layer can say its step in phases
-        self.fuse_decode = os.environ.get("AIRFRAME_B200_FUSE_DECODE", "0") == "1"
-        self._programs: dict = {}
-        self.not_fused_because = None
 
     # ------------------------------------------------------------------ weights
 
@@ -84,48 +77,9 @@ class Model:
 
     # ------------------------------------------------------------------ forward
 
-    def layer_program(self, batch, cache):
-        """The one-kernel form of this decode step's layers, or None (then
-        ``not_fused_because`` says why).  Programs are kept per step shape."""
-        if (not self.fuse_decode or batch.is_prefill or self.ctx.compute_dtype != torch.bfloat16
-                or self.ctx.device.type != "cuda"):
-            return None
-        from .. import kernels
-        from .layer_program import LayerProgram
-        if batch.n_tokens > kernels.decode_layers_limits()["tokens"]:
-            return None
-        # the number of splits of the keys depends on the longest sequence: steps of one shape share a program
-        sched = self.spec.schedule
-        needs = {cache.views[i].kv.need for i in range(len(sched)) if cache.views[i].kv is not None}
-        shape = tuple(sorted(kernels.attn_decode_splits(batch.n_tokens, n.num_kv_heads, batch.max_len_after,
-                                                        n.window or 0) for n in needs))
-        # (a token of the cache's own stands for it: an id could be used again once a cache is gone, and a
-        # program points into its cache's memory)
-        key = (batch.n_tokens, cache.__dict__.setdefault("_program_key", object()), shape)
-        if key not in self._programs:
-            prog = None
-            try:
-                b = LayerProgram(batch.n_tokens, self.spec.hidden_size, self.ctx.device, batch.max_len_after)
-                first = self.blocks[sched[0].layer].first_norm()
-                if first is None:
-                    raise NotFusable("the first layer does not start with a norm")
-                b.norm(0, None, first)
-                for i, e in enumerate(sched):
-                    nxt = self.blocks[sched[i + 1].layer].first_norm() if i + 1 < len(sched) else None
-                    self.blocks[e.layer].emit_decode(b, cache.views[i], nxt)
-                prog = b.finish()
-            except NotFusable as why:
-                self.not_fused_because = str(why)
-            self._programs[key] = prog
-        return self._programs[key]
-
     def hidden(self, batch, cache) -> torch.Tensor:
         """The float32 residual stream [T, H] after all scheduled runs."""
         x = self.embedding.forward(batch.tokens)
-        prog = self.layer_program(batch, cache)
-        if prog is not None:
-            prog.run(x, batch)
-            return x
         sched = self.spec.schedule
         normed = None
         for i, e in enumerate(sched):

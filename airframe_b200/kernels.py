@@ -441,42 +441,5 @@ def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window) -> None:
 
 
 
-# ---------------------------------------------------------------- the layers of a decode step as one kernel
-
-def decode_layers_limits() -> dict:
-    """What the one-kernel decode step is built for."""
-    f = _lib().af_decode_layers_limit
-    return {"tokens": f(c_int(0)), "k_part": f(c_int(1)), "stage_columns": f(c_int(2)), "attn_bytes": f(c_int(3)),
-            "words": f(c_int(4))}
-
-
-def tensor_map_bf16(t, rows: int, cols: int, box_rows: int) -> bytes:
-    """The 128-byte TMA descriptor of the bfloat16 matrix [rows, cols] that starts
-    at ``t``'s first element, with boxes of 64 columns x ``box_rows`` rows."""
-    if t.dtype != torch.bfloat16 or not t.is_cuda or not t.is_contiguous():
-        raise KernelError("tensor_map_bf16: a contiguous bfloat16 CUDA tensor is needed")
-    if rows * cols > t.numel():
-        raise KernelError("tensor_map_bf16: the matrix is larger than the tensor")
-    buf = ctypes.create_string_buffer(128)
-    _check(_lib().af_tensor_map_bf16(buf, _ptr(t), c_longlong(rows), c_longlong(cols), c_longlong(cols),
-                                     c_int(box_rows)))
-    return buf.raw
-
-
-def decode_layers(prog, x, positions, slots, len_after, n_phases=None, trace=None) -> None:
-    """Runs a :class:`~airframe_b200.engine.layer_program.LayerProgram` on the
-    residual stream x (float32 [tokens, width], in place); ``n_phases`` stops it
-    early; ``trace`` (int64 [blocks, phases, 8]) receives, per block and phase,
-    when it began, when its work ended, and marks inside it (nanoseconds)."""
-    i32 = torch.int32
-    _check(_lib().af_decode_layers(
-        _ptr(prog.d_phases, "phases", i32), c_int(n_phases or prog.n_phases), _ptr(prog.d_attn, "attn", i32),
-        _ptr(prog.d_maps, "maps", torch.uint8), c_int(prog.n_tok), c_int(prog.hidden), c_int(prog.head_dim),
-        c_int(prog.n_blocks), _ptr(x, "x", torch.float32), _ptr(prog.normed), _ptr(prog.attn_out), _ptr(prog.gated),
-        _ptr(prog.q), _ptr(prog.parts, "parts", torch.float32), _ptr(prog.part_o, "part_o", torch.float32),
-        _ptr(prog.part_ml, "part_ml", torch.float32), _ptr(positions, "positions", i32),
-        _ptr(slots, "slots", i32), _ptr(len_after, "len_after", i32), _ptr(prog.sync, "sync", i32),
-        _ptr(error_word(x.device), "err", i32), _ptr(trace, "trace", torch.int64, allow_none=True), _stream()))
-
 
 __all__ = [n for n in dir() if not n.startswith("_")]

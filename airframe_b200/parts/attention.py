@@ -15,7 +15,7 @@ import torch
 from .. import kernels
 from ..config.base import ConfigError, PartSpec
 from ..weights.loader import WeightDecl
-from .base import KVNeed, Mixer, NotFusable, build_part, register_part
+from .base import KVNeed, Mixer, build_part, register_part
 from .linear import PartialSums, linear_split
 
 
@@ -67,16 +67,6 @@ class Attention(Mixer):
         self.w_qkv = torch.cat([weights[q], weights[k], weights[v]], dim=0).to(dt).contiguous()
         self.w_o = weights[o].to(dt).contiguous()
         self.position.load(weights)
-
-    def emit_decode(self, prog, view) -> int:
-        if not view.writes:
-            raise NotFusable("a run that reads another run's cache")
-        e = prog.attention_entry(self.nq, self.nkv, self.hd, self.window or 0, view.kv, self.scale, self.softcap,
-                                 self.position.fused_rotary(self.hd))
-        qkv = prog.gemv(self.w_qkv, "normed", "rope", attn=e, heads=self.nq + 2 * self.nkv)
-        prog.attention(e, written_by=qkv)
-        prog.merge(e)
-        return prog.gemv(self.w_o, "attn_out", "parts")
 
     def forward(self, x, batch, view):
         nq, nkv, hd = self.nq, self.nkv, self.hd

@@ -84,11 +84,6 @@ class StateNeed:
 # interfaces
 # --------------------------------------------------------------------------
 
-class NotFusable(Exception):
-    """A part cannot express its decode step as phases of the one-kernel
-    layer program (``engine/layer_program.py``); the step then runs kernel by kernel."""
-
-
 class Part:
     """Base of all parts.
 
@@ -132,11 +127,6 @@ class Norm(Part):
         also returns then.forward(x) in ``out_dtype``."""
         raise NotImplementedError
 
-    def fused_params(self):
-        """(weight float32 [H], eps, weight offset) when the norm is
-        y = x * rsqrt(mean(x^2) + eps) * (offset + w), for the layer program."""
-        raise NotFusable(f"norm '{self.kind}' has no form for the layer program")
-
 
 class PositionEncoding(Part):
     """Applied by a mixer to its packed query/key/value rows."""
@@ -147,12 +137,6 @@ class PositionEncoding(Part):
         k and v in the cache.  ``parts`` (float32 [S, T, width]), when given,
         are split-K partial sums of the rows: their sum is written to ``qkv`` first."""
         raise NotImplementedError
-
-    def fused_rotary(self, hd: int):
-        """float32 [hd / 2] inverse frequencies when the encoding is a rotation
-        of the pairs (i, i + hd / 2) of every q and k head by position * frequency,
-        for the layer program."""
-        raise NotFusable(f"position encoding '{self.kind}' has no form for the layer program")
 
 
 class Mixer(Part):
@@ -170,21 +154,11 @@ class Mixer(Part):
         ``view`` the layer's :class:`~airframe_b200.cache.LayerCacheView`."""
         raise NotImplementedError
 
-    def emit_decode(self, prog, view) -> int:
-        """Append this mixer's decode step to the layer program ``prog`` (its
-        input is the ``normed`` buffer); returns the number of partial sums its
-        last product leaves for the residual sum."""
-        raise NotFusable(f"mixer '{self.kind}' has no form for the layer program")
-
 
 class FeedForward(Part):
     def forward(self, x, batch):
         """x [T, H] compute dtype -> [T, H] compute dtype."""
         raise NotImplementedError
-
-    def emit_decode(self, prog) -> int:
-        """As :meth:`Mixer.emit_decode`."""
-        raise NotFusable(f"feed-forward '{self.kind}' has no form for the layer program")
 
 
 class Block(Part):
@@ -223,9 +197,3 @@ class Block(Part):
         Returns next_pre.forward(x) in the compute dtype when ``next_pre`` (the
         next layer's first norm) is given, else None."""
         raise NotImplementedError
-
-    def emit_decode(self, prog, view, next_pre) -> None:
-        """Append this layer's decode step to the layer program ``prog``: on
-        entry the ``normed`` buffer holds first_norm()(x); on exit x is updated
-        and ``normed`` holds next_pre(x) (when given)."""
-        raise NotFusable(f"block '{self.kind}' has no form for the layer program")

@@ -36,11 +36,6 @@ class SandwichBlock(Block):
     def first_norm(self):
         return self.norms["pre_mixer"]
 
-    def emit_decode(self, prog, view, next_pre) -> None:
-        n = self.norms
-        prog.norm(self.mixer.emit_decode(prog, view), n["post_mixer"], n["pre_feed_forward"])
-        prog.norm(self.feed_forward.emit_decode(prog), n["post_feed_forward"], next_pre)
-
 
 @register_part("block", "prenorm")
 class PreNormBlock(Block):

@@ -11,7 +11,7 @@ import torch
 from .. import kernels
 from ..config.base import ConfigError
 from ..weights.loader import WeightDecl
-from .base import FeedForward, NotFusable, register_part
+from .base import FeedForward, register_part
 from .linear import gated_linear, linear_split
 
 
@@ -50,12 +50,6 @@ class GatedMlp(FeedForward):
         self.w_gu = (kernels.interleave_gate_up(wg, wu) if self.interleaved
                      else torch.cat([wg, wu], dim=0).contiguous())
         self.w_down = weights[d].to(dt).contiguous()
-
-    def emit_decode(self, prog) -> int:
-        if not self.interleaved:
-            raise NotFusable("the gate and up rows are not in the gated layout")
-        prog.gemv(self.w_gu, "normed", "gated", out_rows=self.inter, activation=self.activation)
-        return prog.gemv(self.w_down, "gated", "parts")
 
     def forward(self, x, batch):
         h = gated_linear(x, self.w_gu, self.inter, self.activation, self.interleaved)

@@ -36,9 +36,6 @@ class RmsNorm(Norm):
         # statistics and the (offset + w) factor are 32-bit in both precisions
         self.w = weights[self.name].to(torch.float32).contiguous()
 
-    def fused_params(self):
-        return self.w, self.eps, self.offset
-
     def forward(self, x, out_dtype, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]
         y = torch.empty(n, self.size, dtype=out_dtype, device=x.device)

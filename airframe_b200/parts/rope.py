@@ -41,11 +41,6 @@ class Rope(PositionEncoding):
     def load(self, weights):
         self.inv_freq = self._inv_freq_host.to(self.ctx.device)
 
-    def fused_rotary(self, hd: int):
-        if self.pairing != "half" or self.rotary_dim != hd:
-            return super().fused_rotary(hd)
-        return self.inv_freq
-
     def encode_and_store(self, qkv, batch, nq, nkv, hd, kv, parts=None):
         if self.rotary_dim > hd:
             raise ConfigError(f"rope: rotary_dim {self.rotary_dim} exceeds head_dim {hd}")

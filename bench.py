@@ -204,7 +204,6 @@ def run_ours(args) -> dict:
     rt = GpuRuntime.random(cfg, seed=0, dtype="bfloat16", max_tokens=budget, max_context=CONTEXT,
                            max_sequences=max_b, on_device=True)
     eng = rt.engine
-    eng.model.fuse_decode = bool(args.fused_decode or args.phase_times)
     dev = eng.device
     V = cfg.vocab_size
     greedy = SamplingParams(max_tokens=1, temperature=0.0, repetition_penalty=1.0, ignore_eos=True)
@@ -238,30 +237,7 @@ def run_ours(args) -> dict:
         t0 = evs[first].time_range.start
         return [(e.time_range.start - t0, e.time_range.end - e.time_range.start, e.name) for e in evs[first:]]
 
-    def phase_times(batch):
-        """The one-kernel decode step (--fused-decode) once more on the last step's inputs, with its
-        per-block, per-phase clock marks: begin and duration of each phase over all blocks (us)."""
-        model = eng.model
-        g = eng._graphs[eng.padded_batch(batch)]
-        sb = g["batch"]
-        prog = next(p for p in model._programs.values() if p is not None and p.n_tok == sb.n_tokens)
-        x = model.embedding.forward(sb.tokens)
-        trace = torch.zeros(prog.n_blocks, prog.n_phases, 8, dtype=torch.int64, device=dev)
-        kernels.decode_layers(prog, x, sb.positions, sb.slots, sb.len_after, trace=trace)
-        torch.cuda.synchronize()
-        t = trace.cpu().double()
-        t = (t - t[:, 0, 0].min()) / 1e3
-        names = {0: "product", 1: "attention", 2: "merge", 3: "norm"}
-        eps = {0: "partial sums", 1: "rotary, q and cache", 2: "gated"}
-        rows = []
-        for i, w in enumerate(prog.phases):
-            nxt = float(t[:, i + 1, 0].max()) if i + 1 < prog.n_phases else float(t[:, i, 1].max())
-            what = names[w[0]] + (f" ({eps[w[6]]}; {w[3]} tiles x {w[4]} K parts)" if w[0] == 0 else "")
-            rows.append((float(t[:, i, 0].min()), float(t[:, i, 1].median()) - float(t[:, i, 0].min()),
-                         float(t[:, i, 1].max()) - float(t[:, i, 0].min()), nxt - float(t[:, i, 0].min()), what))
-        return rows
-
-    def decode_rate(batch, steps, warm, clocks=None, timeline=None, after=None):
+    def decode_rate(batch, steps, warm, clocks=None, timeline=None):
         """tokens/s, ms/step and launches of `steps` decode steps at `batch` after 2,048-token prompts."""
         sampler = Sampler(V, dev)
         states = [sampler.new_state(greedy, i) for i in range(batch)]
@@ -292,8 +268,6 @@ def run_ours(args) -> dict:
             state["pending"].result()
             launches = kernels.launch_count() + eng.replayed_launches - n0
             lens = [eng.length(s) for s in slots]
-            if after is not None:
-                after()
             return batch * steps / (ms / 1e3), ms / steps, launches, lens
         finally:
             for s in slots:
@@ -315,15 +289,6 @@ def run_ours(args) -> dict:
     pf_flops = prefill_flops(cfg_dict, n_layers, PROMPT_LEN, 1)
     prefill = {"value": PROMPT_LEN / (pf_ms / 1e3), "tokens": PROMPT_LEN, "ms": pf_ms,
                "frac": pf_flops / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
-
-    if args.phase_times:
-        out = []
-        decode_rate(B, 4, W, after=lambda: out.extend(phase_times(B)))
-        print(f"# the one-kernel decode step, batch {B}, {n_layers} layers: phase, begin us, work done in the median "
-              "block / in the last block, all blocks past the barrier (from begin, us), what")
-        for i, (t0, med, last, dur, what) in enumerate(out):
-            print(f"{i:4d} {t0:9.2f} {med:7.2f} {last:7.2f} {dur:7.2f}  {what}")
-        return None
 
     if args.timeline:
         tl = []
@@ -391,7 +356,6 @@ def run_ours(args) -> dict:
                    "kv_heads": cfg_dict["num_key_value_heads"], "head_dim": cfg_dict["head_dim"],
                    "intermediate": cfg_dict["intermediate_size"], "vocab": cfg_dict["vocab_size"],
                    "sliding_window": cfg_dict["sliding_window"], "sampling": "greedy on device",
-                   "decode_layers": "one kernel" if eng.model.fuse_decode else "kernel chain",
                    "l2": f"inputs larger than L2 (weights {model_bytes(cfg_dict, n_layers) / 1e9:.1f} GB per step)"},
         "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
         "gpu_launches": launches, "clocks": clock_info, "impl": "ours",
@@ -411,10 +375,6 @@ def main() -> int:
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--timeline", action="store_true",
                     help="print the kernels of one decode step with their start and duration, then exit")
-    ap.add_argument("--fused-decode", action="store_true",
-                    help="run the layers of a decode step of up to 8 tokens as one kernel (opt-in path)")
-    ap.add_argument("--phase-times", action="store_true",
-                    help="print the phases of one fused decode step with their times and exit")
     ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
                     help="tokens of every prompt, and of the prefill that is timed (not the default run)")
     ap.add_argument("--sizes", default="2b", choices=sorted(SIZES), help="layer sizes of this Gemma-2 model")

@@ -67,13 +67,12 @@ ODD_G = {
     "torch_dtype": "bfloat16",
 }
 
-# small sizes that the one-kernel decode step takes (head size 128, widths that are multiples of 64):
-# three query heads on one kv head, K parts of 128 and 64 columns, a window whose ring wraps
-FUSE_H = dict(WIDE_D, num_hidden_layers=3, hidden_size=192, num_attention_heads=3, num_key_value_heads=1,
+# small sizes with head size 128: three query heads on one kv head, a window whose ring wraps
+SMALL_H = dict(WIDE_D, num_hidden_layers=3, hidden_size=192, num_attention_heads=3, num_key_value_heads=1,
               head_dim=128, intermediate_size=320, vocab_size=500, sliding_window=70, query_pre_attn_scalar=100,
               attn_logit_softcapping=20.0, rms_norm_eps=1e-5, rope_theta=5000.0)
 
-CONFIGS = {"H": FUSE_H, "A": TINY_A, "B": TINY_B, "C": TINY_C, "D": WIDE_D, "E": WIDE_E, "F": WIDE_F, "G": ODD_G}
+CONFIGS = {"H": SMALL_H, "A": TINY_A, "B": TINY_B, "C": TINY_C, "D": WIDE_D, "E": WIDE_E, "F": WIDE_F, "G": ODD_G}
 
 
 def make_folder(cfg_dict, seed=0, store_dtype=None, root=None):
