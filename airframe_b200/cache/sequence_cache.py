@@ -141,6 +141,12 @@ class SequenceCache:
     cache_from | None)``.  ``max_tokens`` is the most tokens live sequences
     hold together, each rounded up to whole pages; ``max_context`` the longest
     single sequence.  With ``device=None`` only the bookkeeping exists.
+
+    ``max_sequences`` bounds the slots.  A group with a window never holds
+    more than its ring of a sequence, so it gets ``slots x ring`` pages when
+    that is less than ``max_tokens``: the saving of memory that the ring is
+    for shows only when the caller names the most sequences it will hold at a
+    time (by default there are as many slots as pages, and no saving).
     """
 
     def __init__(self, needs, max_tokens: int, max_context: int, dtype=torch.bfloat16, device=None,
@@ -249,6 +255,14 @@ class SequenceCache:
     def flush(self) -> None:
         for g in self.groups.values():
             g.flush()
+
+    def fits(self, token_counts) -> bool:
+        """Whether sequences that come to hold these many tokens fit together:
+        a slot each, and in every group the pages they hold there (a group with
+        a window holds at most its ring of a sequence)."""
+        if len(token_counts) > self.n_slots:
+            return False
+        return all(sum(pages_for(g.rows_held(n)) for n in token_counts) <= g.n_pages for g in self.groups.values())
 
     # ------------------------------------------------------------------ figures
 

@@ -13,6 +13,10 @@ in which something is wanted, ``DIR/<step>.f32`` receives the logits at the
 wanted places, in the order of the entries and of ``want``, as little-endian
 32-bit floats [wanted, vocab].  After every step a line ``done <step>`` is
 printed and flushed.  Requests named in ``end`` give back what they hold.
+With ``--layers``, a step in which something is wanted also writes
+``DIR/<step>.layers.json``: per scheduled run of a layer, for every wanted row of
+the residual stream, its RMS, first 20 values and bit-sum checksum (the
+localizer of :mod:`airframe_b200.engine.probe`; such steps run kernel by kernel).
 
 Reference: the fixture-driven replays (``src/runtime/multi_token_engine.rs:199-205``,
 ``src/bin/invariant_probe.rs:1-20``) and the one-token-at-a-time trace of
@@ -34,6 +38,8 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     ap.add_argument("--max-tokens", type=int, required=True,
                     help="most tokens live requests hold at any time (each rounded up to 64)")
     ap.add_argument("--device", default="cuda:0")
+    ap.add_argument("--layers", action="store_true",
+                    help="also write <step>.layers.json: per layer RMS, first values and checksum of the wanted rows")
     args = ap.parse_args(argv)
     stdin = stdin or sys.stdin
     stdout = stdout or sys.stdout
@@ -41,7 +47,7 @@ def main(argv=None, stdin=None, stdout=None) -> int:
     import torch
     from .. import kernels
     from ..config import config_from_folder
-    from ..engine import GpuRuntime, StepEntry
+    from ..engine import GpuRuntime, LayerProbe, StepEntry
 
     out_dir = Path(args.out)
     out_dir.mkdir(parents=True, exist_ok=True)
@@ -66,7 +72,12 @@ def main(argv=None, stdin=None, stdout=None) -> int:
                 entries.append(StepEntry(slots[rid], [int(t) for t in e["tokens"]],
                                          [int(w) for w in e.get("want", [])]))
             if entries:
-                logits = rt.step(entries)
+                probe = LayerProbe() if args.layers and any(e.want for e in entries) else None
+                logits = rt.step(entries, probe=probe)
+                if probe is not None:
+                    tmp = out_dir / f"{step}.layers.json.tmp"
+                    tmp.write_text(json.dumps(probe.to_json()))
+                    tmp.replace(out_dir / f"{step}.layers.json")
                 if logits is not None:
                     data = logits.to(torch.float32).contiguous().cpu().numpy().astype("<f4", copy=False)
                     tmp = out_dir / f"{step}.f32.tmp"

@@ -65,9 +65,13 @@ class KeyReader:
             raise ConfigError(f"{self.where}: key '{key}' must be > 0, got {v}")
         return v
 
-    def optional_number(self, key: str, default: Optional[float]) -> Optional[float]:
-        """A number, or ``None`` when the key is null; ``default`` when absent."""
+    def optional_number(self, key: str, default=_MISSING) -> Optional[float]:
+        """A number, or ``None`` when the key is null.  An absent key gives
+        ``default``; without one the key must be there (null is an answer,
+        silence is not)."""
         if key not in self.data:
+            if default is _MISSING:
+                raise ConfigError(f"{self.where}: required key '{key}' is missing (write null to switch it off)")
             return default
         if self.data[key] is None:
             return None

@@ -89,8 +89,10 @@ class Gemma2Config(ModelConfig):
             max_position_embeddings=r.integer("max_position_embeddings", minimum=1),
             sliding_window=r.integer("sliding_window", minimum=1),
             query_pre_attn_scalar=r.number("query_pre_attn_scalar", float(hd), positive=True),
-            attn_logit_softcapping=r.optional_number("attn_logit_softcapping", None),
-            final_logit_softcapping=r.optional_number("final_logit_softcapping", None),
+            # no value of its own stands here for a cap: the key says a number or null (off); a folder
+            # that leaves it out is refused rather than run with another model's logits
+            attn_logit_softcapping=r.optional_number("attn_logit_softcapping"),
+            final_logit_softcapping=r.optional_number("final_logit_softcapping"),
             hidden_activation=act,
             tie_word_embeddings=r.boolean("tie_word_embeddings", True),
             layer_types=layer_types,
@@ -126,6 +128,9 @@ class Gemma2Config(ModelConfig):
         eos = d.pop("eos_token_ids")
         d["eos_token_id"] = eos[0] if len(eos) == 1 else (eos or None)
         d["hidden_act"] = self.hidden_activation
+        # other readers of this layout want an integer here when the value is one
+        if float(self.query_pre_attn_scalar).is_integer():
+            d["query_pre_attn_scalar"] = int(self.query_pre_attn_scalar)
         return d
 
     # ----------------------------------------------------------------------

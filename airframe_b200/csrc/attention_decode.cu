@@ -414,6 +414,10 @@ __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long l
     n_splits = da_splits_of(total_pages_s, my_pages, rows_of_grid, n_sms, max_splits);
   }
   pdl_wait();
+  // (the number of splits is known before the wait and the loads below depend on nothing else: without
+  // this the compiler may move them, through the const __restrict__ pointers, above the wait)
+  part_o = pdl_fresh(part_o);
+  part_ml = pdl_fresh(part_ml);
   constexpr int FEW = 8;
   const int d = threadIdx.x;   // HD >= 128: threads 0..127 take d and d + 128 (HD 256)
   if (n_splits <= FEW) {
@@ -466,12 +470,15 @@ int launch_decode(DecodeArgs a, int batch, long long n_pages, cudaStream_t strea
   const size_t stage_bytes = (size_t)da_stages<HD>() * 2 * AF_PAGE * HD * 2;
   const size_t merge_bytes = (size_t)DA_WARPS * 16 * HD * sizeof(float);
   const size_t smem = (stage_bytes > merge_bytes ? stage_bytes : merge_bytes) + 1024;
-  static bool configured = false;
-  if (!configured) {
+  // (the limit on dynamic shared memory is a device's: set once on each)
+  static bool configured[AF_MAX_DEVICES] = {};
+  const int dev__ = af_current_device();
+  if (dev__ < 0) return -1;
+  if (!configured[dev__]) {
     cudaError_t e = cudaFuncSetAttribute(attn_decode_split_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return af_fail((int)e, "af_attn_decode: %s", cudaGetErrorString(e));
-    configured = true;
+    configured[dev__] = true;
   }
   // the cache of one layer as a matrix [pages * kv heads * 64 rows, HD]; boxes of 64 rows x 64 columns
   CUtensorMap mk, mv;
@@ -533,15 +540,8 @@ AF_EXPORT int af_attn_decode(void* out, long long out_stride, const void* q, lon
   a.ring_rows = ring_rows;
   a.n_splits = n_splits;
   a.batch = batch;
-  {
-    static int sms = 0;
-    if (sms == 0) {
-      int dev = 0;
-      cudaGetDevice(&dev);
-      cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
-    }
-    a.n_sms = sms > 0 ? sms : 148;
-  }
+  a.n_sms = af_sm_count();
+  if (a.n_sms <= 0) return -1;
   a.part_o = scratch;
   a.part_ml = scratch + (size_t)batch * nq * n_splits * hd;
   a.err = err;

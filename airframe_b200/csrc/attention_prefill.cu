@@ -275,11 +275,14 @@ template <int HD>
 int launch_prefill(const PrefillArgs& a, int n_seqs, int max_len, cudaStream_t stream) {
   constexpr int PF_BM = PfShape<HD>::BM, PF_BN = PfShape<HD>::BN;
   const int smem = PF_BM * HD * 2 + 4 * PF_BN * HD * 2;
-  static bool configured = false;
-  if (!configured) {
+  // (the limit on dynamic shared memory is a device's: set once on each)
+  static bool configured[AF_MAX_DEVICES] = {};
+  const int dev__ = af_current_device();
+  if (dev__ < 0) return -1;
+  if (!configured[dev__]) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_mma_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return af_fail((int)e, "af_attn_prefill: %s", cudaGetErrorString(e));
-    configured = true;
+    configured[dev__] = true;
   }
   dim3 grid((max_len + PF_BM - 1) / PF_BM, n_seqs, a.nq);
   af_launch(attn_prefill_mma_kernel<HD>, dim3(grid), dim3(PF_BM * 2), smem, stream, a);

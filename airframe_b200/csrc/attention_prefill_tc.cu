@@ -425,11 +425,14 @@ template <int HD>
 int launch_ta(const CUtensorMap& mq, const CUtensorMap& mk, const CUtensorMap& mv, const TaArgs& a, int n_seqs,
               int max_len, cudaStream_t stream) {
   constexpr int smem = 2 * TA_BN * HD * 2 + 2 * TA_KT * HD * 2 + TA_BM * TA_BN * 2;  // two K pairs (Q arrives in one), two V tiles, P
-  static bool configured = false;
-  if (!configured) {
+  // (the limit on dynamic shared memory is a device's: set once on each)
+  static bool configured[AF_MAX_DEVICES] = {};
+  const int dev__ = af_current_device();
+  if (dev__ < 0) return -1;
+  if (!configured[dev__]) {
     cudaError_t e = cudaFuncSetAttribute(attn_prefill_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return af_fail((int)e, "af_attn_prefill_tc: %s", cudaGetErrorString(e));
-    configured = true;
+    configured[dev__] = true;
   }
   dim3 grid((max_len + TA_BM - 1) / TA_BM, n_seqs, a.nq);
   af_launch(attn_prefill_tc_kernel<HD>, grid, dim3(TA_THREADS), smem, stream, mq, mk, mv, a);

@@ -45,6 +45,21 @@ extern unsigned long long g_af_launches;
     return 0;                 \
   } while (0)
 
+// ---- the current device
+// Limits and attributes belong to a device, not to the process: what is learnt or set once is
+// kept per device ordinal.
+constexpr int AF_MAX_DEVICES = 64;
+// Ordinal of the current device, or -1 (with the error recorded) when it cannot be had or lies beyond AF_MAX_DEVICES.
+int af_current_device();
+// Streaming multiprocessors of the current device, asked of the driver once per device; <= 0 with the error recorded.
+int af_sm_count();
+// True the first time it is called for (flags, current device): the caller then sets what must be set once per device.
+inline bool af_first_on_device(bool* flags, int dev) {
+  if (dev < 0 || dev >= AF_MAX_DEVICES || flags[dev]) return false;
+  flags[dev] = true;
+  return true;
+}
+
 // ---- programmatic dependent launch
 // Kernels are launched so that a kernel's blocks may become resident while the
 // kernel before it in the stream still runs.  Every kernel calls

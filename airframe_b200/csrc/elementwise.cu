@@ -23,6 +23,39 @@ AF_EXPORT const char* af_last_error() { return g_error; }
 
 AF_EXPORT int af_abi_version() { return 1; }
 
+int af_current_device() {
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) {
+    af_fail((int)e, "cudaGetDevice: %s", cudaGetErrorString(e));
+    return -1;
+  }
+  if (dev < 0 || dev >= AF_MAX_DEVICES) {
+    af_fail(-1, "device ordinal %d beyond the %d this library keeps state for", dev, AF_MAX_DEVICES);
+    return -1;
+  }
+  return dev;
+}
+
+int af_sm_count() {
+  static int sms[AF_MAX_DEVICES] = {};
+  const int dev = af_current_device();
+  if (dev < 0) return -1;
+  if (sms[dev] == 0) {
+    int n = 0;
+    cudaError_t e = cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+    if (e != cudaSuccess || n <= 0) {
+      af_fail(e != cudaSuccess ? (int)e : -1, "the multiprocessor count of device %d: %s", dev, cudaGetErrorString(e));
+      return -1;
+    }
+    sms[dev] = n;
+  }
+  return sms[dev];
+}
+
+// Streaming multiprocessors of the current device (the policies that cut work into blocks ask for it).
+AF_EXPORT int af_device_sm_count() { return af_sm_count(); }
+
 unsigned long long g_af_launches = 0;
 int g_af_pdl = 1;
 
@@ -383,8 +416,10 @@ __global__ void add_kernel(float* __restrict__ x, const T* __restrict__ a, size_
 
 AF_EXPORT int af_add(float* x, const void* a, int a_dtype, long long n, cudaStream_t stream) {
   if (n == 0) return 0;
+  const int sms = af_sm_count();
+  if (sms <= 0) return -1;
   long long blocks = (n + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > (long long)sms * 16) blocks = (long long)sms * 16;
   AF_DISPATCH_DTYPE(a_dtype, T, af_launch(add_kernel<T>, dim3((int)blocks), dim3(256), 0, stream, x, (const T*)a, (size_t)n));
   AF_CHECK_LAUNCH("af_add");
 }
@@ -401,8 +436,10 @@ __global__ void softcap_kernel(float* __restrict__ z, size_t n, float cap) {
 
 AF_EXPORT int af_softcap(float* z, long long n, float cap, cudaStream_t stream) {
   if (n == 0 || cap <= 0.f) return 0;
+  const int sms = af_sm_count();
+  if (sms <= 0) return -1;
   long long blocks = (n + 255) / 256;
-  if (blocks > 148 * 16) blocks = 148 * 16;
+  if (blocks > (long long)sms * 16) blocks = (long long)sms * 16;
   af_launch(softcap_kernel, dim3((int)blocks), dim3(256), 0, stream, z, (size_t)n, cap);
   AF_CHECK_LAUNCH("af_softcap");
 }

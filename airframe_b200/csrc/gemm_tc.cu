@@ -31,7 +31,6 @@ namespace {
 constexpr int TC_BM = 128;  // features per CTA = UMMA M
 constexpr int TC_BK = 64;   // K per stage: 128 bytes of bfloat16 = one swizzle row
 constexpr int TC_THREADS = 192;
-constexpr int TC_SMS = 148;
 constexpr int TC_SMEM_BUDGET = 192 * 1024;    // of one block alone on its SM
 constexpr int TC_SMEM_BUDGET_2 = 108 * 1024;  // of each of two blocks that share an SM
 
@@ -288,12 +287,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
 template <int BN, int NACC, int ACT, typename TO, int PER_SM>
 int launch_on(dim3 grid, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, cudaStream_t stream) {
   constexpr int smem = tc_stages(BN, NACC, PER_SM) * tc_stage_bytes(BN, NACC) + 1024;
-  static bool configured = false;
-  if (!configured) {
+  // (the limit on dynamic shared memory is a device's: set once on each)
+  static bool configured[AF_MAX_DEVICES] = {};
+  const int dev__ = af_current_device();
+  if (dev__ < 0) return -1;
+  if (!configured[dev__]) {
     cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel<BN, NACC, ACT, TO, PER_SM>,
                                          cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
     if (e != cudaSuccess) return af_fail((int)e, "gemm_tc: %s", cudaGetErrorString(e));
-    configured = true;
+    configured[dev__] = true;
   }
   af_launch(gemm_tc_kernel<BN, NACC, ACT, TO, PER_SM>, grid, dim3(TC_THREADS), smem, stream, mw, mx, a);
   AF_CHECK_LAUNCH("af_gemm_tc");
@@ -306,14 +308,16 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcArgs a, long long n_w
   a.tiles_w = (int)((w_tiles + NACC - 1) / NACC);
   a.tiles_m = (a.M + BN - 1) / BN;
   const long long tiles = (long long)a.tiles_w * a.tiles_m;
+  const int sms = af_sm_count();
+  if (sms <= 0) return -1;
   if constexpr (BN <= 64 && NACC == 1) {
     // bound by the weight stream: a block per tile; many waves of them run two to an SM
     dim3 grid((unsigned)tiles, 1, splits);
-    if (tiles * splits > 2 * TC_SMS) return launch_on<BN, NACC, ACT, TO, 2>(grid, mw, mx, a, stream);
+    if (tiles * splits > 2 * sms) return launch_on<BN, NACC, ACT, TO, 2>(grid, mw, mx, a, stream);
     return launch_on<BN, NACC, ACT, TO, 1>(grid, mw, mx, a, stream);
   }
   // bound by the products: one block per SM walks the tiles
-  dim3 grid((unsigned)(tiles < TC_SMS ? tiles : TC_SMS), 1, splits);
+  dim3 grid((unsigned)(tiles < sms ? tiles : sms), 1, splits);
   return launch_on<BN, NACC, ACT, TO, 1>(grid, mw, mx, a, stream);
 }
 

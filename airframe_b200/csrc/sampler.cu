@@ -329,11 +329,14 @@ AF_EXPORT int af_sample(float* logits, int ld, int rows, int vocab, const int* r
   AF_REQUIRE(temperature >= 0.f && top_p > 0.f && penalty > 0.f, "af_sample: bad options");
   AF_REQUIRE(temperature < 1e-7f || uniform != nullptr, "af_sample: uniform numbers are required");
   const size_t smem = SM_BINS * sizeof(u64);
-  static bool configured = false;
-  if (!configured) {
+  // (the limit on dynamic shared memory is a device's: set once on each)
+  static bool configured[AF_MAX_DEVICES] = {};
+  const int dev__ = af_current_device();
+  if (dev__ < 0) return -1;
+  if (!configured[dev__]) {
     cudaError_t e = cudaFuncSetAttribute(sample_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (e != cudaSuccess) return af_fail((int)e, "af_sample: %s", cudaGetErrorString(e));
-    configured = true;
+    configured[dev__] = true;
   }
   af_launch(sample_kernel, dim3(rows), dim3(SM_THREADS), smem, stream, logits, ld, vocab, recent, n_recent, recent_stride,
                                                     temperature, top_p, penalty, uniform, out);

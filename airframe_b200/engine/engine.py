@@ -88,24 +88,26 @@ class Engine:
             raise StepError("sequences that go on bring one token each")
         return lens
 
-    def step(self, entries, pad_to: int = 0, borrow: bool = False):
+    def step(self, entries, pad_to: int = 0, borrow: bool = False, probe=None):
         """Run one step.  Returns float32 logits [wanted, vocab] on the device,
         in the order of the entries and of their ``want`` lists, or None when
         nothing is wanted.  ``borrow``: the caller uses the logits before the
         next step and may get a buffer that the next step overwrites (saves a
-        copy when the step ran as a CUDA graph)."""
+        copy when the step ran as a CUDA graph).  ``probe``: a
+        :class:`~airframe_b200.engine.probe.LayerProbe` that is shown the
+        residual stream after every run (the step then runs kernel by kernel)."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         lens = self.check(entries)
         growth = {e.slot: n + len(e.tokens) for e, n in zip(entries, lens)}
         self.cache.reserve(growth)
         self.cache.flush()
-        if self.use_graphs and lens[0] > 0 and all(e.want == [0] for e in entries):
+        if probe is None and self.use_graphs and lens[0] > 0 and all(e.want == [0] for e in entries):
             logits = self._decode_graphed([e.slot for e in entries], lens, tokens=[e.tokens[0] for e in entries])
             if not borrow:
                 logits = logits.clone()
         else:
             batch = build_batch(entries, lens, self.device, pad_to=pad_to)
-            logits = self.model.forward(batch, self.cache)
+            logits = self.model.forward(batch, self.cache, probe)
         self.cache.commit(growth)
         return logits
 

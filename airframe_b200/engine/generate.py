@@ -23,6 +23,17 @@ What the host knows without the tokens (max_tokens, the context limit) it
 applies in time; a stop token it sees one step late: that sequence's next
 step is already queued, its result is dropped and nothing of it is emitted.
 The tokens are the same either way.
+
+A ``logits_processor`` is the loop's control hook (reference: ``InferenceControl::intervene``
+with its decisions Allow / ForceToken / EarlyExit / BlockAndTerminate, ``src/control.rs:29-52``,
+applied per token at ``src/runtime/engine.rs:183-205``).  It is called for every live
+sequence before its token is chosen, with the request's index, the generation step
+(0 for the first new token), the sequence's row of logits on the device (which it may
+change in place: then the sampler chooses among what it left) and the tokens so far.
+It returns None (go on), a token id (that token is emitted instead of the sampler's
+choice), or :data:`STOP` (the sequence ends cleanly, reason ``control``); raising
+:class:`Blocked` ends the whole call.  With a processor the loop steps in lock-step
+(the host must see every token before the next step is laid out).
 """
 from __future__ import annotations
 
@@ -31,6 +42,13 @@ from typing import Callable, Optional
 
 from ..kernels_const import PAGE
 from .batch import StepEntry
+
+
+STOP = "stop"
+
+
+class Blocked(RuntimeError):
+    """A logits processor refused to let generation go on."""
 
 
 class RequestError(ValueError):
@@ -86,12 +104,17 @@ class GenerationLoop:
         limit = self.engine.cache.n_slots
         if self.max_batch:
             limit = min(limit, self.max_batch)
+        # a cache whose groups of layers have storage of their own answers for each of them
+        fits = getattr(self.engine.cache, "fits", None)
         batches, cur, cur_pages = [], [], 0
         for i, p in enumerate(prompts):
-            need = _pages(self.tokens_held(len(p), params))
-            if need > total_pages:
+            held = self.tokens_held(len(p), params)
+            need = _pages(held)
+            if need > total_pages or (fits is not None and not fits([held])):
                 raise RequestError(f"request {i} needs {need} cache pages, the cache has {total_pages}")
-            if cur and (len(cur) >= limit or cur_pages + need > total_pages):
+            if cur and (len(cur) >= limit or cur_pages + need > total_pages
+                        or (fits is not None and not fits([self.tokens_held(len(prompts[j]), params) for j in cur]
+                                                          + [held]))):
                 batches.append(cur)
                 cur, cur_pages = [], 0
             cur.append(i)
@@ -102,9 +125,12 @@ class GenerationLoop:
 
     # ------------------------------------------------------------------ running
 
-    def generate(self, prompts, params, on_token: Optional[Callable] = None) -> list:
+    def generate(self, prompts, params, on_token: Optional[Callable] = None,
+                 logits_processor: Optional[Callable] = None) -> list:
         """New token ids per request, in request order.  ``on_token(request
-        index, token id)`` is called for every emitted token."""
+        index, token id)`` is called for every emitted token;
+        ``logits_processor(request index, step, logits row, tokens so far)``
+        before every choice (see the module's text)."""
         self.check(prompts, params)
         results = [[] for _ in prompts]
         self.finish_reasons = [None] * len(prompts)
@@ -122,7 +148,7 @@ class GenerationLoop:
                 for s in seqs:
                     s.slot = self.engine.take_slot()
                     s.state = self.sampler.new_state(params, s.index)
-                self._run_batch(seqs, params, stops, on_token)
+                self._run_batch(seqs, params, stops, on_token, logits_processor)
             finally:
                 for s in seqs:
                     if s.slot >= 0:
@@ -138,24 +164,44 @@ class GenerationLoop:
         self.engine.free_slot(s.slot)
         s.slot = -1
 
-    def _run_batch(self, seqs, params, stops, on_token) -> None:
-        ahead = (self.pipelined and params.repetition_penalty == 1.0 and hasattr(self.engine, "decode_rows")
+    def _run_batch(self, seqs, params, stops, on_token, processor=None) -> None:
+        ahead = (self.pipelined and processor is None and params.repetition_penalty == 1.0
+                 and hasattr(self.engine, "decode_rows")
                  and hasattr(self.sampler, "sample_async") and getattr(self.engine, "use_graphs", False))
         if ahead:
             self._run_batch_ahead(seqs, params, stops, on_token)
         else:
-            self._run_batch_in_step(seqs, params, stops, on_token)
+            self._run_batch_in_step(seqs, params, stops, on_token, processor)
 
-    def _run_batch_in_step(self, seqs, params, stops, on_token) -> None:
+    def _run_batch_in_step(self, seqs, params, stops, on_token, processor=None) -> None:
         """Every step waits for the tokens of the step before."""
         logits = self.engine.step([StepEntry(s.slot, s.prompt, [len(s.prompt) - 1]) for s in seqs])
         for s in seqs:
             s.length = len(s.prompt)
         active = list(seqs)
         while active:
+            decisions = [None] * len(active)
+            if processor is not None:
+                for r, s in enumerate(active):
+                    d = processor(s.index, len(s.out), logits[r], s.prompt + s.out)
+                    if not (d is None or d == STOP or (isinstance(d, int) and not isinstance(d, bool)
+                                                       and 0 <= d < self.engine.vocab_size)):
+                        raise RequestError(f"request {s.index}: the logits processor returned {d!r} "
+                                           f"(None, a token id or STOP)")
+                    decisions[r] = d
             tokens = self.sampler.sample(logits, [s.state for s in active], params)
             going = []
-            for s, t in zip(active, tokens):
+            for s, t, d in zip(active, tokens, decisions):
+                if d == STOP:
+                    self._end(s, "control")
+                    continue
+                if d is not None:
+                    # the sampler's choice is discarded (its draw is spent, as in the reference, where the
+                    # candidate is sampled before the hook sees it); what sampling remembers is the forced token
+                    fix = getattr(s.state, "replace_last", None)
+                    if fix is not None:
+                        fix(d)
+                    t = d
                 if t in stops:
                     self._end(s, "stop")
                     continue

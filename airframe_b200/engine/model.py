@@ -77,15 +77,21 @@ class Model:
 
     # ------------------------------------------------------------------ forward
 
-    def hidden(self, batch, cache) -> torch.Tensor:
-        """The float32 residual stream [T, H] after all scheduled runs."""
+    def hidden(self, batch, cache, probe=None) -> torch.Tensor:
+        """The float32 residual stream [T, H] after all scheduled runs.
+        ``probe`` (a :class:`~airframe_b200.engine.probe.LayerProbe`) is shown
+        the stream after the embedding and after every run."""
         x = self.embedding.forward(batch.tokens)
+        if probe is not None:
+            probe.after(-1, -1, x, batch)
         sched = self.spec.schedule
         normed = None
         for i, e in enumerate(sched):
             blk = self.blocks[e.layer]
             nxt = self.blocks[sched[i + 1].layer].first_norm() if i + 1 < len(sched) else None
             normed = blk.forward(x, batch, cache.views[i], normed=normed, next_pre=nxt)
+            if probe is not None:
+                probe.after(i, e.layer, x, batch)
         return x
 
     def logits(self, x, want_rows) -> torch.Tensor:
@@ -93,8 +99,8 @@ class Model:
         y = self.final_norm.forward(x, self.ctx.compute_dtype, rows=want_rows)
         return self.head.forward(y)
 
-    def forward(self, batch, cache):
-        x = self.hidden(batch, cache)
+    def forward(self, batch, cache, probe=None):
+        x = self.hidden(batch, cache, probe)
         if batch.want_rows is None:
             return None
         return self.logits(x, batch.want_rows)

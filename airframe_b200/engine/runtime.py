@@ -84,9 +84,13 @@ class GpuRuntime:
 
     # ------------------------------------------------------------------ use
 
-    def generate(self, prompt, params=None, on_token=None):
+    def generate(self, prompt, params=None, on_token=None, logits_processor=None):
         """``prompt``: token ids of one request, or a list of such lists.
-        Returns the new token ids (a list, or a list of lists)."""
+        Returns the new token ids (a list, or a list of lists).
+        ``on_token(request index, token id)`` sees every emitted token;
+        ``logits_processor`` is the control hook of
+        :mod:`airframe_b200.engine.generate` (the reference's third argument of
+        ``generate``, ``src/runtime/gpu.rs:644-654``)."""
         from .generate import GenerationLoop
         from ..sampling import SamplingParams, Sampler
         if self._loop is None:
@@ -94,11 +98,12 @@ class GpuRuntime:
                                         stop_token_ids=self.model.spec.stop_token_ids)
         params = params or SamplingParams()
         single = len(prompt) > 0 and isinstance(prompt[0], int)
-        out = self._loop.generate([list(prompt)] if single else [list(p) for p in prompt], params, on_token)
+        out = self._loop.generate([list(prompt)] if single else [list(p) for p in prompt], params, on_token,
+                                  logits_processor)
         return out[0] if single else out
 
-    def step(self, entries):
-        return self.engine.step(entries)
+    def step(self, entries, probe=None):
+        return self.engine.step(entries, probe=probe)
 
     def spec(self):
         return self.model.spec

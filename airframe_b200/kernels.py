@@ -84,6 +84,22 @@ def launch_count() -> int:
     return int(f())
 
 
+_SMS = {}
+
+
+def sm_count() -> int:
+    """Streaming multiprocessors of the current device (asked of the driver
+    once per device): what the policies that cut work into blocks divide by."""
+    dev = _current_device()
+    n = _SMS.get(dev)
+    if n is None:
+        n = int(_lib().af_device_sm_count())
+        if n <= 0:
+            _check(n or -1)
+        _SMS[dev] = n
+    return n
+
+
 def require_cuda_tensor(t, name="tensor"):
     if not t.is_cuda:
         raise KernelError(f"{name} must live on a CUDA device")
@@ -286,7 +302,7 @@ def gemm_tc_splits(M: int, N: int, K: int) -> int:
     kb = (K + 63) // 64
     if tiles >= 96 or kb < 8:
         return 1
-    want = max(1, min(148 // tiles, kb // 4, 16))
+    want = max(1, min(sm_count() // tiles, kb // 4, 16))
     per = (kb + want - 1) // want
     return (kb + per - 1) // per
 
@@ -383,20 +399,23 @@ def attn_prefill(out, q, k, v, batch, nq, nkv, hd, scale, cap, window) -> None:
     attn_prefill_plain(out, q, k, v, batch.positions, nq, nkv, hd, scale, cap, window)
 
 
-def attn_decode_splits(batch: int, nkv: int, max_len: int, window: int, blocks: int = 148) -> int:
-    """How many ways the keys of a sequence are split so that the step fills the GPU."""
+def attn_decode_splits(batch: int, nkv: int, max_len: int, window: int, blocks: int = 0) -> int:
+    """How many ways the keys of a sequence are split so that the step fills
+    the GPU (``blocks``: its multiprocessors, asked of the device when 0)."""
+    blocks = blocks or sm_count()
     rows = min(max_len, window) if window else max_len
     pages = max(1, (rows + PAGE - 1) // PAGE + (1 if window else 0))
     want = max(1, blocks // max(1, batch * nkv))   # one wave of blocks, each with a long run of pages
     return max(1, min(want, pages, 64))
 
 
-def attn_decode_max_splits(batch: int, nkv: int, max_len: int, window: int, blocks: int = 148) -> int:
+def attn_decode_max_splits(batch: int, nkv: int, max_len: int, window: int, blocks: int = 0) -> int:
     """The most splits the split kernel may give one sequence (the third extent
     of its grid).  With sequences of equal lengths it uses
     :func:`attn_decode_splits` of them; the room above that is for a long
     sequence among short ones, up to three blocks an SM in all (a block without
     a split of its own leaves at once, but the SMs start them one by one)."""
+    blocks = blocks or sm_count()
     rows = min(max_len, window) if window else max_len
     pages = max(1, (rows + PAGE - 1) // PAGE + (1 if window else 0))
     units = max(1, batch * nkv)

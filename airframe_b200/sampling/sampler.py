@@ -27,6 +27,11 @@ class SequenceSamplingState:
         if len(self.recent) > RECENT_WINDOW:
             del self.recent[0]
 
+    def replace_last(self, token: int) -> None:
+        """The token noted last was not emitted after all (a control hook put another in its place)."""
+        if self.recent:
+            self.recent[-1] = token
+
 
 class PendingTokens:
     """Tokens that the sampling kernel has been asked for: on the device at once

@@ -123,3 +123,17 @@ def test_slot_count_and_ring_pool_are_bounded():
 def test_reading_a_cache_with_other_head_sizes_is_refused():
     with pytest.raises(ValueError, match="other head sizes"):
         SequenceCache([(KVNeed(2, 16, None), None, None), (KVNeed(4, 16, None), None, 0)], 640, 512)
+
+
+def test_a_group_with_a_window_has_storage_of_its_own_size():
+    """With the most sequences named, the ring's group holds slots x ring pages, fewer than the group that
+    keeps all keys; ``fits`` answers for every group."""
+    c = SequenceCache(_needs(), max_tokens=64 * 40, max_context=1024, max_sequences=4)
+    ring, full = c.groups[KVNeed(2, 16, 100)], c.groups[KVNeed(2, 16, None)]
+    assert full.n_pages == 40 and ring.n_pages == 4 * 2
+    assert c.fits([640, 640, 640, 640])                   # 40 pages of all keys, 8 of the ring
+    assert not c.fits([640, 640, 640, 641])               # a 41st page of all keys
+    assert not c.fits([64] * 5)                           # a fifth slot
+    # without the most sequences there are as many slots as pages and the ring's group saves nothing
+    c = SequenceCache(_needs(), max_tokens=64 * 40, max_context=1024)
+    assert c.groups[KVNeed(2, 16, 100)].n_pages == 40

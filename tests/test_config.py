@@ -56,13 +56,26 @@ def test_layer_types_key_wins_over_alternation():
         config_from_dict(dict(TINY_B, layer_types=["full_attention", "x", "full_attention"]))
 
 
-def test_softcaps_may_be_null_or_absent():
-    d = dict(TINY_A, attn_logit_softcapping=None)
-    del d["final_logit_softcapping"]
+def test_softcaps_may_be_null_but_not_absent():
+    d = dict(TINY_A, attn_logit_softcapping=None, final_logit_softcapping=None)
     c = config_from_dict(d)
     assert c.attn_logit_softcapping is None and c.final_logit_softcapping is None
     spec = c.model_spec()
     assert spec.layers[0].mixer.params["softcap"] == 0.0 and spec.head.params["softcap"] == 0.0
+    # an absent key is no answer: neither "off" nor some other model's value is assumed
+    for key in ("attn_logit_softcapping", "final_logit_softcapping"):
+        d = dict(TINY_A)
+        del d[key]
+        with pytest.raises(ConfigError, match=key):
+            config_from_dict(d)
+
+
+def test_written_config_keeps_integers_integer():
+    d = config_from_dict(TINY_A).to_dict()
+    assert d["query_pre_attn_scalar"] == 16 and isinstance(d["query_pre_attn_scalar"], int)
+    assert config_from_dict(d) == config_from_dict(TINY_A)
+    d = config_from_dict(dict(TINY_A, query_pre_attn_scalar=12.5)).to_dict()
+    assert d["query_pre_attn_scalar"] == 12.5
 
 
 @pytest.mark.parametrize("key", ["hidden_size", "num_hidden_layers", "intermediate_size", "num_attention_heads",

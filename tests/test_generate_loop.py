@@ -226,3 +226,64 @@ def test_a_repetition_penalty_keeps_the_loop_in_step():
     loop = GenerationLoop(eng, AheadSampler({0: [3, 9]}), stop_token_ids=[9])
     out = loop.generate([[1]], SamplingParams(temperature=0.0, repetition_penalty=1.3, max_tokens=4))
     assert out == [[3]] and eng.steps == [[(0, [1])], [(0, [3])]]
+
+
+# ---------------------------------------------------------------- the control hook
+
+def test_logits_processor_allows_forces_stops_and_blocks():
+    from airframe_b200.engine.generate import STOP, Blocked
+    script = {0: [10, 11, 12, 13, 14], 1: [20, 21, 22, 23, 24], 2: [30, 31, 32, 33, 34]}
+    eng = FakeEngine()
+    loop = GenerationLoop(eng, ScriptSampler(script), stop_token_ids=[99])
+    seen = []
+
+    def control(index, step, row, tokens):
+        seen.append((index, step, row, list(tokens)))
+        if index == 0 and step == 1:
+            return 77                      # ForceToken: 77 goes out instead of the sampler's 11
+        if index == 1 and step == 2:
+            return STOP                    # EarlyExit after two tokens
+        if index == 2 and step == 1:
+            return 99                      # a forced stop token ends the sequence like a sampled one
+        return None                        # Allow
+
+    params = SamplingParams(max_tokens=4, temperature=0.0)
+    out = loop.generate([[1, 2], [3], [4, 5, 6]], params, logits_processor=control)
+    assert out == [[10, 77, 12, 13], [20, 21], [30]]
+    assert loop.finish_reasons == ["length", "control", "stop"]
+    # the hook sees, per live sequence and step, its own row of logits and its tokens so far
+    assert (0, 0, 0, [1, 2]) in seen and (0, 2, 0, [1, 2, 10, 77]) in seen and (1, 2, 1, [3, 20, 21]) in seen
+    assert not any(i == 1 and st == 3 for i, st, _, _ in seen)
+    # the forced token is what the next step is fed
+    assert (0, [77]) in [x for stp in eng.steps for x in stp]
+    assert eng.pool.n_held == 0
+
+    def block(index, step, row, tokens):
+        if step == 1:
+            raise Blocked("policy says no")
+        return None
+
+    with pytest.raises(Blocked, match="policy"):
+        loop.generate([[1, 2]], params, logits_processor=block)
+    assert eng.pool.n_held == 0            # the slots came back although the call ended in an error
+    with pytest.raises(RequestError, match="logits processor returned"):
+        loop.generate([[1, 2]], params, logits_processor=lambda i, s, r, t: 1000)
+    assert eng.pool.n_held == 0
+
+
+def test_a_processor_keeps_the_loop_in_lock_step():
+    """With a processor the loop never uses decode_rows (the host must see every token first)."""
+    class AheadEngine(FakeEngine):
+        use_graphs = True
+
+        def decode_rows(self, slots, tokens):
+            raise AssertionError("queued a step ahead although a processor was given")
+
+    class S(ScriptSampler):
+        def sample_async(self, *a):
+            raise AssertionError("sampled ahead although a processor was given")
+
+    loop = GenerationLoop(AheadEngine(), S({0: [5, 6, 7]}))
+    out = loop.generate([[1]], SamplingParams(max_tokens=3, temperature=0.0, repetition_penalty=1.0),
+                        logits_processor=lambda i, s, r, t: None)
+    assert out == [[5, 6, 7]]

@@ -417,6 +417,21 @@ def test_gemm_tensor_cores(K, M, N, Kd, out_dtype):
         close(out, twin.cpu(), torch.float32)
 
 
+@pytest.mark.parametrize("M,N,Kd", [(2048, 2304, 2304), (16384, 384, 520), (2048, 300, 9216), (4100, 18432 // 16, 264)])
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+def test_gemm_tensor_cores_many_token_tiles(K, M, N, Kd, out_dtype):
+    """Prompts of thousands of tokens: 8 to 64 token tiles, which the blocks walk tile after tile."""
+    torch.manual_seed(M + N + Kd)
+    x = torch.randn(M, Kd).to(torch.bfloat16)
+    w = (torch.randn(N, Kd) * 0.05).to(torch.bfloat16)
+    ref = x.double() @ w.double().T
+    for n_acc in (0, 1, 2):
+        out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
+        K.gemm_tc(out, x.to(DEV), w.to(DEV), n_acc=n_acc)
+        K.check_device_errors(DEV)
+        close(out, ref, out_dtype if out_dtype == torch.bfloat16 else torch.float32)
+
+
 @pytest.mark.parametrize("M,N,Kd,splits", [(8, 256, 1024, 4), (3, 130, 2304, 9), (40, 384, 9216, 16), (16, 128, 520, 3)])
 def test_gemm_tensor_cores_split_k(K, M, N, Kd, splits):
     x = torch.randn(M, Kd).to(torch.bfloat16)

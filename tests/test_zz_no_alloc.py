@@ -18,6 +18,8 @@ from ctypes import c_float, c_int, c_longlong, c_void_p
 import pytest
 import torch
 
+import plain_gemma2 as plain
+
 pytestmark = pytest.mark.gpu
 PAGE = 64
 
@@ -62,6 +64,17 @@ def _call(lib, fn, p, batch, nq, nkv, hd, splits, scratch=None):
     return rc, out, int(err.item())
 
 
+def _plain_last_token(p, b, nq, nkv, hd, cap):
+    """The plain implementation's attention of sequence b's last token over its cached rows."""
+    n = int(p["lens"][b])
+    pages = p["table"][b, : (n + PAGE - 1) // PAGE].long().cpu()
+    k = p["kc"].cpu()[pages].permute(0, 2, 1, 3).reshape(-1, nkv, hd)[:n].double()      # [rows, kv heads, hd]
+    v = p["vc"].cpu()[pages].permute(0, 2, 1, 3).reshape(-1, nkv, hd)[:n].double()
+    q = torch.zeros(n, nq, hd, dtype=torch.float64)
+    q[-1] = p["q"][b].cpu().double().reshape(nq, hd)
+    return plain.attention(q, k, v, 1.0 / math.sqrt(hd), cap, p["window"] or None)[-1]
+
+
 def test_static_scratch_entry_point_matches_the_allocating_one_twice_in_a_row():
     lib = _lib()
     batch, nq, nkv, hd, splits = 3, 8, 4, 128, 5
@@ -78,6 +91,11 @@ def test_static_scratch_entry_point_matches_the_allocating_one_twice_in_a_row():
         diff = (got.float() - ref.float()).abs().max().item()
         assert diff <= 1.2e-2 * max(1.0, ref.float().abs().max().item()), diff    # the kernel tests' bfloat16 bound
         assert diff == 0.0                                                        # the same kernels: the same bits
+        # and against the plain implementation, so that the test stands without the other entry point
+        for b in range(batch):
+            want = _plain_last_token(p, b, nq, nkv, hd, 30.0)
+            off = (got[b].double().cpu() - want).abs().max().item()
+            assert off <= 1.2e-2 * max(1.0, want.abs().max().item()), (b, off)
 
 
 def test_static_scratch_entry_point_refuses_what_does_not_fit():
