@@ -235,7 +235,7 @@ __device__ __forceinline__ void attn_load_q(WarpAttn& st, const T* q, int hd, in
 
 template <typename T>
 __device__ __forceinline__ void attn_key(WarpAttn& st, const T* k, const T* v, int hd, int lane,
-                                         float scale, float cap) {
+                                         float scale, float cap, float bias) {
   float dot = 0.f;
 #pragma unroll
   for (int e = 0; e < AF_HD_SLICES; ++e) {
@@ -243,7 +243,7 @@ __device__ __forceinline__ void attn_key(WarpAttn& st, const T* k, const T* v, i
     if (d < hd) dot += st.q[e] * to_f32(k[d]);
   }
   dot = warp_sum(dot);
-  const float s = softcap_f32(dot * scale, cap);
+  const float s = softcap_f32(dot * scale, cap) + bias;   // bias: a position encoding's slope * (key - query)
   const float m_new = fmaxf(st.m, s);
   const float corr = expf(st.m - m_new);  // exp(-inf) = 0 on the first key
   const float p = expf(s - m_new);
@@ -274,7 +274,7 @@ __global__ void attn_prefill_plain_kernel(T* __restrict__ out, int out_stride, c
                                           const T* __restrict__ v, int v_stride,
                                           const int* __restrict__ positions,
                                           int n_tokens, int nq, int nkv, int hd, float scale, float cap,
-                                          int window) {
+                                          int window, const float* __restrict__ slopes) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -287,10 +287,11 @@ __global__ void attn_prefill_plain_kernel(T* __restrict__ out, int out_stride, c
   WarpAttn st;
   attn_load_q(st, q + (size_t)t * q_stride + (size_t)h * hd, hd, lane);
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+  const float slope = slopes ? slopes[h] : 0.f;
   for (int j = lo; j <= pos; ++j) {
     const size_t r = (size_t)(first_row + j);
     attn_key(st, k + r * k_stride + (size_t)g * hd, v + r * v_stride + (size_t)g * hd, hd, lane, scale,
-             cap);
+             cap, slope * (float)(j - pos));
   }
   attn_store(st, out + (size_t)t * out_stride + (size_t)h * hd, hd, lane);
 }
@@ -298,7 +299,8 @@ __global__ void attn_prefill_plain_kernel(T* __restrict__ out, int out_stride, c
 AF_EXPORT int af_attn_prefill_plain(void* out, int out_stride, const void* q, int q_stride,
                                     const void* k, int k_stride, const void* v, int v_stride, int dtype,
                                     const int* positions, int n_tokens, int nq, int nkv, int hd,
-                                    float scale, float cap, int window, cudaStream_t stream) {
+                                    float scale, float cap, int window, const float* slopes,
+                                    cudaStream_t stream) {
   if (n_tokens == 0) return 0;
   AF_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "af_attn_prefill_plain: heads %d, groups %d", nq, nkv);
   AF_REQUIRE(hd > 0 && hd <= AF_MAX_HD, "af_attn_prefill_plain: head_dim %d beyond %d", hd, AF_MAX_HD);
@@ -309,7 +311,7 @@ AF_EXPORT int af_attn_prefill_plain(void* out, int out_stride, const void* q, in
   AF_DISPATCH_DTYPE(dtype, T,
                     af_launch(attn_prefill_plain_kernel<T>, dim3((unsigned)blocks), dim3(wpb * 32), 0, stream, 
                         (T*)out, out_stride, (const T*)q, q_stride, (const T*)k, k_stride, (const T*)v,
-                        v_stride, positions, n_tokens, nq, nkv, hd, scale, cap, window));
+                        v_stride, positions, n_tokens, nq, nkv, hd, scale, cap, window, slopes));
   AF_CHECK_LAUNCH("af_attn_prefill_plain");
 }
 
@@ -321,7 +323,8 @@ __global__ void attn_decode_plain_kernel(T* __restrict__ out, int out_stride, co
                                          const T* __restrict__ vcache, const int* __restrict__ page_table,
                                          int max_pages, const int* __restrict__ slots,
                                          const int* __restrict__ lens, int batch, int nq, int nkv, int hd,
-                                         float scale, float cap, int window, int ring_rows) {
+                                         float scale, float cap, int window, int ring_rows,
+                                         const float* __restrict__ slopes) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -341,10 +344,11 @@ __global__ void attn_decode_plain_kernel(T* __restrict__ out, int out_stride, co
   attn_load_q(st, q + (size_t)b * q_stride + (size_t)h * hd, hd, lane);
   const int lo = window > 0 ? max(0, pos - window + 1) : 0;
   const int* pt = page_table + (size_t)slot * max_pages;
+  const float slope = slopes ? slopes[h] : 0.f;
   for (int j = lo; j <= pos; ++j) {
     const int r = ring_rows > 0 ? j % ring_rows : j;
     const size_t base = (((size_t)pt[r / AF_PAGE] * nkv + g) * AF_PAGE + r % AF_PAGE) * hd;
-    attn_key(st, kcache + base, vcache + base, hd, lane, scale, cap);
+    attn_key(st, kcache + base, vcache + base, hd, lane, scale, cap, slope * (float)(j - pos));
   }
   attn_store(st, o, hd, lane);
 }
@@ -353,7 +357,8 @@ AF_EXPORT int af_attn_decode_plain(void* out, int out_stride, const void* q, int
                                    const void* kcache, const void* vcache, int dtype,
                                    const int* page_table, int max_pages, const int* slots,
                                    const int* lens, int batch, int nq, int nkv, int hd, float scale,
-                                   float cap, int window, int ring_rows, cudaStream_t stream) {
+                                   float cap, int window, int ring_rows, const float* slopes,
+                                   cudaStream_t stream) {
   if (batch == 0) return 0;
   AF_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "af_attn_decode_plain: heads %d, groups %d", nq, nkv);
   AF_REQUIRE(hd > 0 && hd <= AF_MAX_HD, "af_attn_decode_plain: head_dim %d beyond %d", hd, AF_MAX_HD);
@@ -366,6 +371,6 @@ AF_EXPORT int af_attn_decode_plain(void* out, int out_stride, const void* q, int
                     af_launch(attn_decode_plain_kernel<T>, dim3((unsigned)blocks), dim3(wpb * 32), 0, stream, 
                         (T*)out, out_stride, (const T*)q, q_stride, (const T*)kcache, (const T*)vcache,
                         page_table, max_pages, slots, lens, batch, nq, nkv, hd, scale, cap, window,
-                        ring_rows));
+                        ring_rows, slopes));
   AF_CHECK_LAUNCH("af_attn_decode_plain");
 }

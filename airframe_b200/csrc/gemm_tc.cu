@@ -302,7 +302,7 @@ int launch_on(dim3 grid, const CUtensorMap& mw, const CUtensorMap& mx, const TcA
 }
 
 template <int BN, int NACC, int ACT, typename TO>
-int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcArgs a, long long n_w_rows, int splits,
+int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcArgs a, long long n_w_rows, int splits, int per_sm,
            cudaStream_t stream) {
   const long long w_tiles = (n_w_rows + TC_BM - 1) / TC_BM;
   a.tiles_w = (int)((w_tiles + NACC - 1) / NACC);
@@ -313,7 +313,8 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcArgs a, long long n_w
   if constexpr (BN <= 64 && NACC == 1) {
     // bound by the weight stream: a block per tile; many waves of them run two to an SM
     dim3 grid((unsigned)tiles, 1, splits);
-    if (tiles * splits > 2 * sms) return launch_on<BN, NACC, ACT, TO, 2>(grid, mw, mx, a, stream);
+    if (per_sm == 2 || (per_sm == 0 && tiles * splits > 2 * sms))
+      return launch_on<BN, NACC, ACT, TO, 2>(grid, mw, mx, a, stream);
     return launch_on<BN, NACC, ACT, TO, 1>(grid, mw, mx, a, stream);
   }
   // bound by the products: one block per SM walks the tiles
@@ -323,30 +324,30 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcArgs a, long long n_w
 
 template <int NACC, int ACT, typename TO>
 int launch_bn(int bn, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a, long long rows, int splits,
-              cudaStream_t s) {
+              int per_sm, cudaStream_t s) {
   switch (bn) {
-    case 16: return launch<16, NACC, ACT, TO>(mw, mx, a, rows, splits, s);
-    case 32: return launch<32, NACC, ACT, TO>(mw, mx, a, rows, splits, s);
-    case 64: return launch<64, NACC, ACT, TO>(mw, mx, a, rows, splits, s);
-    case 128: return launch<128, NACC, ACT, TO>(mw, mx, a, rows, splits, s);
-    case 256: return launch<256, NACC, ACT, TO>(mw, mx, a, rows, splits, s);
+    case 16: return launch<16, NACC, ACT, TO>(mw, mx, a, rows, splits, per_sm, s);
+    case 32: return launch<32, NACC, ACT, TO>(mw, mx, a, rows, splits, per_sm, s);
+    case 64: return launch<64, NACC, ACT, TO>(mw, mx, a, rows, splits, per_sm, s);
+    case 128: return launch<128, NACC, ACT, TO>(mw, mx, a, rows, splits, per_sm, s);
+    case 256: return launch<256, NACC, ACT, TO>(mw, mx, a, rows, splits, per_sm, s);
   }
   return af_fail(-1, "gemm_tc: token tile %d", bn);
 }
 
 template <typename TO>
 int launch_variant(int nacc, int gated, int act, int bn, const CUtensorMap& mw, const CUtensorMap& mx, const TcArgs& a,
-                   long long rows, int splits, cudaStream_t s) {
+                   long long rows, int splits, int per_sm, cudaStream_t s) {
   if (gated && act == AF_ACT_GELU_TANH) {
-    if (nacc == 2) return launch_bn<2, AF_ACT_GELU_TANH, TO>(bn, mw, mx, a, rows, 1, s);
-    return launch_bn<1, AF_ACT_GELU_TANH, TO>(bn, mw, mx, a, rows, 1, s);
+    if (nacc == 2) return launch_bn<2, AF_ACT_GELU_TANH, TO>(bn, mw, mx, a, rows, 1, per_sm, s);
+    return launch_bn<1, AF_ACT_GELU_TANH, TO>(bn, mw, mx, a, rows, 1, per_sm, s);
   }
   if (gated) {
-    if (nacc == 2) return launch_bn<2, AF_ACT_SILU, TO>(bn, mw, mx, a, rows, 1, s);
-    return launch_bn<1, AF_ACT_SILU, TO>(bn, mw, mx, a, rows, 1, s);
+    if (nacc == 2) return launch_bn<2, AF_ACT_SILU, TO>(bn, mw, mx, a, rows, 1, per_sm, s);
+    return launch_bn<1, AF_ACT_SILU, TO>(bn, mw, mx, a, rows, 1, per_sm, s);
   }
-  if (nacc == 2) return launch_bn<2, -1, TO>(bn, mw, mx, a, rows, splits, s);
-  return launch_bn<1, -1, TO>(bn, mw, mx, a, rows, splits, s);
+  if (nacc == 2) return launch_bn<2, -1, TO>(bn, mw, mx, a, rows, splits, per_sm, s);
+  return launch_bn<1, -1, TO>(bn, mw, mx, a, rows, splits, per_sm, s);
 }
 
 }  // namespace
@@ -363,10 +364,13 @@ AF_EXPORT int af_gemm_tc_token_tile(int M) {
 // 16 features, N = n_w_rows / 2, and out[m, f] = act(x . gate_f) * (x . up_f).
 // n_acc: 1 or 2 weight tiles per block.  splits > 1: out is float [splits, M,
 // N] partial sums (part_stride elements apart) and out_dtype must be AF_F32.
+// per_sm (weight-bound products of up to 64 tokens only): 2 gives a block half an SM's shared memory, so that the
+// blocks of the next product in the stream fit beside it and fetch their first weight tiles while this one still
+// runs; 1 gives it the whole SM; 0 chooses (2 for grids of more than two waves).
 // err: device word set to 1 when a wait inside the kernel ran out of time.
 AF_EXPORT int af_gemm_tc(void* out, int out_dtype, long long ldo, long long part_stride, const void* x,
                          long long ldx, const void* w, long long ldw, long long n_w_rows, int M, int K, int gated,
-                         int act, int n_acc, float cap, int splits, int* err, cudaStream_t stream) {
+                         int act, int n_acc, float cap, int splits, int per_sm, int* err, cudaStream_t stream) {
   if (M == 0 || n_w_rows == 0) return 0;
   AF_REQUIRE(M > 0 && n_w_rows > 0 && K > 0, "af_gemm_tc: bad sizes %d %lld %d", M, n_w_rows, K);
   AF_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "af_gemm_tc: K %d and row strides must be multiples of 8", K);
@@ -375,6 +379,7 @@ AF_EXPORT int af_gemm_tc(void* out, int out_dtype, long long ldo, long long part
   AF_REQUIRE(!(gated && splits > 1), "af_gemm_tc: the gated variant does not split K");
   AF_REQUIRE(!gated || n_w_rows % 32 == 0, "af_gemm_tc: a gated weight holds whole groups of 16 + 16 rows");
   AF_REQUIRE(n_acc == 1 || n_acc == 2, "af_gemm_tc: %d accumulators", n_acc);
+  AF_REQUIRE(per_sm >= 0 && per_sm <= 2, "af_gemm_tc: %d blocks per SM", per_sm);
   AF_REQUIRE(!gated || act == AF_ACT_GELU_TANH || act == AF_ACT_SILU, "af_gemm_tc: unknown activation %d", act);
   const int total_kb = (K + TC_BK - 1) / TC_BK;
   AF_REQUIRE(splits <= total_kb, "af_gemm_tc: %d splits of %d K blocks", splits, total_kb);
@@ -388,6 +393,7 @@ AF_EXPORT int af_gemm_tc(void* out, int out_dtype, long long ldo, long long part
   if (rc) return rc;
   const int N = gated ? (int)(n_w_rows / 2) : (int)n_w_rows;
   TcArgs a{out, ldo, part_stride, M, N, K, kb_per_split, 0, 0, cap, err};
-  if (out_dtype == AF_BF16) return launch_variant<__nv_bfloat16>(n_acc, gated, act, bn, mw, mx, a, n_w_rows, splits, stream);
-  return launch_variant<float>(n_acc, gated, act, bn, mw, mx, a, n_w_rows, splits, stream);
+  if (out_dtype == AF_BF16)
+    return launch_variant<__nv_bfloat16>(n_acc, gated, act, bn, mw, mx, a, n_w_rows, splits, per_sm, stream);
+  return launch_variant<float>(n_acc, gated, act, bn, mw, mx, a, n_w_rows, splits, per_sm, stream);
 }

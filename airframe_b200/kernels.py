@@ -208,28 +208,62 @@ def rope_cache_write(qkv, positions, inv_freq, nq: int, nkv: int, hd: int, rot_d
         _stream()))
 
 
+_EMPTY_F32 = {}
+
+
+def _no_frequencies(device):
+    key = str(device)
+    if key not in _EMPTY_F32:
+        _EMPTY_F32[key] = torch.empty(0, dtype=torch.float32, device=device)
+    return _EMPTY_F32[key]
+
+
+def store_kv(qkv, batch, nq: int, nkv: int, hd: int, kv, parts=None) -> None:
+    """A mixer's cache store: the k and v heads of the packed rows [q | k | v]
+    go to each token's row of its cache page (``kv``: the layer's view of its
+    pages).  ``parts`` (split-K partial sums of the rows) are added into
+    ``qkv`` first.  Nothing is rotated."""
+    rope_cache_write(qkv, batch.positions, _no_frequencies(qkv.device), nq, nkv, hd, 0, "half",
+                     seq_of_token=batch.seq_of_token, slots=batch.slots, len_after=batch.len_after,
+                     kcache=kv.k, vcache=kv.v, page_table=kv.page_table, ring_rows=kv.ring_rows, parts=parts)
+
+
+def sum_parts(qkv, parts, batch, nq: int, nkv: int, hd: int) -> None:
+    """qkv = the sum of the split-K partial sums ``parts`` (float32 [S, T, width]), in index order."""
+    rope_cache_write(qkv, batch.positions, _no_frequencies(qkv.device), nq, nkv, hd, 0, "half", parts=parts)
+
+
 def attn_prefill_plain(out, q, k, v, positions, nq: int, nkv: int, hd: int, scale: float, cap: float,
-                       window: int) -> None:
+                       window: int, slopes=None) -> None:
     """Attention of prompts that start at position 0 over the step's own keys.
-    q [T, nq*hd], k/v [T, nkv*hd] are row views (any row stride)."""
+    q [T, nq*hd], k/v [T, nkv*hd] are row views (any row stride).  ``slopes``
+    (float32 [nq]): slope[h] * (key position - query position) is added to head
+    h's scores after scale and cap (a position encoding that biases scores)."""
+    if slopes is not None and slopes.numel() != nq:
+        raise KernelError(f"attn_prefill_plain: {slopes.numel()} slopes for {nq} heads")
     T = q.shape[0]
     _check(_lib().af_attn_prefill_plain(
         _ptr(out), c_int(_rows(out, "out")), _ptr(q), c_int(_rows(q, "q")), _ptr(k), c_int(_rows(k, "k")),
         _ptr(v), c_int(_rows(v, "v")), c_int(dtype_code(q.dtype)), _ptr(positions, "positions", torch.int32),
-        c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_float(cap), c_int(window), _stream()))
+        c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_float(cap), c_int(window),
+        _ptr(slopes, "slopes", torch.float32, allow_none=True), _stream()))
 
 
 def attn_decode_plain(out, q, kcache, vcache, page_table, slots, lens, nq: int, nkv: int, hd: int,
-                      scale: float, cap: float, window: int, ring_rows: int) -> None:
-    """Attention of one new token per sequence over the cache pages."""
+                      scale: float, cap: float, window: int, ring_rows: int, slopes=None) -> None:
+    """Attention of one new token per sequence over the cache pages
+    (``slopes`` as in :func:`attn_prefill_plain`)."""
     B = q.shape[0]
+    if slopes is not None and slopes.numel() != nq:
+        raise KernelError(f"attn_decode_plain: {slopes.numel()} slopes for {nq} heads")
     if kcache.dtype != q.dtype:
         raise KernelError("attn_decode_plain: cache dtype differs from the activations'")
     _check(_lib().af_attn_decode_plain(
         _ptr(out), c_int(_rows(out, "out")), _ptr(q), c_int(_rows(q, "q")), _ptr(kcache), _ptr(vcache),
         c_int(dtype_code(q.dtype)), _ptr(page_table, "page_table", torch.int32), c_int(page_table.shape[1]),
         _ptr(slots, "slots", torch.int32), _ptr(lens, "lens", torch.int32), c_int(B), c_int(nq), c_int(nkv),
-        c_int(hd), c_float(scale), c_float(cap), c_int(window), c_int(ring_rows), _stream()))
+        c_int(hd), c_float(scale), c_float(cap), c_int(window), c_int(ring_rows),
+        _ptr(slopes, "slopes", torch.float32, allow_none=True), _stream()))
 
 
 def add_(x, a) -> None:
@@ -307,8 +341,12 @@ def gemm_tc_splits(M: int, N: int, K: int) -> int:
     return (kb + per - 1) // per
 
 
+# Blocks per SM of the weight-bound product (up to 64 tokens): 0 lets the library choose.
+GEMM_TC_PER_SM = 0
+
+
 def gemm_tc(out, x, w, cap: float = 0.0, splits: int = 1, gated: bool = False, activation: str = "gelu_tanh",
-            n_acc: int = 0, checked: bool = False) -> None:
+            n_acc: int = 0, checked: bool = False, per_sm: int = -1) -> None:
     """out = x @ w^T on the tcgen05 tensor cores (bfloat16 operands, 32-bit
     accumulation in TMEM).  splits > 1: out is float32 [splits, M, N] partial
     sums.  gated: w holds, per group of 32 rows, 16 gate rows then the 16 up
@@ -337,7 +375,7 @@ def gemm_tc(out, x, w, cap: float = 0.0, splits: int = 1, gated: bool = False, a
     _check(_lib().af_gemm_tc(_ptr(out), c_int(dtype_code(out.dtype)), c_longlong(ldo), c_longlong(part), _ptr(x),
                              c_longlong(x.stride(0)), _ptr(w), c_longlong(w.stride(0)), c_longlong(rows),
                              c_int(M), c_int(K), c_int(1 if gated else 0), c_int(ACTIVATIONS[activation]),
-                             c_int(n_acc), c_float(cap), c_int(splits),
+                             c_int(n_acc), c_float(cap), c_int(splits), c_int(GEMM_TC_PER_SM if per_sm < 0 else per_sm),
                              _ptr(error_word(x.device), "err", torch.int32), _stream()))
 
 
@@ -385,9 +423,13 @@ def attn_prefill_tc(out, q, k, v, seq_starts, n_seqs: int, max_len: int, nq, nkv
         c_float(cap), c_int(window), _ptr(error_word(q.device), "err", torch.int32), _stream()))
 
 
-def attn_prefill(out, q, k, v, batch, nq, nkv, hd, scale, cap, window) -> None:
+def attn_prefill(out, q, k, v, batch, nq, nkv, hd, scale, cap, window, slopes=None) -> None:
     """Attention of a prefill step: for bfloat16 the tcgen05 kernel (head sizes
-    128, 256) or the mma.sync kernel (64), else the plain kernel."""
+    128, 256) or the mma.sync kernel (64), else the plain kernel (which also
+    serves scores with a per-head slope)."""
+    if slopes is not None:
+        attn_prefill_plain(out, q, k, v, batch.positions, nq, nkv, hd, scale, cap, window, slopes)
+        return
     aligned = all(t.stride(0) % 8 == 0 and t.data_ptr() % 16 == 0 for t in (q, k, v, out))
     if q.dtype == torch.bfloat16 and aligned and _lib().af_attn_prefill_tc_supported(c_int(hd)):
         attn_prefill_tc(out, q, k, v, batch.seq_starts, batch.n_seqs, batch.max_len, nq, nkv, hd, scale, cap, window)
@@ -447,16 +489,17 @@ def attn_decode_split(out, q, kcache, vcache, page_table, slots, lens, nq, nkv, 
         _ptr(error_word(q.device), "err", torch.int32), _stream()))
 
 
-def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window) -> None:
+def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window, slopes=None) -> None:
     """Attention of a decode step over the cache: the split kernel for
-    bfloat16 and head sizes it takes, else the plain kernel."""
-    if q.dtype == torch.bfloat16 and _lib().af_attn_decode_supported(c_int(hd)):
+    bfloat16 and head sizes it takes, else the plain kernel (which also serves
+    scores with a per-head slope)."""
+    if slopes is None and q.dtype == torch.bfloat16 and _lib().af_attn_decode_supported(c_int(hd)):
         n = attn_decode_max_splits(batch.n_seqs, nkv, batch.max_len_after, window)
         attn_decode_split(out, q, kv.k, kv.v, kv.page_table, batch.slots, batch.len_after, nq, nkv, hd, scale, cap,
                           window, kv.ring_rows, n)
         return
     attn_decode_plain(out, q, kv.k, kv.v, kv.page_table, batch.slots, batch.len_after, nq, nkv, hd,
-                      scale, cap, window, kv.ring_rows)
+                      scale, cap, window, kv.ring_rows, slopes)
 
 
 

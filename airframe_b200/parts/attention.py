@@ -76,7 +76,14 @@ class Attention(Mixer):
             parts = qkv.parts
             qkv = torch.empty(x.shape[0], (nq + 2 * nkv) * hd, dtype=x.dtype, device=x.device)
         kv = view.kv
-        self.position.encode_and_store(qkv, batch, nq, nkv, hd, kv if view.writes else None, parts=parts)
+        # positions into q and k, then k and v into the cache: the store is this mixer's; an encoding
+        # that can do both in one kernel says so
+        if not view.writes:
+            self.position.encode(qkv, batch, nq, nkv, hd, parts=parts)
+        elif not self.position.encode_and_store(qkv, batch, nq, nkv, hd, kv, parts=parts):
+            self.position.encode(qkv, batch, nq, nkv, hd, parts=parts)
+            kernels.store_kv(qkv, batch, nq, nkv, hd, kv)
+        slopes = self.position.score_slopes(nq)
         q = qkv[:, : nq * hd]
         k = qkv[:, nq * hd: (nq + nkv) * hd]
         v = qkv[:, (nq + nkv) * hd:]
@@ -87,7 +94,7 @@ class Attention(Mixer):
                 k, v = batch.step_kv[view.cache_id]
             elif view.keep_step_kv:
                 batch.step_kv[view.cache_id] = (k.clone(), v.clone())
-            kernels.attn_prefill(ctx, q, k, v, batch, nq, nkv, hd, self.scale, self.softcap, window)
+            kernels.attn_prefill(ctx, q, k, v, batch, nq, nkv, hd, self.scale, self.softcap, window, slopes)
         else:
-            kernels.attn_decode(ctx, q, kv, batch, nq, nkv, hd, self.scale, self.softcap, window)
+            kernels.attn_decode(ctx, q, kv, batch, nq, nkv, hd, self.scale, self.softcap, window, slopes)
         return linear_split(ctx, self.w_o)

@@ -129,14 +129,30 @@ class Norm(Part):
 
 
 class PositionEncoding(Part):
-    """Applied by a mixer to its packed query/key/value rows."""
+    """How a mixer's queries and keys learn their positions.  An encoding may
+    rewrite the q and k rows (:meth:`encode`, e.g. a rotation), bias the
+    scores (:meth:`score_slopes`), or both; storing keys and values in the
+    cache is the mixer's business, not the encoding's."""
 
-    def encode_and_store(self, qkv, batch, nq: int, nkv: int, hd: int, kv, parts=None) -> None:
-        """Encode positions into the q and k heads of ``qkv`` ([T, (nq + 2 nkv) hd],
-        in place) and, if ``kv`` (a cache view that is written) is given, store
-        k and v in the cache.  ``parts`` (float32 [S, T, width]), when given,
-        are split-K partial sums of the rows: their sum is written to ``qkv`` first."""
-        raise NotImplementedError
+    def encode(self, qkv, batch, nq: int, nkv: int, hd: int, parts=None) -> None:
+        """Encode positions into the q and k heads of the packed rows ``qkv``
+        ([T, (nq + 2 nkv) hd], in place).  ``parts`` (float32 [S, T, width]),
+        when given, are split-K partial sums of the rows: their sum is written
+        to ``qkv`` first.  The default encodes nothing."""
+        if parts is not None:
+            from .. import kernels
+            kernels.sum_parts(qkv, parts, batch, nq, nkv, hd)
+
+    def score_slopes(self, nq: int):
+        """None, or float32 [nq] on the device: slope[h] * (key position -
+        query position) is added to head h's scores after scale and softcap."""
+        return None
+
+    def encode_and_store(self, qkv, batch, nq: int, nkv: int, hd: int, kv, parts=None) -> bool:
+        """Optional fast path: :meth:`encode` and the mixer's cache store in one
+        kernel.  Returns False when the encoding has none (the mixer then calls
+        :meth:`encode` and stores by itself)."""
+        return False
 
 
 class Mixer(Part):
@@ -151,7 +167,13 @@ class Mixer(Part):
     def forward(self, x, batch, view):
         """x [T, H] in the compute dtype (normalised) -> [T, H] in the compute
         dtype, or a :class:`~airframe_b200.parts.linear.PartialSums` of it.  ``batch`` is the :class:`~airframe_b200.engine.batch.StepBatch`,
-        ``view`` the layer's :class:`~airframe_b200.cache.LayerCacheView`."""
+        ``view`` the layer's :class:`~airframe_b200.cache.LayerCacheView`.
+
+        A captured decode step is padded to a fixed number of rows: padding
+        rows carry ``batch.slots[seq] == -1`` (token 0, position 0, length 0).
+        A mixer must not read or write cache pages or per-sequence state for
+        them (they have none) and may leave anything in their output rows;
+        a ``graph_safe`` mixer meets them, others never do."""
         raise NotImplementedError
 
 

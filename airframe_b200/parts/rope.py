@@ -41,38 +41,25 @@ class Rope(PositionEncoding):
     def load(self, weights):
         self.inv_freq = self._inv_freq_host.to(self.ctx.device)
 
-    def encode_and_store(self, qkv, batch, nq, nkv, hd, kv, parts=None):
+    def encode(self, qkv, batch, nq, nkv, hd, parts=None):
         if self.rotary_dim > hd:
             raise ConfigError(f"rope: rotary_dim {self.rotary_dim} exceeds head_dim {hd}")
-        if kv is None:
-            kernels.rope_cache_write(qkv, batch.positions, self.inv_freq, nq, nkv, hd, self.rotary_dim,
-                                     self.pairing, parts=parts)
-        else:
-            kernels.rope_cache_write(qkv, batch.positions, self.inv_freq, nq, nkv, hd, self.rotary_dim,
-                                     self.pairing, seq_of_token=batch.seq_of_token, slots=batch.slots,
-                                     len_after=batch.len_after, kcache=kv.k, vcache=kv.v,
-                                     page_table=kv.page_table, ring_rows=kv.ring_rows, parts=parts)
+        kernels.rope_cache_write(qkv, batch.positions, self.inv_freq, nq, nkv, hd, self.rotary_dim,
+                                 self.pairing, parts=parts)
+
+    def encode_and_store(self, qkv, batch, nq, nkv, hd, kv, parts=None) -> bool:
+        """The rotation and the mixer's cache store as one kernel (the rotated
+        k rows are what the cache keeps)."""
+        if self.rotary_dim > hd:
+            raise ConfigError(f"rope: rotary_dim {self.rotary_dim} exceeds head_dim {hd}")
+        kernels.rope_cache_write(qkv, batch.positions, self.inv_freq, nq, nkv, hd, self.rotary_dim,
+                                 self.pairing, seq_of_token=batch.seq_of_token, slots=batch.slots,
+                                 len_after=batch.len_after, kcache=kv.k, vcache=kv.v,
+                                 page_table=kv.page_table, ring_rows=kv.ring_rows, parts=parts)
+        return True
 
 
 @register_part("position", "none")
 class NoPosition(PositionEncoding):
-    """No encoding: only stores k and v."""
+    """No encoding (the base class's behaviour under a name)."""
     graph_safe = True
-
-
-    def __init__(self, params, ctx):
-        super().__init__(params, ctx)
-        self.inv_freq = None
-
-    def load(self, weights):
-        self.inv_freq = torch.zeros(0, dtype=torch.float32, device=self.ctx.device)
-
-    def encode_and_store(self, qkv, batch, nq, nkv, hd, kv, parts=None):
-        if kv is None:
-            if parts is not None:
-                kernels.rope_cache_write(qkv, batch.positions, self.inv_freq, nq, nkv, hd, 0, "half", parts=parts)
-            return
-        kernels.rope_cache_write(qkv, batch.positions, self.inv_freq, nq, nkv, hd, 0, "half",
-                                 seq_of_token=batch.seq_of_token, slots=batch.slots,
-                                 len_after=batch.len_after, kcache=kv.k, vcache=kv.v,
-                                 page_table=kv.page_table, ring_rows=kv.ring_rows, parts=parts)

@@ -77,13 +77,17 @@ def test_layers_agree_with_the_plain_implementation_and_a_fault_is_named(dtype, 
             got = torch.tensor(facts["first"], dtype=torch.float64)
             assert float((got - want[:20]).abs().max()) <= tol * float(want.abs().max())
     assert first_difference(recs, ref_rms, tol) is None
-    # a fault in layer 2 (its down projection three times too large): the first run that differs is run 2
+    # a fault in layer 2 (half of its down projection's rows three times too large; all of them would be
+    # undone by the norm that follows): the first run that differs is run 2
     bad = tmp_path / "bad"
     shutil.copytree(folder, bad)
     tensors = plain.read_safetensors(bad / "model.safetensors")
     key = "model.layers.2.mlp.down_proj.weight"
-    tensors[key] = (tensors[key].float() * 3.0).to(tensors[key].dtype)
-    write_safetensors(bad / "model.safetensors", tensors)
+    wrong = tensors[key].float()
+    wrong[: wrong.shape[0] // 2] *= 3.0
+    tensors[key] = wrong.to(tensors[key].dtype)
+    write_safetensors(bad / "model.safetensors",
+                      [(n, tuple(t.shape), t.dtype, (lambda t=t: t)) for n, t in tensors.items()])
     assert first_difference(probed(bad), ref_rms, tol) [:2] == (2, 2)
 
 

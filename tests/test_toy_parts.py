@@ -53,27 +53,42 @@ def _register():
 
     @register_part("position", "toy_learned_offset")
     class LearnedOffset(PositionEncoding):
-        """q_h += P[pos], k_h += P[pos] for every head; the framework's own part stores k and v."""
+        """q_h += P[pos], k_h += P[pos] for every head; the mixer stores k and v."""
 
         def __init__(self, params, ctx):
             super().__init__(params, ctx)
             self.name, self.n, self.hd = params["weight"], params["positions"], params["head_dim"]
-            self.store = build_part("position", PartSpec("none"), ctx)
 
         def weight_decls(self):
             return [WeightDecl(self.name, (self.n, self.hd))]
 
         def load(self, weights):
             self.table = weights[self.name].float()
-            self.store.load(weights)
 
-        def encode_and_store(self, qkv, batch, nq, nkv, hd, kv, parts=None):
+        def encode(self, qkv, batch, nq, nkv, hd, parts=None):
             if parts is not None:
                 qkv.copy_(parts.sum(0))
             add = self.table[batch.positions.long()].to(qkv.dtype)            # [T, hd]
             heads = qkv.view(qkv.shape[0], nq + 2 * nkv, hd)
             heads[:, : nq + nkv] += add[:, None, :]
-            self.store.encode_and_store(qkv, batch, nq, nkv, hd, kv)
+
+    @register_part("position", "toy_distance_slopes")
+    class DistanceSlopes(PositionEncoding):
+        """Nothing is written into q or k: head h's scores get slope_h * (key - query), slope_h = base^-(h+1)."""
+        graph_safe = True
+
+        def __init__(self, params, ctx):
+            super().__init__(params, ctx)
+            self.base, self.heads = float(params["base"]), int(params["heads"])
+            self.slopes = None
+
+        def load(self, weights):
+            self.slopes = torch.tensor([self.base ** -(h + 1) for h in range(self.heads)], dtype=torch.float32,
+                                       device=self.ctx.device)
+
+        def score_slopes(self, nq):
+            assert nq == self.heads
+            return self.slopes
     return Top1Experts, LearnedOffset
 
 
@@ -162,6 +177,95 @@ def test_routed_feed_forward_and_learned_positions_step_through_the_engine():
     finally:
         unregister_part("feed_forward", "toy_top1_experts")
         unregister_part("position", "toy_learned_offset")
+        unregister_part("position", "toy_distance_slopes")
+
+
+@pytest.mark.parametrize("dtype,tol", [(torch.float32, FP32_VS_PLAIN), (torch.bfloat16, 3e-2)])
+def test_a_position_encoding_that_biases_scores(dtype, tol):
+    """A slope-times-distance bias on the scores (no rotation, nothing written into q or k), registered from
+    outside: the mixer stores k and v itself, the attention kernels take the slopes, decode steps are
+    captured (the part is graph-safe), and prompts cut in any way give the same logits."""
+    from airframe_b200.config import LayerSpec, ModelSpec, PartSpec, ScheduleEntry
+    from airframe_b200.engine import Engine, Model, StepEntry
+    from airframe_b200.parts import known_parts, unregister_part
+    from airframe_b200.weights import RandomSource, load_weights
+    _register()
+    try:
+        assert "toy_distance_slopes" in known_parts("position")
+        H, V, nq, nkv, hd, I, P = 64, 90, 4, 2, 16, 96, 200
+        base = 2.0
+
+        def norm(name):
+            return PartSpec("rms_norm", {"weight": name, "size": H, "eps": 1e-6, "weight_offset": 1.0})
+
+        layers = []
+        for i in range(2):
+            p = f"l{i}."
+            mixer = PartSpec("attention", {"hidden_size": H, "num_heads": nq, "num_kv_heads": nkv, "head_dim": hd,
+                                           "scale": 0.25, "softcap": 0.0, "window": 70 if i == 0 else None,
+                                           "position": PartSpec("toy_distance_slopes", {"base": base, "heads": nq}),
+                                           "q_weight": p + "q", "k_weight": p + "k", "v_weight": p + "v", "o_weight": p + "o"})
+            ffn = PartSpec("gated_mlp", {"hidden_size": H, "intermediate_size": I, "activation": "silu",
+                                         "gate_weight": p + "g", "up_weight": p + "u", "down_weight": p + "d"})
+            layers.append(LayerSpec(p, PartSpec("prenorm"), mixer, ffn,
+                                    {"pre_mixer": norm(p + "n1"), "pre_feed_forward": norm(p + "n2")}))
+        spec = ModelSpec("toy", H, V, P, PartSpec("token_embedding", {"weight": "emb", "vocab_size": V, "hidden_size": H,
+                                                                      "scale": 1.0}),
+                         layers, [ScheduleEntry(0), ScheduleEntry(1)], norm("nf"),
+                         PartSpec("lm_head", {"vocab_size": V, "hidden_size": H, "softcap": 0.0, "tied_to": "emb"}))
+        model = Model(spec, dtype, DEV)
+        assert model.graph_safe
+        decls = model.weight_decls()
+        wts = load_weights(RandomSource(decls, 12, torch.bfloat16), decls, dtype, DEV)
+        for i in range(2):                               # sharper scores, so that the bias decides something
+            wts[f"l{i}.q"] = wts[f"l{i}.q"] * 20.0
+        model.load(wts)
+        eng = Engine(model, 64 * 12)
+        w = {k: v.double().cpu() for k, v in wts.items()}
+
+        def rms(x, wt):
+            return x * torch.rsqrt((x * x).mean(-1, keepdim=True) + 1e-6) * (1.0 + wt)
+
+        def reference(ids):
+            T = len(ids)
+            x = w["emb"][ids]
+            i_, j_ = torch.arange(T)[:, None], torch.arange(T)[None, :]
+            for i in range(2):
+                p = f"l{i}."
+                h = rms(x, w[p + "n1"])
+                q = (h @ w[p + "q"].T).reshape(T, nq, hd)
+                k = (h @ w[p + "k"].T).reshape(T, nkv, hd)
+                v = (h @ w[p + "v"].T).reshape(T, nkv, hd)
+                mask = plain.visibility(T, 70 if i == 0 else None)
+                ctx = torch.empty(T, nq, hd, dtype=torch.float64)
+                for hh in range(nq):
+                    sc = (q[:, hh] @ k[:, hh // (nq // nkv)].T) * 0.25 + base ** -(hh + 1) * (j_ - i_)
+                    ctx[:, hh] = torch.softmax(sc.masked_fill(~mask, float("-inf")), -1) @ v[:, hh // (nq // nkv)]
+                x = x + ctx.reshape(T, nq * hd) @ w[p + "o"].T
+                h = rms(x, w[p + "n2"])
+                g = h @ w[p + "g"].T
+                x = x + ((g / (1 + torch.exp(-g))) * (h @ w[p + "u"].T)) @ w[p + "d"].T
+            return rms(x, w["nf"]) @ w["emb"].T
+
+        reqs = [replay.random_ids(V, n, 40 + n) for n in (150, 9, 75)]
+        ref = [reference(r) for r in reqs]
+        # the bias matters: without it the logits are others
+        rt = eng_as_runtime(eng)
+        alone = [replay.run_whole(rt, r) for r in reqs]
+        for a, r in zip(alone, ref):
+            assert rel_err(a, r) < tol
+        tails = [replay.run_tail(rt, r, 8) for r in reqs]
+        for t, a, r in zip(tails, alone, ref):
+            assert rel_err(t, r) < tol
+        assert eng.use_graphs and eng._graphs              # the decode steps ran as captured graphs
+        got, _ = replay.run_batches(rt, reqs, 3, [100, 9, 20])
+        for i in range(3):
+            assert rel_err(got[i], ref[i]) < tol
+        assert eng.cache.slots.n_held == 0
+    finally:
+        unregister_part("feed_forward", "toy_top1_experts")
+        unregister_part("position", "toy_learned_offset")
+        unregister_part("position", "toy_distance_slopes")
 
 
 class eng_as_runtime:
