@@ -211,6 +211,63 @@ AF_EXPORT int af_rope_cache_write(void* qkv, int dtype, int row_stride, const fl
   AF_CHECK_LAUNCH("af_rope_cache_write");
 }
 
+// ---------------------------------------------------------------- tables of a step
+
+// (cos, sin) of position * frequency for every token and rotary pair: float [n_tokens][half][2].  Made once
+// per step for all layers that rotate by the same frequencies; 32-bit angles as in the rotary kernels.
+__global__ void rope_table_kernel(float2* __restrict__ table, const int* __restrict__ positions,
+                                  const float* __restrict__ inv_freq, int half) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float pos = (float)positions[t];
+  for (int p = threadIdx.x; p < half; p += blockDim.x) {
+    float s, c;
+    sincosf(pos * inv_freq[p], &s, &c);
+    table[(size_t)t * half + p] = make_float2(c, s);
+  }
+}
+
+AF_EXPORT int af_rope_table(float* table, const int* positions, const float* inv_freq, int n_tokens, int half,
+                            cudaStream_t stream) {
+  if (n_tokens == 0 || half == 0) return 0;
+  AF_REQUIRE(n_tokens > 0 && half > 0 && ((uintptr_t)table & 7) == 0, "af_rope_table: bad sizes");
+  af_launch(rope_table_kernel, dim3(n_tokens), dim3(half < 32 ? 32 : (half > 256 ? 256 : half)), 0, stream,
+            reinterpret_cast<float2*>(table), positions, inv_freq, half);
+  AF_CHECK_LAUNCH("af_rope_table");
+}
+
+// Where each token's keys and values go in the cache of one group of layers: rows[t] = page * nkv * AF_PAGE +
+// row in page (the row of kv head 0; head h lies h * AF_PAGE rows further), or -1 when the token is not stored
+// (a padding row; a token of a long prompt whose ring row a later token of the same step takes).
+__global__ void kv_rows_kernel(int* __restrict__ rows, const int* __restrict__ positions,
+                               const int* __restrict__ seq_of_token, const int* __restrict__ slots,
+                               const int* __restrict__ len_after, const int* __restrict__ page_table, int max_pages,
+                               int ring_rows, int nkv, int n_tokens) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n_tokens) return;
+  const int pos = positions[t], seq = seq_of_token[t], slot = slots[seq];
+  int row = -1;
+  if (slot >= 0 && !(ring_rows > 0 && pos + ring_rows < len_after[seq])) {
+    const int r = ring_rows > 0 ? pos % ring_rows : pos;
+    const int page = page_table[(size_t)slot * max_pages + r / AF_PAGE];
+    row = page * nkv * AF_PAGE + r % AF_PAGE;
+  }
+  rows[t] = row;
+}
+
+AF_EXPORT int af_kv_rows(int* rows, const int* positions, const int* seq_of_token, const int* slots,
+                         const int* len_after, const int* page_table, int max_pages, int ring_rows, int nkv,
+                         int n_tokens, cudaStream_t stream) {
+  if (n_tokens == 0) return 0;
+  AF_REQUIRE(n_tokens > 0 && nkv > 0 && ring_rows % AF_PAGE == 0, "af_kv_rows: bad sizes");
+  af_launch(kv_rows_kernel, dim3((n_tokens + 127) / 128), dim3(128), 0, stream, rows, positions, seq_of_token, slots,
+            len_after, page_table, max_pages, ring_rows, nkv, n_tokens);
+  AF_CHECK_LAUNCH("af_kv_rows");
+}
+
 // ---------------------------------------------------------------- plain attention
 
 // Online-softmax state of one (query, head) held by a warp: lane l owns the

@@ -21,6 +21,22 @@
 // epilogue); split-K (gridDim.z > 1) writes float partial sums [split, M, N]
 // that the consumer adds in order; `cap` > 0 applies cap * tanh(v / cap).
 //
+// ARGMAX (ACT == -3) is the head of greedy decoding: instead of writing logits it keeps, per token, the largest
+// (capped) value and its row: every epilogue warp reduces its 32 rows and joins the result into a 64-bit key per
+// token with one atomicMax (value in order-preserving bits above, ~row below: equal values go to the lowest row),
+// so [tokens, vocabulary] never goes to memory.  Only finite values take part.
+//
+// ROPE (ACT == -2) is the projection of a mixer's packed [q | k | v] rows with the rotary
+// position encoding and the cache write in its epilogue.  The weight's rows are permuted within
+// each head into groups of 32: 16 rows of the head's first half, then the 16 rows they are
+// rotated with (element i pairs with i + head_dim / 2), so that a pair meets inside a warp by
+// one shuffle, as gate and up do.  Cosines and sines come from a table made once per step
+// ([token][pair] of (cos, sin), 32-bit); rotated q, k and plain v go to the output rows in the
+// unpermuted order, and k and v also to each token's row of its cache page.  With split-K the
+// partial tiles go to scratch memory and the last block of a tile to finish (a ticket per tile
+// and epilogue warp) adds them in index order and runs the epilogue: the sum does not depend on
+// who was last.
+//
 // Every wait on an mbarrier is bounded in time.  A wait that runs out sets an
 // error word that the host reads after the launch; the CTA then lets its
 // copies in flight land, releases its TMEM and returns.
@@ -68,7 +84,23 @@ struct TcArgs {
                           // blockIdx.x, blockIdx.x + gridDim.x, ... (token tile fastest)
   float cap;
   int* err;
+  // ROPE only
+  const float2* rope_table;  // [M][hd / 2] (cos, sin) of each token's position
+  const int* kv_rows;        // [M] row of the token in the cache for kv head 0 (-1: not stored), or null
+  __nv_bfloat16* kcache;     // pages [.., kv heads, AF_PAGE, hd]
+  __nv_bfloat16* vcache;
+  int hd, nq, nkv;
+  float* parts;              // split-K: [splits][M][N] partial sums
+  int* tickets;              // split-K: a counter per tile, zero between launches
+  // ARGMAX only
+  unsigned long long* keys;  // [M] best (value, row) per token, zero before the launch
 };
+
+// Float bits whose unsigned order is the floats' order.
+__device__ __forceinline__ uint32_t tc_ordered_bits(float v) {
+  const uint32_t b = __float_as_uint(v);
+  return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
+}
 
 // ACT: -1 plain product, else the gated epilogue's activation.  PER_SM: 2 halves the stages so that
 // two blocks share an SM (grids of several waves: one block's fill and drain hide behind the other).
@@ -76,6 +108,8 @@ template <int BN, int NACC, int ACT, typename TO, int PER_SM>
 __global__ void __launch_bounds__(TC_THREADS, PER_SM)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x, TcArgs a) {
   constexpr bool GATED = ACT >= 0;
+  constexpr bool ROPE = ACT == -2;
+  constexpr bool ARGMAX = ACT == -3;
   constexpr int STAGES = tc_stages(BN, NACC, PER_SM);
   constexpr int A_BYTES = TC_BM * TC_BK * 2;
   constexpr int STAGE_BYTES = tc_stage_bytes(BN, NACC);
@@ -212,6 +246,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
         // the output feature of this lane: a weight row, or for GATED the feature whose gate row it is
         const int wt = tile_w * NACC + acc;
         const int f = GATED ? wt * 64 + quarter * 16 + (lane & 15) : wt * TC_BM + quarter * 32 + lane;
+        // ROPE: this warp's 32 weight rows are one group of a head: pairs p .. p + 15, low lanes the first half
+        const int g_row0 = (wt * 4 + quarter) * 32;
+        const int rp_head = ROPE ? g_row0 / a.hd : 0;
+        const int rp_pair = ROPE ? ((g_row0 % a.hd) >> 5) * 16 + (lane & 15) : 0;
 #pragma unroll 1
         for (int c0 = 0; c0 < BN; c0 += CW) {
           float v[CW];
@@ -227,6 +265,75 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty);
+          }
+          if constexpr (ROPE) {
+            const int half = a.hd >> 1;
+            const bool live = g_row0 < a.N;              // (whole groups: N is a multiple of 32)
+            if constexpr (BN <= 64 && NACC == 1) {
+              if (gridDim.z > 1) {
+                // split-K: leave this warp's part of the partial tile and take a ticket for its 32 rows; the
+                // last of the tile's blocks to come adds all parts in index order.  (A ticket per warp, so that
+                // no block-wide barrier stands behind a wait that may give up.)
+                float* part = a.parts + (size_t)blockIdx.z * a.part_stride;
+                if (live) {
+#pragma unroll
+                  for (int j = 0; j < CW; ++j)
+                    if (m0 + j < a.M) part[(size_t)(m0 + j) * a.N + g_row0 + lane] = v[j];
+                }
+                __threadfence();
+                __syncwarp();
+                int ticket = 0;
+                if (lane == 0) ticket = atomicAdd(a.tickets + tile * 4 + quarter, 1);
+                ticket = __shfl_sync(0xffffffffu, ticket, 0);
+                if (ticket != (int)gridDim.z - 1) continue;          // (not the last: done)
+                __threadfence();
+                if (lane == 0) a.tickets[tile * 4 + quarter] = 0;    // every block of the tile has taken its ticket
+#pragma unroll
+                for (int j = 0; j < CW; ++j) v[j] = 0.f;
+                if (live) {
+                  for (int sp = 0; sp < (int)gridDim.z; ++sp) {
+                    const float* ps = a.parts + (size_t)sp * a.part_stride + g_row0 + lane;
+#pragma unroll
+                    for (int j = 0; j < CW; ++j)
+                      if (m0 + j < a.M) v[j] += __ldcg(ps + (size_t)(m0 + j) * a.N);
+                  }
+                }
+              }
+            }
+            const bool hi = lane >= 16;
+            const bool rotate = rp_head < a.nq + a.nkv;
+            const int d = rp_pair + (hi ? half : 0);
+            const bool is_kv = rp_head >= a.nq && a.kv_rows != nullptr;
+            const bool is_v = rp_head >= a.nq + a.nkv;
+            __nv_bfloat16* cache = is_v ? a.vcache : a.kcache;
+            const int kvh = rp_head - a.nq - (is_v ? a.nkv : 0);
+            // Cosines, sines and cache rows of 16 tokens are fetched together before the first store: a load
+            // that stands behind a store in the program is not moved before it by the compiler, and the loads
+            // of a loop that stores as it goes would pay the memory's latency one after the other.
+#pragma unroll
+            for (int j0 = 0; j0 < CW; j0 += 16) {
+              float2 cs[16];
+              int crow[16];
+#pragma unroll
+              for (int u = 0; u < 16; ++u) {
+                const int tok = m0 + c0 + j0 + u;
+                const bool on = live && tok < a.M;
+                cs[u] = on && rotate ? __ldg(a.rope_table + (size_t)tok * half + rp_pair) : make_float2(1.f, 0.f);
+                crow[u] = on && is_kv ? __ldg(a.kv_rows + tok) : -1;
+              }
+#pragma unroll
+              for (int u = 0; u < 16; ++u) {
+                const int j = j0 + u;
+                const int tok = m0 + c0 + j;
+                const float other = __shfl_xor_sync(0xffffffffu, v[j], 16);
+                if (!live || tok >= a.M) continue;
+                const float r = hi ? v[j] * cs[u].x + other * cs[u].y : v[j] * cs[u].x - other * cs[u].y;
+                const __nv_bfloat16 rb = __float2bfloat16_rn(r);
+                reinterpret_cast<__nv_bfloat16*>(a.out)[(size_t)tok * a.ldo + (size_t)rp_head * a.hd + d] = rb;
+                if (crow[u] >= 0) cache[((size_t)crow[u] + (size_t)kvh * AF_PAGE) * a.hd + d] = rb;
+              }
+            }
+            continue;
           }
           if (GATED) {
             // Within a warp lanes 0..15 hold gate rows and lanes 16..31 the up rows of the
@@ -244,6 +351,22 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           if (a.cap > 0.f) {  // (fully unrolled: v stays in registers)
 #pragma unroll
             for (int j = 0; j < CW; ++j) v[j] = a.cap * tanhf(v[j] / a.cap);
+          }
+          if constexpr (ARGMAX) {
+#pragma unroll
+            for (int j = 0; j < CW; ++j) {
+              const bool has = f < a.N && isfinite(v[j]);
+              unsigned long long key =
+                  has ? ((unsigned long long)tc_ordered_bits(v[j]) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)f)
+                      : 0ull;
+#pragma unroll
+              for (int o = 16; o > 0; o >>= 1) {
+                const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
+                key = other > key ? other : key;
+              }
+              if (lane == 0 && key != 0ull && m0 + c0 + j < a.M) atomicMax(a.keys + m0 + c0 + j, key);
+            }
+            continue;
           }
           if (GATED) {
             // lane l and lane l + 16 write the same feature, for the first and the second half of the tokens
@@ -350,6 +473,22 @@ int launch_variant(int nacc, int gated, int act, int bn, const CUtensorMap& mw, 
   return launch_bn<1, -1, TO>(bn, mw, mx, a, rows, splits, per_sm, s);
 }
 
+// Tensor maps of the two operands and the checks both entry points share.
+int prepare(CUtensorMap* mw, CUtensorMap* mx, const char* who, const void* x, long long ldx, const void* w, long long ldw,
+            long long n_w_rows, int M, int K, int splits, int* kb_per_split, int* bn) {
+  AF_REQUIRE(M > 0 && n_w_rows > 0 && K > 0, "%s: bad sizes %d %lld %d", who, M, n_w_rows, K);
+  AF_REQUIRE(K % 8 == 0 && ldx % 8 == 0 && ldw % 8 == 0, "%s: K %d and row strides must be multiples of 8", who, K);
+  AF_REQUIRE(((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0, "%s: operands must be 16-byte aligned", who);
+  const int total_kb = (K + TC_BK - 1) / TC_BK;
+  AF_REQUIRE(splits >= 1 && splits <= total_kb, "%s: %d splits of %d K blocks", who, splits, total_kb);
+  *kb_per_split = (total_kb + splits - 1) / splits;
+  AF_REQUIRE((splits - 1) * *kb_per_split < total_kb, "%s: an empty K split", who);
+  *bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  int rc = af_make_map_bf16(mw, w, n_w_rows, K, ldw, TC_BM);
+  if (rc) return rc;
+  return af_make_map_bf16(mx, x, M, K, ldx, *bn);
+}
+
 }  // namespace
 
 // The token tile the kernel uses for M rows.
@@ -381,19 +520,77 @@ AF_EXPORT int af_gemm_tc(void* out, int out_dtype, long long ldo, long long part
   AF_REQUIRE(n_acc == 1 || n_acc == 2, "af_gemm_tc: %d accumulators", n_acc);
   AF_REQUIRE(per_sm >= 0 && per_sm <= 2, "af_gemm_tc: %d blocks per SM", per_sm);
   AF_REQUIRE(!gated || act == AF_ACT_GELU_TANH || act == AF_ACT_SILU, "af_gemm_tc: unknown activation %d", act);
-  const int total_kb = (K + TC_BK - 1) / TC_BK;
-  AF_REQUIRE(splits <= total_kb, "af_gemm_tc: %d splits of %d K blocks", splits, total_kb);
-  const int kb_per_split = (total_kb + splits - 1) / splits;
-  AF_REQUIRE((splits - 1) * kb_per_split < total_kb, "af_gemm_tc: an empty K split");
-  const int bn = af_gemm_tc_token_tile(M);
+  int kb_per_split = 0, bn = 0;
   CUtensorMap mw, mx;
-  int rc = af_make_map_bf16(&mw, w, n_w_rows, K, ldw, TC_BM);
-  if (rc) return rc;
-  rc = af_make_map_bf16(&mx, x, M, K, ldx, bn);
+  const int rc = prepare(&mw, &mx, "af_gemm_tc", x, ldx, w, ldw, n_w_rows, M, K, splits, &kb_per_split, &bn);
   if (rc) return rc;
   const int N = gated ? (int)(n_w_rows / 2) : (int)n_w_rows;
   TcArgs a{out, ldo, part_stride, M, N, K, kb_per_split, 0, 0, cap, err};
   if (out_dtype == AF_BF16)
     return launch_variant<__nv_bfloat16>(n_acc, gated, act, bn, mw, mx, a, n_w_rows, splits, per_sm, stream);
   return launch_variant<float>(n_acc, gated, act, bn, mw, mx, a, n_w_rows, splits, per_sm, stream);
+}
+
+
+// The projection of a mixer's packed rows with rotary encoding and cache write in its epilogue:
+// out[M, n_w_rows] bfloat16 = rotated q heads | rotated k heads | v heads, where w [(nq + 2 nkv) hd, K] holds
+// the heads' rows permuted into groups of 32 (16 rows of a head's first half, then the 16 rows hd / 2 further on;
+// head_dim a multiple of 32), and out is written in the unpermuted order.  rope_table: float [M][hd / 2][2]
+// (cos, sin).  kv_rows (or null: nothing is stored): int [M], the row of each token in the cache for kv head 0
+// (page * nkv * 64 + row in page; -1: skip), kcache / vcache the layer's pages.  splits > 1 (up to 64 tokens
+// only): parts is float [splits][M][n_w_rows] scratch, tickets int [4 * tiles] that are zero between launches.
+AF_EXPORT int af_gemm_tc_rope(void* out, long long ldo, const void* x, long long ldx, const void* w, long long ldw,
+                              long long n_w_rows, int M, int K, int n_acc, int splits, float* parts, int* tickets,
+                              const float* rope_table, const int* kv_rows, void* kcache, void* vcache, int hd,
+                              int nq, int nkv, int per_sm, int* err, cudaStream_t stream) {
+  if (M == 0) return 0;
+  AF_REQUIRE(hd > 0 && hd % 32 == 0 && nq > 0 && nkv > 0 && n_w_rows == (long long)(nq + 2 * nkv) * hd,
+             "af_gemm_tc_rope: %lld rows are not (%d + 2 x %d) heads of %d (a multiple of 32)", n_w_rows, nq, nkv, hd);
+  AF_REQUIRE(rope_table != nullptr && ((uintptr_t)rope_table & 7) == 0, "af_gemm_tc_rope: the table of cosines and sines");
+  AF_REQUIRE(kv_rows == nullptr || (kcache != nullptr && vcache != nullptr), "af_gemm_tc_rope: cache pages");
+  AF_REQUIRE(n_acc == 1 || n_acc == 2, "af_gemm_tc_rope: %d accumulators", n_acc);
+  AF_REQUIRE(per_sm >= 0 && per_sm <= 2, "af_gemm_tc_rope: %d blocks per SM", per_sm);
+  AF_REQUIRE(splits == 1 || (M <= 64 && n_acc == 1 && parts != nullptr && tickets != nullptr),
+             "af_gemm_tc_rope: split-K serves up to 64 tokens and needs scratch and tickets");
+  int kb_per_split = 0, bn = 0;
+  CUtensorMap mw, mx;
+  const int rc = prepare(&mw, &mx, "af_gemm_tc_rope", x, ldx, w, ldw, n_w_rows, M, K, splits, &kb_per_split, &bn);
+  if (rc) return rc;
+  TcArgs a{out, ldo, (long long)M * n_w_rows, M, (int)n_w_rows, K, kb_per_split, 0, 0, 0.f, err};
+  a.rope_table = reinterpret_cast<const float2*>(rope_table);
+  a.kv_rows = kv_rows;
+  a.kcache = (__nv_bfloat16*)kcache;
+  a.vcache = (__nv_bfloat16*)vcache;
+  a.hd = hd;
+  a.nq = nq;
+  a.nkv = nkv;
+  a.parts = parts;
+  a.tickets = tickets;
+  if (n_acc == 2) return launch_bn<2, -2, __nv_bfloat16>(bn, mw, mx, a, n_w_rows, splits, per_sm, stream);
+  return launch_bn<1, -2, __nv_bfloat16>(bn, mw, mx, a, n_w_rows, splits, per_sm, stream);
+}
+
+// The head of greedy decoding: keys[m] = max over the rows n of (softcap(x[m] . w[n]), n) as a 64-bit key (see
+// the ARGMAX epilogue); keys must be zero before the call; af_argmax_finish turns them into token ids and
+// zeroes them again.
+AF_EXPORT int af_gemm_tc_argmax(unsigned long long* keys, const void* x, long long ldx, const void* w, long long ldw,
+                                long long n_w_rows, int M, int K, float cap, int per_sm, int* err,
+                                cudaStream_t stream) {
+  if (M == 0) return 0;
+  AF_REQUIRE(keys != nullptr && ((uintptr_t)keys & 7) == 0, "af_gemm_tc_argmax: keys");
+  AF_REQUIRE(n_w_rows < 0xffffffffll, "af_gemm_tc_argmax: %lld rows", n_w_rows);
+  AF_REQUIRE(per_sm >= 0 && per_sm <= 2, "af_gemm_tc_argmax: %d blocks per SM", per_sm);
+  int kb_per_split = 0, bn = 0;
+  CUtensorMap mw, mx;
+  const int rc = prepare(&mw, &mx, "af_gemm_tc_argmax", x, ldx, w, ldw, n_w_rows, M, K, 1, &kb_per_split, &bn);
+  if (rc) return rc;
+  TcArgs a{nullptr, 0, 0, M, (int)n_w_rows, K, kb_per_split, 0, 0, cap, err};
+  a.keys = keys;
+  return launch_bn<1, -3, float>(bn, mw, mx, a, n_w_rows, 1, per_sm, stream);
+}
+
+// How many tickets af_gemm_tc_rope needs for these sizes.
+AF_EXPORT int af_gemm_tc_rope_tickets(int M, long long n_w_rows) {
+  const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : M <= 128 ? 128 : 256;
+  return (int)(4 * ((n_w_rows + TC_BM - 1) / TC_BM) * ((M + bn - 1) / bn));
 }

@@ -39,6 +39,9 @@ class StepBatch:
     n_want: int = 0
     max_len_after: int = 0              # host: longest sequence after the step
     step_kv: dict = field(default_factory=dict)   # cache id -> (k, v) of this step, for runs that share a cache
+    # what parts make once per forward pass and share between layers (a table of rotary cosines and sines,
+    # the tokens' rows in a group's cache pages); emptied when a pass begins
+    aux: dict = field(default_factory=dict)
 
 
 def build_batch(entries, lens_before, device, pad_to: int = 0) -> StepBatch:

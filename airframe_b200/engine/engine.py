@@ -88,26 +88,32 @@ class Engine:
             raise StepError("sequences that go on bring one token each")
         return lens
 
-    def step(self, entries, pad_to: int = 0, borrow: bool = False, probe=None):
+    fused_greedy = True     # step(..., greedy=True) and decode_rows(..., greedy=True) give tokens instead of logits
+
+    def step(self, entries, pad_to: int = 0, borrow: bool = False, probe=None, greedy: bool = False):
         """Run one step.  Returns float32 logits [wanted, vocab] on the device,
         in the order of the entries and of their ``want`` lists, or None when
         nothing is wanted.  ``borrow``: the caller uses the logits before the
         next step and may get a buffer that the next step overwrites (saves a
         copy when the step ran as a CUDA graph).  ``probe``: a
         :class:`~airframe_b200.engine.probe.LayerProbe` that is shown the
-        residual stream after every run (the step then runs kernel by kernel)."""
+        residual stream after every run (the step then runs kernel by kernel).
+        ``greedy``: instead of logits, the arg-max token at every wanted place
+        (int32 [wanted] on the device; the logits are not written where the
+        head can find the best without them)."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         lens = self.check(entries)
         growth = {e.slot: n + len(e.tokens) for e, n in zip(entries, lens)}
         self.cache.reserve(growth)
         self.cache.flush()
         if probe is None and self.use_graphs and lens[0] > 0 and all(e.want == [0] for e in entries):
-            logits = self._decode_graphed([e.slot for e in entries], lens, tokens=[e.tokens[0] for e in entries])
+            logits = self._decode_graphed([e.slot for e in entries], lens, tokens=[e.tokens[0] for e in entries],
+                                          greedy=greedy)
             if not borrow:
                 logits = logits.clone()
         else:
             batch = build_batch(entries, lens, self.device, pad_to=pad_to)
-            logits = self.model.forward(batch, self.cache, probe)
+            logits = self.model.forward(batch, self.cache, probe, greedy=greedy)
         self.cache.commit(growth)
         return logits
 
@@ -122,13 +128,14 @@ class Engine:
                 return b
         return (n + 127) // 128 * 128
 
-    def decode_rows(self, slots, tokens_dev, borrow: bool = True):
+    def decode_rows(self, slots, tokens_dev, borrow: bool = True, greedy: bool = False):
         """One decode step whose tokens are already on the device (the sampler's
         output of the step before): row r carries the next token ``tokens_dev[r]``
         of the sequence in ``slots[r]``; a row with slot None is not used.  Rows keep
         their places from step to step, so the host can queue this step before it has
         read the tokens themselves.  Needs CUDA graphs (``use_graphs``).  Returns the
-        logits of all rows [len(slots), vocab]."""
+        logits of all rows [len(slots), vocab], or with ``greedy`` their arg-max
+        tokens (int32 [len(slots)])."""
         if not self.use_graphs:
             raise StepError("decode_rows needs captured decode steps")
         live = [s for s in slots if s is not None]
@@ -145,11 +152,12 @@ class Engine:
         growth = {s: n + 1 for s, n in zip(slots, lens) if s is not None}
         self.cache.reserve(growth)
         self.cache.flush()
-        logits = self._decode_graphed([-1 if s is None else s for s in slots], lens, tokens_dev=tokens_dev)
+        logits = self._decode_graphed([-1 if s is None else s for s in slots], lens, tokens_dev=tokens_dev,
+                                      greedy=greedy)
         self.cache.commit(growth)
         return logits if borrow else logits.clone()
 
-    def _decode_graphed(self, slots, lens, tokens=None, tokens_dev=None):
+    def _decode_graphed(self, slots, lens, tokens=None, tokens_dev=None, greedy: bool = False):
         """One decode step, every row wanting its token's logits, through a CUDA
         graph.  Rows with slot -1 are padding.  The tokens come from the host
         (``tokens``) or lie on the device already (``tokens_dev``).  The result is
@@ -157,10 +165,11 @@ class Engine:
         padded size."""
         B = len(slots)
         Bp = self.padded_batch(B)
-        g = self._graphs.get(Bp)
+        key = (Bp, "greedy") if greedy else Bp
+        g = self._graphs.get(key)
         if g is None:
-            g = self._capture(Bp)
-            self._graphs[Bp] = g
+            g = self._capture(Bp, greedy)
+            self._graphs[key] = g
         # two pinned staging buffers in turn: one may still be in flight when the next step is laid out
         k = g["turn"] = g["turn"] ^ 1
         host, sent = g["host"][k], g["sent"][k]
@@ -184,7 +193,7 @@ class Engine:
         self.replayed_launches += g["launches"]
         return g["logits"][:B]
 
-    def _capture(self, Bp: int) -> dict:
+    def _capture(self, Bp: int, greedy: bool = False) -> dict:
         dev = self.device
         # [tokens | positions | slots | len_after] change every step; the rest is fixed
         dynamic = torch.zeros(4 * Bp, dtype=torch.int32, device=dev)
@@ -201,14 +210,14 @@ class Engine:
         side = torch.cuda.Stream(device=dev)
         side.wait_stream(torch.cuda.current_stream(dev))
         with torch.cuda.stream(side):
-            self.model.forward(batch, self.cache)
+            self.model.forward(batch, self.cache, greedy=greedy)
         torch.cuda.current_stream(dev).wait_stream(side)
         torch.cuda.synchronize(dev)
         from .. import kernels
         graph = torch.cuda.CUDAGraph()
         n0 = kernels.launch_count()
         with torch.cuda.graph(graph):
-            logits = self.model.forward(batch, self.cache)
+            logits = self.model.forward(batch, self.cache, greedy=greedy)
         return {"graph": graph, "dynamic": dynamic, "logits": logits, "batch": batch, "fixed": fixed,
                 "launches": kernels.launch_count() - n0, "turn": 0,
                 "host": (hosts := [torch.empty(4 * Bp, dtype=torch.int32).pin_memory() for _ in range(2)]),

@@ -225,12 +225,17 @@ class GenerationLoop:
         """The device one step ahead of the host.  Row r of every decode step
         belongs to seqs[r]; a sequence that has ended leaves its row unused."""
         eng, smp = self.engine, self.sampler
-        logits = eng.step([StepEntry(s.slot, s.prompt, [len(s.prompt) - 1]) for s in seqs])
+        # greedy decoding with an engine whose head finds the best token itself: the steps give tokens,
+        # not logits, and the sampler only brings them to the host
+        fused = bool(params.greedy and getattr(eng, "fused_greedy", False) and hasattr(smp, "adopt"))
+        kw = {"greedy": True} if fused else {}
+        logits = eng.step([StepEntry(s.slot, s.prompt, [len(s.prompt) - 1]) for s in seqs], **kw)
         for s in seqs:
             s.length = len(s.prompt)
         n = len(seqs)
         sampled = [1] * n                       # samples asked for per row, the one in flight included
-        pend = smp.sample_async(logits, [s.state for s in seqs], params)
+        pend = (smp.adopt(logits, [s.state for s in seqs]) if fused
+                else smp.sample_async(logits, [s.state for s in seqs], params))
         pend_rows = list(range(n))              # rows whose tokens `pend` carries
         while True:
             # rows that go on whatever their token in flight is, unless it is a stop token
@@ -240,8 +245,9 @@ class GenerationLoop:
             nxt = None
             if go:
                 on = set(go)
-                logits = eng.decode_rows([seqs[r].slot if r in on else None for r in range(n)], pend.device)
-                nxt = smp.sample_async(logits, [seqs[r].state if r in on else None for r in range(n)], params)
+                logits = eng.decode_rows([seqs[r].slot if r in on else None for r in range(n)], pend.device, **kw)
+                states = [seqs[r].state if r in on else None for r in range(n)]
+                nxt = smp.adopt(logits, states) if fused else smp.sample_async(logits, states, params)
             # now the tokens in flight (the next step is queued behind them)
             tokens = pend.result()
             for r in pend_rows:

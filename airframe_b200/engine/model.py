@@ -81,6 +81,7 @@ class Model:
         """The float32 residual stream [T, H] after all scheduled runs.
         ``probe`` (a :class:`~airframe_b200.engine.probe.LayerProbe`) is shown
         the stream after the embedding and after every run."""
+        batch.aux.clear()       # (a captured step's tables are made inside the capture, not left from the run before)
         x = self.embedding.forward(batch.tokens)
         if probe is not None:
             probe.after(-1, -1, x, batch)
@@ -99,11 +100,25 @@ class Model:
         y = self.final_norm.forward(x, self.ctx.compute_dtype, rows=want_rows)
         return self.head.forward(y)
 
-    def forward(self, batch, cache, probe=None):
+    def greedy_tokens(self, x, want_rows) -> torch.Tensor:
+        """int32 [R]: the arg-max token at the wanted rows (a head that can, finds
+        it without writing the logits)."""
+        y = self.final_norm.forward(x, self.ctx.compute_dtype, rows=want_rows)
+        best = getattr(self.head, "forward_argmax", None)
+        if best is not None:
+            return best(y)
+        from .. import kernels
+        logits = self.head.forward(y)
+        tokens = torch.empty(logits.shape[0], dtype=torch.int32, device=logits.device)
+        kernels.sample(logits, tokens, 0.0, 1.0, 1.0)
+        return tokens
+
+    def forward(self, batch, cache, probe=None, greedy: bool = False):
+        """Logits at the wanted rows, or with ``greedy`` their arg-max tokens."""
         x = self.hidden(batch, cache, probe)
         if batch.want_rows is None:
             return None
-        return self.logits(x, batch.want_rows)
+        return self.greedy_tokens(x, batch.want_rows) if greedy else self.logits(x, batch.want_rows)
 
 
 def declared_weights(spec: ModelSpec) -> list:

@@ -54,14 +54,23 @@ class LayerProbe:
         return self.records
 
 
-def first_difference(records, reference_rms, tolerance: float):
-    """The first run whose RMS differs from ``reference_rms[run][row]`` by more
-    than ``tolerance`` (relative), as (run, layer, row), or None."""
+def first_difference(records, reference, tolerance: float):
+    """The first run whose facts differ from another implementation's by more
+    than ``tolerance`` (relative), as (run, layer, row), or None.
+    ``reference[run][row]`` is that implementation's float row (any sequence of
+    floats, at least as long as the recorded first values): the RMS of the
+    whole row is compared and, value by value, its first elements (relative to
+    the largest of them)."""
     for rec in records:
-        if rec["run"] < 0 or rec["run"] >= len(reference_rms):
+        if rec["run"] < 0 or rec["run"] >= len(reference):
             continue
         for r, facts in enumerate(rec["rows"]):
-            ref = reference_rms[rec["run"]][r]
-            if abs(facts["rms"] - ref) > tolerance * max(abs(ref), 1e-30):
+            ref = np.asarray(reference[rec["run"]][r], dtype=np.float64)
+            ref_rms = float(np.sqrt(np.mean(ref ** 2)))
+            if abs(facts["rms"] - ref_rms) > tolerance * max(ref_rms, 1e-30):
+                return rec["run"], rec["layer"], r
+            got = np.asarray(facts["first"], dtype=np.float64)
+            want = ref[: got.size]
+            if got.size and float(np.abs(got - want).max()) > tolerance * max(float(np.abs(want).max()), 1e-30):
                 return rec["run"], rec["layer"], r
     return None

@@ -47,11 +47,14 @@ class GpuRuntime:
     # ------------------------------------------------------------------ construction
 
     @classmethod
-    def _build(cls, config, source, dtype, device, max_tokens, max_context, max_sequences):
+    def _build(cls, config, source, dtype, device, max_tokens, max_context, max_sequences, spec_edit=None):
         device = _require_gpu(device)
         dt = _dtype(dtype)
         torch.cuda.set_device(device)
-        model = Model(config.model_spec(), dt, device)
+        spec = config.model_spec()
+        if spec_edit is not None:
+            spec_edit(spec)
+        model = Model(spec, dt, device)
         model.load(load_weights(source, model.weight_decls(), dt, device))
         limit = model.spec.max_positions
         ctx = min(max_context or DEFAULT_SAFE_CTX, limit)
@@ -60,27 +63,29 @@ class GpuRuntime:
 
     @classmethod
     def load(cls, path, dtype="bfloat16", device="cuda:0", max_tokens: Optional[int] = None,
-             max_context: Optional[int] = None, max_sequences: Optional[int] = None) -> "GpuRuntime":
+             max_context: Optional[int] = None, max_sequences: Optional[int] = None, spec_edit=None) -> "GpuRuntime":
         """Load a model folder (config.json, model.safetensors).  ``max_tokens``
-        sizes the cache: the most tokens that live sequences hold together."""
+        sizes the cache: the most tokens that live sequences hold together.
+        ``spec_edit(spec)`` may change the :class:`~airframe_b200.config.ModelSpec`
+        before the model is built (options of parts that config.json does not carry)."""
         config = config_from_folder(path)
         source = SafetensorsFolder(path)
         try:
-            return cls._build(config, source, dtype, device, max_tokens, max_context, max_sequences)
+            return cls._build(config, source, dtype, device, max_tokens, max_context, max_sequences, spec_edit)
         finally:
             source.close()
 
     @classmethod
     def random(cls, config: ModelConfig, seed: int = 0, dtype="bfloat16", device="cuda:0",
                max_tokens: Optional[int] = None, max_context: Optional[int] = None,
-               max_sequences: Optional[int] = None, on_device: bool = False) -> "GpuRuntime":
+               max_sequences: Optional[int] = None, on_device: bool = False, spec_edit=None) -> "GpuRuntime":
         """A model of ``config`` with seeded random weights, without a folder.
         ``on_device`` draws them on the GPU (fast for large models; the values
         then differ from a folder written with the same seed)."""
         decls = Model(config.model_spec(), torch.bfloat16, "cpu").weight_decls()
         store = torch.float32 if _dtype(dtype) == torch.float32 else torch.bfloat16
         source = RandomSource(decls, seed, store_dtype=store, device=device if on_device else "cpu")
-        return cls._build(config, source, dtype, device, max_tokens, max_context, max_sequences)
+        return cls._build(config, source, dtype, device, max_tokens, max_context, max_sequences, spec_edit)
 
     # ------------------------------------------------------------------ use
 

@@ -379,6 +379,105 @@ def gemm_tc(out, x, w, cap: float = 0.0, splits: int = 1, gated: bool = False, a
                              _ptr(error_word(x.device), "err", torch.int32), _stream()))
 
 
+def rope_table(positions, inv_freq) -> torch.Tensor:
+    """float32 [T, pairs, 2]: (cos, sin) of position * frequency for every token
+    of the step and every rotary pair (32-bit angles)."""
+    T, half = positions.shape[0], inv_freq.numel()
+    table = torch.empty(T, half, 2, dtype=torch.float32, device=positions.device)
+    _check(_lib().af_rope_table(_ptr(table), _ptr(positions, "positions", torch.int32),
+                                _ptr(inv_freq, "inv_freq", torch.float32), c_int(T), c_int(half), _stream()))
+    return table
+
+
+def kv_rows(batch, kv, nkv: int) -> torch.Tensor:
+    """int32 [T]: each token's row in the cache pages of ``kv`` (a layer's view;
+    all layers of its group share the page table) for kv head 0, -1 for tokens
+    that are not stored."""
+    T = batch.tokens.shape[0]
+    rows = torch.empty(T, dtype=torch.int32, device=batch.tokens.device)
+    _check(_lib().af_kv_rows(_ptr(rows), _ptr(batch.positions, "positions", torch.int32),
+                             _ptr(batch.seq_of_token, "seq_of_token", torch.int32),
+                             _ptr(batch.slots, "slots", torch.int32), _ptr(batch.len_after, "len_after", torch.int32),
+                             _ptr(kv.page_table, "page_table", torch.int32), c_int(kv.page_table.shape[1]),
+                             c_int(kv.ring_rows), c_int(nkv), c_int(T), _stream()))
+    return rows
+
+
+def rope_row_order(n_heads: int, hd: int, device=None) -> torch.Tensor:
+    """The order of a packed [q | k | v] weight's rows that :func:`gemm_tc_rope`
+    wants: within every head, groups of 32 rows, each the 16 rows p .. p + 15
+    of the head's first half followed by the rows p + hd / 2 .. that they are
+    rotated with.  Returns the old row index of every new row (int64)."""
+    if hd % 32:
+        raise KernelError(f"rope_row_order: head_dim {hd} is not a multiple of 32")
+    i = torch.arange(hd, device=device)
+    within = (i // 32) * 16 + i % 16 + (i % 32 >= 16) * (hd // 2)
+    return (torch.arange(n_heads, device=device)[:, None] * hd + within[None, :]).reshape(-1)
+
+
+def gemm_tc_rope_supported(x, w, hd: int) -> bool:
+    return hd % 32 == 0 and gemm_tc_supported(x, w, None)
+
+
+def gemm_tc_rope(out, x, w, table, nq: int, nkv: int, hd: int, rows=None, kcache=None, vcache=None,
+                 splits: int = 1, tickets=None, n_acc: int = 0, per_sm: int = -1) -> None:
+    """out [M, (nq + 2 nkv) hd] bfloat16 = x @ w^T with the rotary encoding and
+    the cache write in the product's epilogue: ``w`` holds the rows in
+    :func:`rope_row_order`, ``table`` is :func:`rope_table` of the step; q and k
+    heads are rotated (pairs i, i + hd / 2), v is not; ``out`` is in the plain
+    order.  With ``rows`` (:func:`kv_rows`) and the layer's cache pages, k and v
+    also go to each token's cache row.  ``splits`` > 1 (up to 64 tokens): the
+    last block of a tile to finish adds the partial tiles in index order;
+    ``tickets`` is a zeroed int32 tensor that the kernel leaves zeroed."""
+    M, K = x.shape
+    N = w.shape[0]
+    if out.dtype != torch.bfloat16 or tuple(out.shape) != (M, N) or N != (nq + 2 * nkv) * hd:
+        raise KernelError(f"gemm_tc_rope: output {tuple(out.shape)} for {(M, (nq + 2 * nkv) * hd)}")
+    if not gemm_tc_rope_supported(x, w, hd):
+        raise KernelError("gemm_tc_rope: operands must be bfloat16 with dense, 16-byte aligned rows, K % 8 == 0 "
+                          "and head_dim % 32 == 0")
+    if tuple(table.shape) != (M, hd // 2, 2) or table.dtype != torch.float32 or not table.is_contiguous():
+        raise KernelError(f"gemm_tc_rope: the table must be float32 [{M}, {hd // 2}, 2]")
+    if rows is not None:
+        if kcache is None or vcache is None or kcache.dtype != torch.bfloat16 or not kcache.is_contiguous() \
+                or tuple(kcache.shape[1:]) != (nkv, PAGE, hd) or vcache.shape != kcache.shape:
+            raise KernelError(f"gemm_tc_rope: cache pages must be bfloat16 [pages, {nkv}, {PAGE}, {hd}]")
+    parts = None
+    if splits > 1:
+        need = int(_lib().af_gemm_tc_rope_tickets(c_int(M), c_longlong(N)))
+        if M > 64 or tickets is None or tickets.dtype != torch.int32 or tickets.numel() < need:
+            raise KernelError(f"gemm_tc_rope: split-K serves up to 64 tokens and needs {need} zeroed int32 tickets")
+        parts = torch.empty(splits, M, N, dtype=torch.float32, device=x.device)
+    if n_acc == 0:
+        blocks2 = ((N + 255) // 256) * ((M + 255) // 256)
+        n_acc = 2 if (M > 128 and splits == 1 and blocks2 >= 120) else 1
+    _check(_lib().af_gemm_tc_rope(
+        _ptr(out), c_longlong(out.stride(0)), _ptr(x), c_longlong(x.stride(0)), _ptr(w), c_longlong(w.stride(0)),
+        c_longlong(N), c_int(M), c_int(K), c_int(n_acc), c_int(splits),
+        _ptr(parts, "parts", torch.float32, allow_none=True), _ptr(tickets, "tickets", torch.int32, allow_none=True),
+        _ptr(table, "table", torch.float32), _ptr(rows, "rows", torch.int32, allow_none=True),
+        _ptr(kcache, allow_none=True), _ptr(vcache, allow_none=True), c_int(hd), c_int(nq), c_int(nkv),
+        c_int(GEMM_TC_PER_SM if per_sm < 0 else per_sm), _ptr(error_word(x.device), "err", torch.int32), _stream()))
+
+
+def gemm_tc_argmax(tokens, x, w, cap: float, keys) -> None:
+    """tokens[m] = argmax over the rows n of softcap(x[m] . w[n]) (finite values
+    only, the lowest row among equals, 0 when none is finite), without the
+    logits going to memory: the product's epilogue joins every block's best
+    into one 64-bit key per token.  ``keys``: int64 [>= M] on the device, zero
+    before the call and zero again after it."""
+    M, K = x.shape
+    if not gemm_tc_supported(x, w, None):
+        raise KernelError("gemm_tc_argmax: operands must be bfloat16 with dense, 16-byte aligned rows and K % 8 == 0")
+    if tokens.dtype != torch.int32 or tokens.numel() < M or keys.dtype != torch.int64 or keys.numel() < M:
+        raise KernelError("gemm_tc_argmax: int32 tokens and int64 keys, one per row")
+    lib = _lib()
+    _check(lib.af_gemm_tc_argmax(_ptr(keys), _ptr(x), c_longlong(x.stride(0)), _ptr(w), c_longlong(w.stride(0)),
+                                 c_longlong(w.shape[0]), c_int(M), c_int(K), c_float(cap), c_int(max(GEMM_TC_PER_SM, 0)),
+                                 _ptr(error_word(x.device), "err", torch.int32), _stream()))
+    _check(lib.af_argmax_finish(_ptr(tokens), _ptr(keys), c_int(M), _stream()))
+
+
 def interleave_gate_up(w_gate, w_up):
     """The gated product's weight layout: groups of 32 rows, each 16 gate rows
     followed by the up rows of the same 16 features.  Rows beyond the last

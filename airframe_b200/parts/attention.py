@@ -24,7 +24,13 @@ class Attention(Mixer):
     """Parameters: ``hidden_size``, ``num_heads``, ``num_kv_heads``, ``head_dim``,
     ``scale``, ``softcap`` (0 = off), ``window`` (None = all keys), ``position``
     (a PartSpec of category ``position``), ``q_weight``/``k_weight``/``v_weight``/
-    ``o_weight`` (tensor names)."""
+    ``o_weight`` (tensor names); optional ``rope_epilogue`` (default false): run the
+    q, k, v projection with the rotary encoding and the cache write in its epilogue
+    (``kernels.gemm_tc_rope``) where sizes and encoding allow.  Off by default
+    because it measures slower than the projection followed by the rotary kernel:
+    four epilogue warps a block cannot hide the latency of the table of cosines
+    that many blocks of the rotary kernel hide easily (Gemma-2 2B sizes: a
+    2,048-token prompt 9.6 ms against 8.3, a decode step at batch 8 1.93 ms against 1.75)."""
 
     @property
     def graph_safe(self):
@@ -48,6 +54,7 @@ class Attention(Mixer):
         self.names = [self.param(k) for k in ("q_weight", "k_weight", "v_weight", "o_weight")]
         self.w_qkv = None
         self.w_o = None
+        self.rope_epilogue = False
 
     def kv_need(self):
         return KVNeed(self.nkv, self.hd, self.window)
@@ -67,22 +74,55 @@ class Attention(Mixer):
         self.w_qkv = torch.cat([weights[q], weights[k], weights[v]], dim=0).to(dt).contiguous()
         self.w_o = weights[o].to(dt).contiguous()
         self.position.load(weights)
+        # bfloat16 with a head size and a K that the tensor-core product takes: the rows of every head in the
+        # order in which the product's epilogue rotates pairs and writes the cache (used only when the position
+        # encoding says, step by step, that it is such a rotation)
+        self.rope_epilogue = (bool(self.params.get("rope_epilogue")) and dt == torch.bfloat16 and self.hd % 32 == 0
+                              and self.hidden % 8 == 0 and self.w_qkv.is_cuda
+                              and self.position.rotates_half_pairs(self.hd))
+        if self.rope_epilogue:
+            order = kernels.rope_row_order(self.nq + 2 * self.nkv, self.hd, self.w_qkv.device)
+            self.w_qkv = self.w_qkv.index_select(0, order).contiguous()
+            self.tickets = torch.zeros(4 * ((self.w_qkv.shape[0] + 127) // 128), dtype=torch.int32,
+                                       device=self.w_qkv.device)
+
+    def _project_rotate_store(self, x, batch, view):
+        """q, k, v rows of the step with positions encoded and k, v stored: the
+        product with the rotation and the cache write in its epilogue."""
+        nq, nkv, hd = self.nq, self.nkv, self.hd
+        table = self.position.rotary_table(batch, hd)
+        M, N = x.shape[0], self.w_qkv.shape[0]
+        rows = kc = vc = None
+        if view.writes:
+            kv = view.kv
+            key = ("kv_rows", kv.page_table.data_ptr(), kv.ring_rows, nkv)
+            if key not in batch.aux:
+                batch.aux[key] = kernels.kv_rows(batch, kv, nkv)
+            rows, kc, vc = batch.aux[key], kv.k, kv.v
+        qkv = torch.empty(M, N, dtype=x.dtype, device=x.device)
+        splits = kernels.gemm_tc_splits(M, N, x.shape[1]) if M <= 64 else 1
+        kernels.gemm_tc_rope(qkv, x, self.w_qkv, table, nq, nkv, hd, rows, kc, vc, splits=splits,
+                             tickets=self.tickets)
+        return qkv
 
     def forward(self, x, batch, view):
         nq, nkv, hd = self.nq, self.nkv, self.hd
-        qkv = linear_split(x, self.w_qkv)
-        parts = None
-        if isinstance(qkv, PartialSums):
-            parts = qkv.parts
-            qkv = torch.empty(x.shape[0], (nq + 2 * nkv) * hd, dtype=x.dtype, device=x.device)
         kv = view.kv
-        # positions into q and k, then k and v into the cache: the store is this mixer's; an encoding
-        # that can do both in one kernel says so
-        if not view.writes:
-            self.position.encode(qkv, batch, nq, nkv, hd, parts=parts)
-        elif not self.position.encode_and_store(qkv, batch, nq, nkv, hd, kv, parts=parts):
-            self.position.encode(qkv, batch, nq, nkv, hd, parts=parts)
-            kernels.store_kv(qkv, batch, nq, nkv, hd, kv)
+        if self.rope_epilogue:
+            qkv = self._project_rotate_store(x, batch, view)
+        else:
+            qkv = linear_split(x, self.w_qkv)
+            parts = None
+            if isinstance(qkv, PartialSums):
+                parts = qkv.parts
+                qkv = torch.empty(x.shape[0], (nq + 2 * nkv) * hd, dtype=x.dtype, device=x.device)
+            # positions into q and k, then k and v into the cache: the store is this mixer's; an encoding
+            # that can do both in one kernel says so
+            if not view.writes:
+                self.position.encode(qkv, batch, nq, nkv, hd, parts=parts)
+            elif not self.position.encode_and_store(qkv, batch, nq, nkv, hd, kv, parts=parts):
+                self.position.encode(qkv, batch, nq, nkv, hd, parts=parts)
+                kernels.store_kv(qkv, batch, nq, nkv, hd, kv)
         slopes = self.position.score_slopes(nq)
         q = qkv[:, : nq * hd]
         k = qkv[:, nq * hd: (nq + nkv) * hd]

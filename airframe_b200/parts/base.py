@@ -148,6 +148,19 @@ class PositionEncoding(Part):
         query position) is added to head h's scores after scale and softcap."""
         return None
 
+    def rotates_half_pairs(self, hd: int) -> bool:
+        """True when :meth:`encode` is nothing but the rotation of the pairs
+        (i, i + hd / 2) of every q and k head by an angle per token and pair,
+        and :meth:`rotary_table` gives its cosines and sines: a mixer may then
+        rotate in the epilogue of its projection instead of calling :meth:`encode`."""
+        return False
+
+    def rotary_table(self, batch, hd: int):
+        """float32 [T, hd / 2, 2] of (cos, sin) for every token of the step and
+        pair of the head (see :meth:`rotates_half_pairs`).  Made once per pass
+        (kept in ``batch.aux``) for all layers that rotate alike."""
+        raise NotImplementedError
+
     def encode_and_store(self, qkv, batch, nq: int, nkv: int, hd: int, kv, parts=None) -> bool:
         """Optional fast path: :meth:`encode` and the mixer's cache store in one
         kernel.  Returns False when the encoding has none (the mixer then calls

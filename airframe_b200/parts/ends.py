@@ -58,6 +58,7 @@ class LmHead(Part):
         self.hidden = int(self.param("hidden_size"))
         self.softcap = float(self.params.get("softcap") or 0.0)
         self.w = None
+        self._keys = None      # the fused arg-max's key per row (zero between calls)
 
     def weight_decls(self):
         shape = (self.vocab, self.hidden)
@@ -77,3 +78,18 @@ class LmHead(Part):
     def forward(self, y):
         """y [R, H] compute dtype (after the final norm) -> float32 logits [R, V]."""
         return linear(y, self.w, out_dtype=torch.float32, cap=self.softcap)
+
+    def forward_argmax(self, y):
+        """The token of greedy decoding for every row: int32 [R], the arg-max of
+        the (capped) logits over finite values, the lowest id among equals.
+        On the tensor-core path the logits never go to memory (the product's
+        epilogue keeps the best per row); else logits and the sampler's arg-max."""
+        R = y.shape[0]
+        tokens = torch.empty(R, dtype=torch.int32, device=y.device)
+        if kernels.gemm_tc_supported(y, self.w, None):
+            if self._keys is None or self._keys.numel() < R:
+                self._keys = torch.zeros(max(R, 256), dtype=torch.int64, device=y.device)
+            kernels.gemm_tc_argmax(tokens, y, self.w, self.softcap, self._keys)
+        else:
+            kernels.sample(self.forward(y), tokens, 0.0, 1.0, 1.0)
+        return tokens

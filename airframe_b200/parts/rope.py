@@ -41,6 +41,15 @@ class Rope(PositionEncoding):
     def load(self, weights):
         self.inv_freq = self._inv_freq_host.to(self.ctx.device)
 
+    def rotates_half_pairs(self, hd):
+        return self.pairing == "half" and self.rotary_dim == hd
+
+    def rotary_table(self, batch, hd):
+        key = ("rope_table", self.theta, self.rotary_dim)
+        if key not in batch.aux:
+            batch.aux[key] = kernels.rope_table(batch.positions, self.inv_freq)
+        return batch.aux[key]
+
     def encode(self, qkv, batch, nq, nkv, hd, parts=None):
         if self.rotary_dim > hd:
             raise ConfigError(f"rope: rotary_dim {self.rotary_dim} exceeds head_dim {hd}")

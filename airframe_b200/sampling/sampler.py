@@ -107,6 +107,16 @@ class Sampler:
                        uniform=dev.view(torch.float32)[:, 0] if not params.greedy else None,
                        recent=dev[:, 2:] if use_penalty else None,
                        n_recent=dev[:, 1] if use_penalty else None)
+        return self.adopt(out, states)
+
+    def adopt(self, out, states) -> PendingTokens:
+        """Tokens that are on the device already (int32 [R], one per state; the
+        step function's own greedy choice): queues their copy to the host like
+        :meth:`sample_async` does for the tokens it draws."""
+        R = len(states)
+        if out.dtype != torch.int32 or out.numel() < R:
+            raise ValueError("one int32 token per state")
+        out = out[:R]
         # the tokens come back through pinned memory kept for the purpose
         k = self._turn = self._turn ^ 1
         if self._done[k] is not None:

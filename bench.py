@@ -244,16 +244,17 @@ def run_ours(args) -> dict:
         slots = [eng.take_slot() for _ in range(batch)]
         try:
             ps = prompts(batch, 100 + batch)
-            logits = eng.step([StepEntry(s, p, [PROMPT_LEN - 1]) for s, p in zip(slots, ps)])
+            first = eng.step([StepEntry(s, p, [PROMPT_LEN - 1]) for s, p in zip(slots, ps)], greedy=True)
             state = {}
 
-            # the product's own way of stepping (GenerationLoop): the step takes its tokens from the device,
-            # where the sampler of the step before left them, and is queued before the host reads those
-            state["pending"] = sampler.sample_async(logits, states, greedy)
+            # the product's own way of stepping (GenerationLoop, greedy): a step gives its arg-max tokens (the
+            # head's epilogue finds them; no logits are written), takes its input tokens from the device, where
+            # the step before left them, and is queued before the host has read those
+            state["pending"] = sampler.adopt(first, states)
 
             def one():
-                lg = eng.decode_rows(slots, state["pending"].device)
-                nxt = sampler.sample_async(lg, states, greedy)
+                toks = eng.decode_rows(slots, state["pending"].device, greedy=True)
+                nxt = sampler.adopt(toks, states)
                 state["pending"].result()                     # the tokens of the step before, on the host
                 state["pending"] = nxt
 
@@ -355,7 +356,7 @@ def run_ours(args) -> dict:
                    "hidden": cfg_dict["hidden_size"], "heads": cfg_dict["num_attention_heads"],
                    "kv_heads": cfg_dict["num_key_value_heads"], "head_dim": cfg_dict["head_dim"],
                    "intermediate": cfg_dict["intermediate_size"], "vocab": cfg_dict["vocab_size"],
-                   "sliding_window": cfg_dict["sliding_window"], "sampling": "greedy on device",
+                   "sliding_window": cfg_dict["sliding_window"], "sampling": "greedy, in the head's epilogue",
                    "l2": f"inputs larger than L2 (weights {model_bytes(cfg_dict, n_layers) / 1e9:.1f} GB per step)"},
         "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
         "gpu_launches": launches, "clocks": clock_info, "impl": "ours",

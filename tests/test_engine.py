@@ -188,3 +188,27 @@ def test_step_errors(case):
     finally:
         rt.engine.free_slot(s)
         rt.engine.free_slot(t)
+
+
+@pytest.mark.parametrize("name", ["D", "F", "H"])
+def test_projection_with_the_rotary_epilogue_switched_on(name, tmp_path):
+    """The attention part's option ``rope_epilogue`` (rotation and cache write in the projection's epilogue):
+    whole prompts, decoding (split-K: the last block adds the parts) and batches give the plain logits."""
+    from airframe_b200.engine import GpuRuntime
+
+    def on(spec):
+        for layer in spec.layers:
+            layer.mixer.params["rope_epilogue"] = True
+
+    folder = make_folder(CONFIGS[name], seed=13, store_dtype="bfloat16", root=tmp_path / "m")
+    cfg, w = plain.read_model_folder(folder)
+    rt = GpuRuntime.load(folder, dtype="bfloat16", max_tokens=64 * 24, spec_edit=on)
+    assert all(b.mixer.rope_epilogue for b in rt.model.blocks)
+    reqs = [replay.random_ids(cfg["vocab_size"], n, 400 + n) for n in (150, 9, 70)]
+    ref = [plain.logits(cfg, w, r) for r in reqs]
+    for r, want in zip(reqs, ref):
+        assert rel_err(replay.run_whole(rt, r), want) < VS_PLAIN["bfloat16"]
+        assert rel_err(replay.run_tail(rt, r, 8), want) < VS_PLAIN["bfloat16"]
+    got, _ = replay.run_batches(rt, reqs, 3, [100, 9, 20])
+    for i, want in enumerate(ref):
+        assert rel_err(got[i], want) < VS_PLAIN["bfloat16"]

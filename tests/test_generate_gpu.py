@@ -132,3 +132,34 @@ def test_runtime_refuses_the_cpu(case):
     from airframe_b200.engine import GpuRuntime
     with pytest.raises(RuntimeError, match="CUDA device only"):
         GpuRuntime.load(case[1], device="cpu")
+
+
+@pytest.mark.parametrize("name", ["D", "C"])
+def test_greedy_tokens_from_the_head_equal_those_from_the_logits(name, tmp_path):
+    """bfloat16, sizes whose head runs on the tensor cores (D) and sizes whose head does not (C): generation with
+    the arg-max found in the head's epilogue gives the tokens that sampling the written logits gives, and the
+    step function's own greedy answer equals the arg-max of its logits."""
+    from airframe_b200.engine import GpuRuntime, StepEntry
+    from airframe_b200.sampling import SamplingParams
+    folder = make_folder(CONFIGS[name], seed=33, store_dtype="bfloat16", root=tmp_path / "m")
+    cfg, _ = plain.read_model_folder(folder)
+    prompts = [replay.random_ids(cfg["vocab_size"], n, 50 + n) for n in (7, 70, 33)]
+    rt = GpuRuntime.load(folder, dtype="bfloat16", max_tokens=64 * 8)
+    params = SamplingParams(max_tokens=10, temperature=0.0, repetition_penalty=1.0, ignore_eos=True)
+    fused = rt.generate(prompts, params)
+    rt.engine.fused_greedy = False                      # the loop then samples the logits it is given
+    try:
+        assert rt.generate(prompts, params) == fused
+    finally:
+        rt.engine.fused_greedy = True
+    slots = [rt.engine.take_slot() for _ in prompts]
+    try:
+        toks = rt.engine.step([StepEntry(s, p, [0, len(p) - 1]) for s, p in zip(slots, prompts)], greedy=True)
+        for s in slots:
+            rt.engine.free_slot(s)
+        slots = [rt.engine.take_slot() for _ in prompts]
+        logits = rt.engine.step([StepEntry(s, p, [0, len(p) - 1]) for s, p in zip(slots, prompts)])
+        assert toks.dtype == torch.int32 and toks.tolist() == logits.argmax(-1).tolist()
+    finally:
+        for s in slots:
+            rt.engine.free_slot(s)

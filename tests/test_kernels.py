@@ -238,6 +238,84 @@ def test_rope_and_cache_write(K, dtype, pairing, rot):
     assert float(kc[1].abs().sum()) == 0 and float(kc[2, :, 6:].abs().sum()) == 0          # nothing else touched
 
 
+@pytest.mark.parametrize("hd,nq,nkv,Kd,lens,ring", [
+    (64, 3, 1, 72, [70, 3], 0),              # one tile and a half of weight rows, a single small token tile
+    (256, 2, 1, 264, [5], 0),                # head size 256: a head is two weight tiles
+    (128, 4, 2, 2304, [8, 1, 7], 0),         # few tokens and a long K: split-K, the last block adds the parts
+    (96, 2, 2, 520, [40, 9], 0),             # head size 96: three groups of pairs a head
+    (256, 8, 4, 136, [300], 128),            # many tokens (two accumulators), a ring that the prompt laps
+    (32, 5, 5, 64, [130, 2, 64], 64)])
+def test_projection_with_rotary_and_cache_write_in_its_epilogue(K, hd, nq, nkv, Kd, lens, ring):
+    theta = 10000.0
+    T, B = sum(lens), len(lens)
+    N = (nq + 2 * nkv) * hd
+    g = torch.Generator().manual_seed(hd + T)
+    x = torch.randn(T, Kd, generator=g).to(torch.bfloat16)
+    w = (torch.randn(N, Kd, generator=g) * 0.08).to(torch.bfloat16)
+    pos = torch.tensor([p for n in lens for p in range(n)], dtype=torch.int32)
+    seq = torch.tensor([b for b, n in enumerate(lens) for _ in range(n)], dtype=torch.int32)
+    inv = (torch.tensor(theta, dtype=torch.float64) ** (-2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)).float()
+    pages_per = max((min(n, ring) if ring else n) + PAGE - 1 for n in lens) // PAGE
+    n_pages = B * pages_per + 1
+    perm = torch.randperm(n_pages - 1, generator=g)[: B * pages_per].reshape(B, pages_per) + 1   # page 0 stays unused
+    kc = torch.zeros(n_pages, nkv, PAGE, hd, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+
+    class Batch:
+        tokens = torch.zeros(T, dtype=torch.int32, device=DEV)
+        positions = pos.to(DEV)
+        seq_of_token = seq.to(DEV)
+        slots = torch.arange(B, dtype=torch.int32, device=DEV)
+        len_after = torch.tensor(lens, dtype=torch.int32, device=DEV)
+
+    class View:
+        k, v = kc, vc
+        page_table = perm.to(torch.int32).to(DEV)
+        ring_rows = ring
+
+    table = K.rope_table(Batch.positions, inv.to(DEV))
+    ang = pos.double()[:, None] * inv.double()[None, :]
+    assert float((table[..., 0].cpu().double() - torch.cos(ang)).abs().max()) < 2e-3      # 32-bit angles of positions to 300
+    rows = K.kv_rows(Batch, View, nkv)
+    order = K.rope_row_order(nq + 2 * nkv, hd)
+    assert sorted(order.tolist()) == list(range(N))
+    wp = w[order].contiguous().to(DEV)
+    # the reference: the plain product, the plain rotation of q and k heads
+    y = (x.double() @ w.double().T).reshape(T, nq + 2 * nkv, hd)
+    want = torch.cat([plain.rope(y[:, : nq + nkv], pos.tolist(), theta), y[:, nq + nkv:]], 1)
+    splits = K.gemm_tc_splits(T, N, Kd) if T <= 64 else 1
+    tickets = torch.zeros(4 * ((N + 127) // 128), dtype=torch.int32, device=DEV)
+    for attempt in range(2):                          # twice: the tickets must come back to zero
+        out = torch.full((T, N), float("nan"), dtype=torch.bfloat16, device=DEV)
+        kc.zero_(), vc.zero_()
+        K.gemm_tc_rope(out, x.to(DEV), wp, table, nq, nkv, hd, rows, kc, vc, splits=splits, tickets=tickets)
+        K.check_device_errors(DEV)
+        assert int(tickets.abs().sum()) == 0
+        close(out.reshape(T, -1, hd), want, torch.bfloat16)
+        # the cache holds, for every sequence, the rows that a ring keeps (all rows without one)
+        first = 0
+        for b, n in enumerate(lens):
+            for p_ in range(max(0, n - ring) if ring else 0, n):
+                r = p_ % ring if ring else p_
+                page = int(perm[b, r // PAGE])
+                got_k, got_v = kc[page, :, r % PAGE].cpu(), vc[page, :, r % PAGE].cpu()
+                assert torch.equal(got_k, out[first + p_].reshape(-1, hd)[nq: nq + nkv].cpu()), (b, p_)
+                assert torch.equal(got_v, out[first + p_].reshape(-1, hd)[nq + nkv:].cpu()), (b, p_)
+            first += n
+        assert float(kc[0].abs().sum()) == 0                       # a page of no sequence stays untouched
+    if splits > 1:
+        # the sum of the partial tiles does not depend on which block came last: the same bits every time
+        again = torch.empty_like(out)
+        K.gemm_tc_rope(again, x.to(DEV), wp, table, nq, nkv, hd, rows, kc, vc, splits=splits, tickets=tickets)
+        assert torch.equal(again, out)
+    # without a cache nothing is stored
+    kc.zero_()
+    K.gemm_tc_rope(out, x.to(DEV), wp, table, nq, nkv, hd, splits=splits, tickets=tickets)
+    assert float(kc.abs().sum()) == 0
+    with pytest.raises(K.KernelError, match="multiple of 32"):
+        K.rope_row_order(3, 48)
+
+
 def test_ring_keeps_the_last_rows_of_a_long_prompt(K):
     nq, nkv, hd = 1, 1, 16
     T, ring = 150, 128

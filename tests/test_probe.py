@@ -30,10 +30,15 @@ def test_row_facts_are_what_they_say():
     row2 = row.copy()
     row2[3] = np.nextafter(row2[3], np.float32(4.0))
     assert row_facts(row2)["checksum"] == want + 1
-    recs = [{"run": -1, "layer": -1, "rows": [{"rms": 9.0}]}, {"run": 0, "layer": 0, "rows": [{"rms": 1.0}]},
-            {"run": 1, "layer": 1, "rows": [{"rms": 2.2}]}, {"run": 2, "layer": 2, "rows": [{"rms": 9.0}]}]
-    assert first_difference(recs, [[1.0], [2.0], [3.0]], 0.05) == (1, 1, 0)
-    assert first_difference(recs[:2], [[1.0], [2.0], [3.0]], 0.05) is None
+    ref = [[[1.0, 1.0]], [[2.0, -2.0]], [[3.0, 3.0]]]                      # [run][row] -> the other implementation's row
+    recs = [{"run": -1, "layer": -1, "rows": [{"rms": 9.0, "first": [9.0]}]},
+            {"run": 0, "layer": 0, "rows": [{"rms": 1.0, "first": [1.0, 1.0]}]},
+            {"run": 1, "layer": 1, "rows": [{"rms": 2.0, "first": [2.0, 2.0]}]},    # the same size, another direction
+            {"run": 2, "layer": 2, "rows": [{"rms": 9.0, "first": [3.0, 3.0]}]}]
+    assert first_difference(recs, ref, 0.05) == (1, 1, 0)
+    assert first_difference(recs[:2], ref, 0.05) is None
+    recs[2]["rows"][0]["first"] = [2.0, -2.0]
+    assert first_difference(recs, ref, 0.05) == (2, 2, 0)                  # now only the size of run 2 is off
 
 
 def _plain_facts(cfg, w, ids, rows):
@@ -56,6 +61,7 @@ def test_layers_agree_with_the_plain_implementation_and_a_fault_is_named(dtype, 
     rows = [0, 41, 89]
     ref = _plain_facts(cfg, w, ids, rows)
     ref_rms = [[float(r.pow(2).mean().sqrt()) for r in layer] for layer in ref]
+    ref_rows = [[r.tolist() for r in layer] for layer in ref]
 
     def probed(path):
         rt = GpuRuntime.load(path, dtype=dtype, max_tokens=256)
@@ -76,7 +82,7 @@ def test_layers_agree_with_the_plain_implementation_and_a_fault_is_named(dtype, 
             assert facts["rms"] == pytest.approx(ref_rms[rec["run"]][r], rel=tol)
             got = torch.tensor(facts["first"], dtype=torch.float64)
             assert float((got - want[:20]).abs().max()) <= tol * float(want.abs().max())
-    assert first_difference(recs, ref_rms, tol) is None
+    assert first_difference(recs, ref_rows, tol) is None
     # a fault in layer 2 (half of its down projection's rows three times too large; all of them would be
     # undone by the norm that follows): the first run that differs is run 2
     bad = tmp_path / "bad"
@@ -88,7 +94,7 @@ def test_layers_agree_with_the_plain_implementation_and_a_fault_is_named(dtype, 
     tensors[key] = wrong.to(tensors[key].dtype)
     write_safetensors(bad / "model.safetensors",
                       [(n, tuple(t.shape), t.dtype, (lambda t=t: t)) for n, t in tensors.items()])
-    assert first_difference(probed(bad), ref_rms, tol) [:2] == (2, 2)
+    assert first_difference(probed(bad), ref_rows, tol)[:2] == (2, 2)
 
 
 @pytest.mark.gpu

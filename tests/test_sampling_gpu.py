@@ -136,3 +136,39 @@ def test_the_sampler_reports_a_kernel_that_gave_up_waiting(K):
     with pytest.raises(K.KernelError, match="gave up waiting"):
         sampler.sample(logits, states, params)
     assert sampler.sample(logits, states, params) == [3, 3]          # the word was cleared
+
+
+@pytest.mark.parametrize("R,V,H,cap", [(1, 1000, 64, 30.0), (8, 256000, 264, 30.0), (5, 777 * 8, 520, 0.0), (40, 5000, 128, 2.0),
+                                       (130, 3000, 64, 0.0), (300, 1300, 72, 15.0)])
+def test_head_with_the_arg_max_in_its_epilogue(R, V, H, cap):
+    """The greedy token of every row without logits in memory: the same token as the arg-max of the logits
+    the product writes (finite values, lowest id among equals), also where the cap makes many values equal."""
+    from airframe_b200 import kernels as K
+    g = torch.Generator().manual_seed(R * V + H)
+    y = torch.randn(R, H, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(V, H, generator=g) * (3.0 if cap == 2.0 else 0.3)).to(torch.bfloat16)
+    w[V // 2] = w[7]                                      # two equal rows: the lower id wins
+    w = w.to(DEV)
+    logits = torch.empty(R, V, dtype=torch.float32, device=DEV)
+    K.gemm_tc(logits, y, w, cap=cap)
+    want = []
+    for r in range(R):
+        row = logits[r]
+        best = row[torch.isfinite(row)].max()
+        want.append(int((row == best).nonzero()[0]))
+    keys = torch.zeros(max(R, 4), dtype=torch.int64, device=DEV)
+    for attempt in range(2):                              # twice: the keys come back to zero
+        tokens = torch.full((R,), -5, dtype=torch.int32, device=DEV)
+        K.gemm_tc_argmax(tokens, y, w, cap, keys)
+        K.check_device_errors(DEV)
+        assert tokens.tolist() == want
+        assert int(keys.abs().sum()) == 0
+    if cap == 2.0:
+        sat = (logits == logits.max()).sum(-1)
+        assert int(sat.max()) > 1                         # the cap did make equal values somewhere
+    # and against the plain implementation's arg-max over the plain logits, where its margin is clear
+    ref = plain.softcap(y.double().cpu() @ w.double().cpu().T, cap if cap > 0 else None)
+    top2 = ref.topk(2, -1).values
+    clear = (top2[:, 0] - top2[:, 1]) > 1e-3 * ref.abs().max()
+    got = torch.tensor(want)
+    assert bool((got[clear] == ref.argmax(-1)[clear]).all())
