@@ -17,6 +17,11 @@ enum AfAct { AF_ACT_GELU_TANH = 0, AF_ACT_SILU = 1 };
 // rotary pairings
 enum AfPairing { AF_PAIR_HALF = 0, AF_PAIR_ADJACENT = 1 };
 
+// The fused arg-max keeps one 64-bit key per token; keys lie this many words apart (a cache line each:
+// every block of the head joins its best into every token's key, and keys in one line would queue up
+// behind one another in the L2).
+#define AF_KEY_STRIDE 16
+
 // Tokens per cache page.  A sequence holds whole pages.
 #define AF_PAGE 64
 

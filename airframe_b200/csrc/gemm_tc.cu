@@ -93,7 +93,7 @@ struct TcArgs {
   float* parts;              // split-K: [splits][M][N] partial sums
   int* tickets;              // split-K: a counter per tile, zero between launches
   // ARGMAX only
-  unsigned long long* keys;  // [M] best (value, row) per token, zero before the launch
+  unsigned long long* keys;  // [M * AF_KEY_STRIDE] best (value, row) per token, zero before the launch
 };
 
 // Float bits whose unsigned order is the floats' order.
@@ -364,7 +364,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
                 key = other > key ? other : key;
               }
-              if (lane == 0 && key != 0ull && m0 + c0 + j < a.M) atomicMax(a.keys + m0 + c0 + j, key);
+              if (lane == 0 && key != 0ull && m0 + c0 + j < a.M) atomicMax(a.keys + (size_t)(m0 + c0 + j) * AF_KEY_STRIDE, key);
             }
             continue;
           }
@@ -570,7 +570,7 @@ AF_EXPORT int af_gemm_tc_rope(void* out, long long ldo, const void* x, long long
   return launch_bn<1, -2, __nv_bfloat16>(bn, mw, mx, a, n_w_rows, splits, per_sm, stream);
 }
 
-// The head of greedy decoding: keys[m] = max over the rows n of (softcap(x[m] . w[n]), n) as a 64-bit key (see
+// The head of greedy decoding: keys[m * AF_KEY_STRIDE] = max over the rows n of (softcap(x[m] . w[n]), n) as a 64-bit key (see
 // the ARGMAX epilogue); keys must be zero before the call; af_argmax_finish turns them into token ids and
 // zeroes them again.
 AF_EXPORT int af_gemm_tc_argmax(unsigned long long* keys, const void* x, long long ldx, const void* w, long long ldw,

@@ -346,16 +346,16 @@ AF_EXPORT int af_sample(float* logits, int ld, int rows, int vocab, const int* r
 
 // ---------------------------------------------------------------- arg-max keys of the fused head
 
-// tokens[r] = the row held in keys[r] (see af_gemm_tc_argmax), 0 when no finite value took part (as the
+// tokens[r] = the row held in keys[r * AF_KEY_STRIDE] (see af_gemm_tc_argmax), 0 when no finite value took part (as the
 // arg-max over finite logits of an all-non-finite row); the keys are zeroed for the next use.
 __global__ void argmax_finish_kernel(int* __restrict__ tokens, unsigned long long* __restrict__ keys, int n) {
   pdl_launch_dependents();
   pdl_wait();
   const int r = blockIdx.x * blockDim.x + threadIdx.x;
   if (r >= n) return;
-  const unsigned long long k = keys[r];
+  const unsigned long long k = keys[(size_t)r * AF_KEY_STRIDE];
   tokens[r] = k ? (int)(0xffffffffu - (uint32_t)k) : 0;
-  keys[r] = 0ull;
+  keys[(size_t)r * AF_KEY_STRIDE] = 0ull;
 }
 
 AF_EXPORT int af_argmax_finish(int* tokens, unsigned long long* keys, int n, cudaStream_t stream) {
@@ -364,3 +364,6 @@ AF_EXPORT int af_argmax_finish(int* tokens, unsigned long long* keys, int n, cud
   af_launch(argmax_finish_kernel, dim3((n + 127) / 128), dim3(128), 0, stream, tokens, keys, n);
   AF_CHECK_LAUNCH("af_argmax_finish");
 }
+
+// Words between the keys of two tokens.
+AF_EXPORT int af_argmax_key_stride() { return AF_KEY_STRIDE; }

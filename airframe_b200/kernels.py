@@ -352,7 +352,9 @@ def gemm_tc(out, x, w, cap: float = 0.0, splits: int = 1, gated: bool = False, a
     sums.  gated: w holds, per group of 32 rows, 16 gate rows then the 16 up
     rows of the same features (see ``interleave_gate_up``); out[m, f] =
     act(x . gate_f) * (x . up_f), N = rows / 2.  n_acc: weight tiles per block
-    (0: chosen from the sizes).  ``checked``: the caller has asked
+    (1 or 2), or 4: the kernel that runs a tile on a pair of SMs
+    (``tcgen05.mma.cta_group::2``, two accumulators in turn: for prompts);
+    0: chosen from the sizes.  ``checked``: the caller has asked
     :func:`gemm_tc_supported` already."""
     M, K = x.shape
     rows = w.shape[0]
@@ -368,10 +370,26 @@ def gemm_tc(out, x, w, cap: float = 0.0, splits: int = 1, gated: bool = False, a
             raise KernelError(f"gemm_tc: output shape {tuple(out.shape)}, expected {(M, N)}")
         ldo, part = out.stride(0), 0
     if n_acc == 0:
-        # two weight tiles per block halve the bytes per flop; worth it once tokens fill the
-        # widest tile and enough blocks remain to fill the GPU
+        # Many tokens.  Two weight tiles per block halve the bytes a block stages per flop; worth it once the
+        # tiles of 256 x 256 fill the GPU.  With fewer tiles and a long K a tile runs on a pair of SMs (the same
+        # bytes per flop, 128 rows a block); with a short K the pair's set-up costs what it saves.  Measured at
+        # 2,048 tokens on a B200: 18432 x 2304 gated 122 us / 124 us / 132 us (two tiles / pair / one tile),
+        # 2304 x 9216 90 / 59 / 63, 2304 x 2048 25 / 17 / 15, 4096 x 2304 31 / 31 / 31.
         blocks2 = ((rows + 255) // 256) * ((M + 255) // 256)
-        n_acc = 2 if (M > 128 and splits == 1 and blocks2 >= 120) else 1
+        n_acc = 1
+        if M > 128 and splits == 1:
+            if blocks2 >= 120:
+                n_acc = 2
+            elif blocks2 >= 60 and K >= 4096:
+                n_acc = 4
+    if n_acc == 4:
+        if splits > 1:
+            raise KernelError("gemm_tc: the kernel on pairs of SMs does not split K")
+        _check(_lib().af_gemm_tc_pair(_ptr(out), c_int(dtype_code(out.dtype)), c_longlong(ldo), _ptr(x),
+                                      c_longlong(x.stride(0)), _ptr(w), c_longlong(w.stride(0)), c_longlong(rows),
+                                      c_int(M), c_int(K), c_int(1 if gated else 0), c_int(ACTIVATIONS[activation]),
+                                      c_float(cap), _ptr(error_word(x.device), "err", torch.int32), _stream()))
+        return
     _check(_lib().af_gemm_tc(_ptr(out), c_int(dtype_code(out.dtype)), c_longlong(ldo), c_longlong(part), _ptr(x),
                              c_longlong(x.stride(0)), _ptr(w), c_longlong(w.stride(0)), c_longlong(rows),
                              c_int(M), c_int(K), c_int(1 if gated else 0), c_int(ACTIVATIONS[activation]),
@@ -460,6 +478,11 @@ def gemm_tc_rope(out, x, w, table, nq: int, nkv: int, hd: int, rows=None, kcache
         c_int(GEMM_TC_PER_SM if per_sm < 0 else per_sm), _ptr(error_word(x.device), "err", torch.int32), _stream()))
 
 
+def argmax_key_stride() -> int:
+    """64-bit words between the keys of two rows of :func:`gemm_tc_argmax`."""
+    return int(_lib().af_argmax_key_stride())
+
+
 def gemm_tc_argmax(tokens, x, w, cap: float, keys) -> None:
     """tokens[m] = argmax over the rows n of softcap(x[m] . w[n]) (finite values
     only, the lowest row among equals, 0 when none is finite), without the
@@ -469,8 +492,9 @@ def gemm_tc_argmax(tokens, x, w, cap: float, keys) -> None:
     M, K = x.shape
     if not gemm_tc_supported(x, w, None):
         raise KernelError("gemm_tc_argmax: operands must be bfloat16 with dense, 16-byte aligned rows and K % 8 == 0")
-    if tokens.dtype != torch.int32 or tokens.numel() < M or keys.dtype != torch.int64 or keys.numel() < M:
-        raise KernelError("gemm_tc_argmax: int32 tokens and int64 keys, one per row")
+    if tokens.dtype != torch.int32 or tokens.numel() < M or keys.dtype != torch.int64 \
+            or keys.numel() < M * argmax_key_stride():
+        raise KernelError("gemm_tc_argmax: int32 tokens, one per row, and int64 keys, argmax_key_stride() per row")
     lib = _lib()
     _check(lib.af_gemm_tc_argmax(_ptr(keys), _ptr(x), c_longlong(x.stride(0)), _ptr(w), c_longlong(w.stride(0)),
                                  c_longlong(w.shape[0]), c_int(M), c_int(K), c_float(cap), c_int(max(GEMM_TC_PER_SM, 0)),

@@ -87,8 +87,9 @@ class LmHead(Part):
         R = y.shape[0]
         tokens = torch.empty(R, dtype=torch.int32, device=y.device)
         if kernels.gemm_tc_supported(y, self.w, None):
-            if self._keys is None or self._keys.numel() < R:
-                self._keys = torch.zeros(max(R, 256), dtype=torch.int64, device=y.device)
+            stride = kernels.argmax_key_stride()
+            if self._keys is None or self._keys.numel() < R * stride:
+                self._keys = torch.zeros(max(R, 256) * stride, dtype=torch.int64, device=y.device)
             kernels.gemm_tc_argmax(tokens, y, self.w, self.softcap, self._keys)
         else:
             kernels.sample(self.forward(y), tokens, 0.0, 1.0, 1.0)

@@ -487,12 +487,15 @@ def test_gemm_tensor_cores(K, M, N, Kd, out_dtype):
     x = torch.randn(M, Kd).to(torch.bfloat16)
     w = (torch.randn(N, Kd) * 0.05).to(torch.bfloat16)
     ref = x.double() @ w.double().T
-    for n_acc in (0, 1, 2):
+    for n_acc in (0, 1, 2, 4):                        # 4: the kernel on pairs of SMs
         out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
         K.gemm_tc(out, x.to(DEV), w.to(DEV), n_acc=n_acc)
         K.check_device_errors(DEV)
         close(out, ref, out_dtype if out_dtype == torch.bfloat16 else torch.float32)
     if out_dtype == torch.float32:
+        out.fill_(float("nan"))
+        K.gemm_tc(out, x.to(DEV), w.to(DEV), cap=1.5, n_acc=4)
+        close(out, plain.softcap(ref, 1.5), torch.float32)
         K.gemm_tc(out, x.to(DEV), w.to(DEV), cap=1.5)
         close(out, plain.softcap(ref, 1.5), torch.float32)
         # against the plain kernel on the same inputs: only the order of the 32-bit sums differs
@@ -509,7 +512,7 @@ def test_gemm_tensor_cores_many_token_tiles(K, M, N, Kd, out_dtype):
     x = torch.randn(M, Kd).to(torch.bfloat16)
     w = (torch.randn(N, Kd) * 0.05).to(torch.bfloat16)
     ref = x.double() @ w.double().T
-    for n_acc in (0, 1, 2):
+    for n_acc in (0, 1, 2, 4):
         out = torch.full((M, N), float("nan"), dtype=out_dtype, device=DEV)
         K.gemm_tc(out, x.to(DEV), w.to(DEV), n_acc=n_acc)
         K.check_device_errors(DEV)
@@ -537,7 +540,7 @@ def test_gemm_tensor_cores_gated(K, M, I, Kd, act):
     ref = (plain.gelu_tanh(g) if act == "gelu_tanh" else g * torch.sigmoid(g)) * u
     wi = K.interleave_gate_up(w[:I].to(DEV), w[I:].to(DEV))
     assert wi.shape[0] == (I + 15) // 16 * 32 and torch.equal(wi[16:32].cpu(), w[I: I + 16])
-    for n_acc in (1, 2):
+    for n_acc in (1, 2, 4):
         out = torch.full((M, wi.shape[0] // 2), float("nan"), dtype=torch.bfloat16, device=DEV)
         K.gemm_tc(out, x.to(DEV), wi, gated=True, activation=act, n_acc=n_acc)
         K.check_device_errors(DEV)

@@ -156,7 +156,7 @@ def test_head_with_the_arg_max_in_its_epilogue(R, V, H, cap):
         row = logits[r]
         best = row[torch.isfinite(row)].max()
         want.append(int((row == best).nonzero()[0]))
-    keys = torch.zeros(max(R, 4), dtype=torch.int64, device=DEV)
+    keys = torch.zeros(max(R, 4) * K.argmax_key_stride(), dtype=torch.int64, device=DEV)
     for attempt in range(2):                              # twice: the keys come back to zero
         tokens = torch.full((R,), -5, dtype=torch.int32, device=DEV)
         K.gemm_tc_argmax(tokens, y, w, cap, keys)
