@@ -23,6 +23,19 @@ from pathlib import Path
 
 SOURCE_DIR = Path(__file__).resolve().parent
 LIB_NAME = "libairframe_b200.so"
+CHECKED_LIB_NAME = "libairframe_b200_checked.so"
+_checked = False
+
+
+def use_checked_build() -> None:
+    """Load the checked build instead (compiled with ``-DAF_BOUNDS_CHECK``: the
+    indices that kernels take from data are checked, a bad one is recorded and
+    its access skipped; ``kernels.bounds_failures()`` reads the record).  Must
+    be called before the library is first used; meant for test runs."""
+    global _checked
+    if _lib is not None and not _checked:
+        raise KernelLibraryError("the kernel library is loaded already; choose the checked build before its first use")
+    _checked = True
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",
@@ -43,8 +56,9 @@ def sources() -> list[Path]:
     return sorted(SOURCE_DIR.glob("*.cu"))
 
 
-def _digest() -> str:
+def _digest(extra: str = "") -> str:
     h = hashlib.sha256()
+    h.update(extra.encode())
     for p in sorted(list(SOURCE_DIR.glob("*.cu")) + list(SOURCE_DIR.glob("*.cuh")) + list(SOURCE_DIR.glob("*.h"))):
         h.update(p.name.encode())
         h.update(p.read_bytes())
@@ -86,19 +100,22 @@ def _run(cmd: list[str], what: str) -> None:
         raise KernelLibraryError(f"{what} failed ({proc.returncode}):\n{' '.join(cmd)}\n{proc.stdout}")
 
 
-def build(force: bool = False, verbose: bool = True) -> Path:
+def build(force: bool = False, verbose: bool = True, checked: bool = False) -> Path:
     """Compile every ``.cu`` here for sm_100a and link the shared object.
-    Returns its path.  Does nothing when the object is up to date."""
+    Returns its path.  Does nothing when the object is up to date.
+    ``checked``: the variant with ``-DAF_BOUNDS_CHECK`` (a library of its own)."""
     out_dir = build_dir()
-    lib = out_dir / LIB_NAME
-    stamp = out_dir / (LIB_NAME + ".sha256")
-    digest = _digest()
+    name = CHECKED_LIB_NAME if checked else LIB_NAME
+    flags = NVCC_FLAGS + (["-DAF_BOUNDS_CHECK"] if checked else [])
+    lib = out_dir / name
+    stamp = out_dir / (name + ".sha256")
+    digest = _digest(" ".join(flags))
     if not force and lib.exists() and stamp.exists() and stamp.read_text().strip() == digest:
         return lib
     nvcc = _nvcc()
     srcs = sources()
     if verbose:
-        _say(f"building {LIB_NAME} from {len(srcs)} sources for sm_100a in {out_dir}")
+        _say(f"building {name} from {len(srcs)} sources for sm_100a in {out_dir}")
     t0 = time.time()
     done = threading.Event()
 
@@ -110,17 +127,17 @@ def build(force: bool = False, verbose: bool = True) -> Path:
     if verbose:
         th.start()
     try:
-        objs = [out_dir / (s.stem + ".o") for s in srcs]
+        objs = [out_dir / (s.stem + (".checked.o" if checked else ".o")) for s in srcs]
 
         def one(pair):
             s, o = pair
-            _run([nvcc, *NVCC_FLAGS, "-I", str(SOURCE_DIR), "-c", str(s), "-o", str(o)], f"compiling {s.name}")
+            _run([nvcc, *flags, "-I", str(SOURCE_DIR), "-c", str(s), "-o", str(o)], f"compiling {s.name}")
             if verbose:
                 _say(f"compiled {s.name} ({time.time() - t0:.0f} s)")
 
         with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
             list(ex.map(one, zip(srcs, objs)))
-        tmp = out_dir / (LIB_NAME + f".tmp{os.getpid()}")
+        tmp = out_dir / (name + f".tmp{os.getpid()}")
         _run([nvcc, "-shared", "-o", str(tmp), *map(str, objs), "-gencode", "arch=compute_100a,code=sm_100a"],
              "linking")
         os.replace(tmp, lib)
@@ -141,7 +158,7 @@ def load_library() -> ctypes.CDLL:
     global _lib
     with _lock:
         if _lib is None:
-            path = build()
+            path = build(checked=_checked)
             try:
                 _lib = ctypes.CDLL(str(path))
             except OSError as e:

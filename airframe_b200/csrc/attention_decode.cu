@@ -201,7 +201,9 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
 
   auto issue = [&](int i) {  // page i of this block's share into stage i % STAGES
     const int pp = pp_begin + i;
-    const int page = pt[ring_pages > 0 ? pp % ring_pages : pp];
+    const int entry = ring_pages > 0 ? pp % ring_pages : pp;
+    int page = AF_INDEX_OK(entry < a.max_pages, entry) ? pt[entry] : 0;
+    if (!AF_INDEX_OK(page >= 0, page)) page = 0;     // (the copy must still be made: the stage's barrier expects its bytes)
     const int row = (page * a.nkv + kvh) * AF_PAGE;
     unsigned char* st = da_smem + (size_t)(i % STAGES) * 2 * TILE_BYTES;
     uint64_t* bar = &full[i % NBAR];

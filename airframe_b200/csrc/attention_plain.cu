@@ -56,10 +56,13 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const flo
     // of the tokens of this step that share a ring row only the last is kept; padding rows are skipped
     if (slot >= 0 && !(ring_rows > 0 && pos + ring_rows < len_after[seq])) {
       const int r = ring_rows > 0 ? pos % ring_rows : pos;
-      const int page = page_table[(size_t)slot * max_pages + r / AF_PAGE];
-      const bool is_v = head >= nq + nkv;
-      const int h = head - nq - (is_v ? nkv : 0);
-      dst = (is_v ? vcache : kcache) + (((size_t)page * nkv + h) * AF_PAGE + r % AF_PAGE) * hd;
+      if (AF_INDEX_OK(pos >= 0 && r / AF_PAGE < max_pages, r)) {
+        const int page = page_table[(size_t)slot * max_pages + r / AF_PAGE];
+        const bool is_v = head >= nq + nkv;
+        const int h = head - nq - (is_v ? nkv : 0);
+        if (AF_INDEX_OK(page >= 0, page))
+          dst = (is_v ? vcache : kcache) + (((size_t)page * nkv + h) * AF_PAGE + r % AF_PAGE) * hd;
+      }
     }
   }
   const bool rotate = head < nq + nkv;
@@ -125,9 +128,11 @@ rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, long long row_stride, con
     const int slot = slots[seq];
     if (slot >= 0 && !(ring_rows > 0 && pos + ring_rows < len_after[seq])) {
       const int r = ring_rows > 0 ? pos % ring_rows : pos;
-      const int page = page_table[(size_t)slot * max_pages + r / AF_PAGE];
-      dst_row = ((size_t)page * nkv) * AF_PAGE + r % AF_PAGE;   // + h * AF_PAGE rows for kv head h
-      store = true;
+      if (AF_INDEX_OK(pos >= 0 && r / AF_PAGE < max_pages, r)) {
+        const int page = page_table[(size_t)slot * max_pages + r / AF_PAGE];
+        dst_row = ((size_t)page * nkv) * AF_PAGE + r % AF_PAGE;   // + h * AF_PAGE rows for kv head h
+        store = AF_INDEX_OK(page >= 0, page);
+      }
     }
   }
   // a thread's pieces all have the same place in their heads when the block's size is a multiple of
@@ -252,8 +257,10 @@ __global__ void kv_rows_kernel(int* __restrict__ rows, const int* __restrict__ p
   int row = -1;
   if (slot >= 0 && !(ring_rows > 0 && pos + ring_rows < len_after[seq])) {
     const int r = ring_rows > 0 ? pos % ring_rows : pos;
-    const int page = page_table[(size_t)slot * max_pages + r / AF_PAGE];
-    row = page * nkv * AF_PAGE + r % AF_PAGE;
+    if (AF_INDEX_OK(pos >= 0 && r / AF_PAGE < max_pages, r)) {
+      const int page = page_table[(size_t)slot * max_pages + r / AF_PAGE];
+      if (AF_INDEX_OK(page >= 0, page)) row = page * nkv * AF_PAGE + r % AF_PAGE;
+    }
   }
   rows[t] = row;
 }
@@ -404,6 +411,7 @@ __global__ void attn_decode_plain_kernel(T* __restrict__ out, int out_stride, co
   const float slope = slopes ? slopes[h] : 0.f;
   for (int j = lo; j <= pos; ++j) {
     const int r = ring_rows > 0 ? j % ring_rows : j;
+    if (!AF_INDEX_OK(r / AF_PAGE < max_pages && pt[r / AF_PAGE] >= 0, r)) continue;
     const size_t base = (((size_t)pt[r / AF_PAGE] * nkv + g) * AF_PAGE + r % AF_PAGE) * hd;
     attn_key(st, kcache + base, vcache + base, hd, lane, scale, cap, slope * (float)(j - pos));
   }

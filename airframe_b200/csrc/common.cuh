@@ -50,6 +50,30 @@ extern unsigned long long g_af_launches;
     return 0;                 \
   } while (0)
 
+// ---- the checked build (-DAF_BOUNDS_CHECK)
+// Indices that kernels take from data (a page of the page table, a row of a page table, a token id) are
+// checked before they are used: a bad one is recorded (a word per translation unit: failed, the index) and
+// its access is skipped; nothing traps.  af_bounds_failures() (elementwise.cu) reads and clears the words.
+// In the normal build AF_INDEX_OK(cond, index) is `true` and costs nothing.
+#ifdef AF_BOUNDS_CHECK
+static __device__ int af_bounds_word[2];
+typedef int (*AfBoundsReader)(int*);
+void af_register_bounds_reader(AfBoundsReader reader);
+static int af_bounds_read_here(int* out) {
+  int zero[2] = {0, 0};
+  cudaError_t e = cudaMemcpyFromSymbol(out, af_bounds_word, sizeof(zero));
+  if (e == cudaSuccess) e = cudaMemcpyToSymbol(af_bounds_word, zero, sizeof(zero));
+  return (int)e;
+}
+static struct AfBoundsRegistration {
+  AfBoundsRegistration() { af_register_bounds_reader(&af_bounds_read_here); }
+} af_bounds_registration;
+#define AF_INDEX_OK(cond, index) \
+  ((cond) ? true : (atomicExch(&af_bounds_word[1], (int)(index)), atomicExch(&af_bounds_word[0], 1), false))
+#else
+#define AF_INDEX_OK(cond, index) true
+#endif
+
 // ---- the current device
 // Limits and attributes belong to a device, not to the process: what is learnt or set once is
 // kept per device ordinal.

@@ -56,6 +56,34 @@ int af_sm_count() {
 // Streaming multiprocessors of the current device (the policies that cut work into blocks ask for it).
 AF_EXPORT int af_device_sm_count() { return af_sm_count(); }
 
+// The checked build's record: how many translation units saw a bad index since the last call (0: none),
+// *index one of the bad values.  The normal build checks nothing and answers -1.
+#ifdef AF_BOUNDS_CHECK
+static AfBoundsReader g_bounds_readers[32];
+static int g_n_bounds_readers = 0;
+void af_register_bounds_reader(AfBoundsReader reader) {
+  if (g_n_bounds_readers < 32) g_bounds_readers[g_n_bounds_readers++] = reader;
+}
+AF_EXPORT int af_bounds_failures(int* index) {
+  cudaDeviceSynchronize();
+  int failed = 0;
+  for (int i = 0; i < g_n_bounds_readers; ++i) {
+    int w[2] = {0, 0};
+    if (g_bounds_readers[i](w) != 0) return af_fail(-1, "af_bounds_failures: cannot read a record");
+    if (w[0]) {
+      ++failed;
+      if (index) *index = w[1];
+    }
+  }
+  return failed;
+}
+#else
+AF_EXPORT int af_bounds_failures(int* index) {
+  (void)index;
+  return -1;
+}
+#endif
+
 unsigned long long g_af_launches = 0;
 int g_af_pdl = 1;
 
@@ -75,6 +103,7 @@ __global__ void embed_kernel(float* __restrict__ out, const TW* __restrict__ tab
   int id = ids[t];
   // ids are validated on the host; a bad one yields zeros rather than a wild read
   const bool ok = id >= 0 && id < vocab;
+  (void)AF_INDEX_OK(ok, id);
   const TW* row = table + (size_t)(ok ? id : 0) * hidden;
   float* o = out + (size_t)t * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) o[i] = ok ? to_f32(row[i]) * scale : 0.f;

@@ -43,7 +43,8 @@ constexpr unsigned long long AF_WAIT_LIMIT_NS = 2000000000ull;  // 2 s
 
 // Waits until the barrier's phase `parity` is complete.  False when the time
 // limit ran out (then *give_up is set) or another thread gave up already.
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* give_up) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* give_up,
+                                          unsigned long long limit_ns = AF_WAIT_LIMIT_NS) {
   if (mbar_try_wait(bar, parity)) return true;
   // try_wait itself suspends the thread for a while; the timer read between two polls
   // keeps waiting threads from crowding out working ones
@@ -51,7 +52,7 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volati
   for (;;) {
     if (mbar_try_wait(bar, parity)) return true;
     if (*give_up) return false;
-    if (now_ns() - t0 > AF_WAIT_LIMIT_NS) {
+    if (now_ns() - t0 > limit_ns) {
       *give_up = 1;
       return false;
     }

@@ -75,6 +75,29 @@ class Model:
             out.append((m.kv_need(), m.state_need(), e.cache_from))
         return out
 
+    # ------------------------------------------------------------------ what a step costs
+
+    def decode_bytes(self, lens) -> int:
+        """Bytes a decode step of sequences that hold ``lens`` tokens has to read:
+        every weight it uses once and the cache of the live sequences (the parts
+        answer for themselves; a run that reads another run's cache reads it again)."""
+        total = self.embedding.decode_bytes(lens) + self.final_norm.decode_bytes(lens) + self.head.decode_bytes(lens)
+        return total + sum(self.blocks[e.layer].decode_bytes(lens) for e in self.spec.schedule)
+
+    def prefill_flops(self, lens, n_logits: int) -> int:
+        """Floating-point operations of a prefill of prompts of ``lens`` tokens with ``n_logits`` rows of logits."""
+        total = sum(self.blocks[e.layer].prefill_flops(lens) for e in self.spec.schedule)
+        flops = getattr(self.head, "logits_flops", None)
+        return total + (flops(n_logits) if flops is not None else 0)
+
+    def score_flops(self, lens) -> int:
+        """The part of :meth:`prefill_flops` that the mixers spend on scores (those that say so)."""
+        total = 0
+        for e in self.spec.schedule:
+            f = getattr(self.blocks[e.layer].mixer, "score_flops", None)
+            total += f(lens) if f is not None else 0
+        return total
+
     # ------------------------------------------------------------------ forward
 
     def hidden(self, batch, cache, probe=None) -> torch.Tensor:

@@ -84,6 +84,17 @@ def launch_count() -> int:
     return int(f())
 
 
+def bounds_failures():
+    """The checked build's record (see ``csrc.use_checked_build``): None in the
+    normal build, else (translation units that saw a bad index since the last
+    call, one of the bad values).  Synchronises the device."""
+    index = c_int(0)
+    n = int(_lib().af_bounds_failures(ctypes.byref(index)))
+    if n < 0:
+        return None
+    return n, int(index.value)
+
+
 _SMS = {}
 
 
@@ -314,6 +325,17 @@ def check_device_errors(device) -> None:
     if int(w.item()) != 0:
         w.zero_()
         raise KernelError("a tensor-core kernel gave up waiting on a barrier (results of the step are invalid)")
+
+
+def selftest_wait_runs_out(device, limit_ms: float = 2.0) -> float:
+    """Runs a kernel whose wait on a barrier nobody arrives on gives up after
+    ``limit_ms`` and sets the device's error word, as the tensor-core kernels'
+    waits do after their limit.  Returns the milliseconds the wait took; the
+    error word is left set (``check_device_errors`` raises and clears it)."""
+    waited = torch.zeros(1, dtype=torch.int64, device=device)
+    _check(_lib().af_selftest_wait_runs_out(_ptr(error_word(device), "err", torch.int32),
+                                            ctypes.c_ulonglong(int(limit_ms * 1e6)), _ptr(waited), _stream()))
+    return float(waited.item()) / 1e6
 
 
 def gemm_tc_supported(x, w, out) -> bool:

@@ -86,6 +86,27 @@ class Attention(Mixer):
             self.tickets = torch.zeros(4 * ((self.w_qkv.shape[0] + 127) // 128), dtype=torch.int32,
                                        device=self.w_qkv.device)
 
+    def _el(self) -> int:
+        return 4 if self.ctx.compute_dtype == torch.float32 else 2
+
+    def decode_bytes(self, lens) -> int:
+        weights = ((self.nq + 2 * self.nkv) * self.hd * self.hidden + self.hidden * self.nq * self.hd) * self._el()
+        kv_row = 2 * self.nkv * self.hd * self._el()
+        return weights + sum(kv_row * (min(n, self.window) if self.window else n) for n in lens)
+
+    def score_flops(self, lens) -> int:
+        """The part of :meth:`prefill_flops` that is scores and their products with v."""
+        pairs = 0
+        for n in lens:          # visible (query, key) pairs of a causal prompt, with the window where there is one
+            w = self.window
+            pairs += n * (n + 1) // 2 if not w or n <= w else w * (w + 1) // 2 + (n - w) * w
+        return 2 * 2 * pairs * self.nq * self.hd
+
+    def prefill_flops(self, lens) -> int:
+        T = sum(lens)
+        proj = 2 * T * ((self.nq + 2 * self.nkv) * self.hd * self.hidden + self.hidden * self.nq * self.hd)
+        return proj + self.score_flops(lens)
+
     def _project_rotate_store(self, x, batch, view):
         """q, k, v rows of the step with positions encoded and k, v stored: the
         product with the rotation and the cache write in its epilogue."""

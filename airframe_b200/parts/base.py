@@ -109,6 +109,17 @@ class Part:
     def load(self, weights: dict) -> None:
         pass
 
+    # ---- what a step costs, for measurement (rooflines): every part answers for itself
+
+    def decode_bytes(self, lens) -> int:
+        """Bytes that one decode step of sequences holding ``lens`` tokens has to
+        read for this part: its weights once, and what it keeps per sequence."""
+        return 0
+
+    def prefill_flops(self, lens) -> int:
+        """Floating-point operations of this part in a prefill of prompts of ``lens`` tokens."""
+        return 0
+
     def param(self, key: str):
         if key not in self.params:
             raise ConfigError(f"{self.category} part '{self.kind}' needs parameter '{key}'")
@@ -226,6 +237,12 @@ class Block(Part):
         """The norm this block applies to x first, or None.  The layer before
         may compute it in its last kernel and pass the result as ``normed``."""
         return None
+
+    def decode_bytes(self, lens) -> int:
+        return sum(c.decode_bytes(lens) for c in self.children())
+
+    def prefill_flops(self, lens) -> int:
+        return sum(c.prefill_flops(lens) for c in self.children())
 
     def forward(self, x, batch, view, normed=None, next_pre=None):
         """Run the layer on the float32 residual stream x [T, H] in place.

@@ -37,6 +37,9 @@ class TokenEmbedding(Part):
     def load(self, weights):
         self.table = weights[self.name].to(self.ctx.compute_dtype).contiguous()
 
+    def decode_bytes(self, lens) -> int:
+        return len(lens) * self.hidden * (4 if self.ctx.compute_dtype == torch.float32 else 2)   # the rows it gathers
+
     def forward(self, ids):
         """ids int32 [T] -> float32 residual stream [T, H]."""
         x = torch.empty(ids.shape[0], self.hidden, dtype=torch.float32, device=ids.device)
@@ -74,6 +77,12 @@ class LmHead(Part):
         if name is None or name not in weights:
             name = self.param("tied_to")
         self.w = weights[name].to(self.ctx.compute_dtype).contiguous()
+
+    def decode_bytes(self, lens) -> int:
+        return self.vocab * self.hidden * (4 if self.ctx.compute_dtype == torch.float32 else 2)
+
+    def logits_flops(self, rows: int) -> int:
+        return 2 * rows * self.vocab * self.hidden
 
     def forward(self, y):
         """y [R, H] compute dtype (after the final norm) -> float32 logits [R, V]."""

@@ -51,6 +51,12 @@ class GatedMlp(FeedForward):
                      else torch.cat([wg, wu], dim=0).contiguous())
         self.w_down = weights[d].to(dt).contiguous()
 
+    def decode_bytes(self, lens) -> int:
+        return 3 * self.hidden * self.inter * (4 if self.ctx.compute_dtype == torch.float32 else 2)
+
+    def prefill_flops(self, lens) -> int:
+        return 2 * sum(lens) * 3 * self.hidden * self.inter
+
     def forward(self, x, batch):
         h = gated_linear(x, self.w_gu, self.inter, self.activation, self.interleaved)
         return linear_split(h, self.w_down)

@@ -36,6 +36,9 @@ class RmsNorm(Norm):
         # statistics and the (offset + w) factor are 32-bit in both precisions
         self.w = weights[self.name].to(torch.float32).contiguous()
 
+    def decode_bytes(self, lens) -> int:
+        return 4 * self.size
+
     def forward(self, x, out_dtype, rows=None):
         n = x.shape[0] if rows is None else rows.shape[0]
         y = torch.empty(n, self.size, dtype=out_dtype, device=x.device)

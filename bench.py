@@ -4,9 +4,9 @@
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
 
 A step is one decode step of a batch of 8 sequences that hold 2,048-token
-prompts (context limit 8192): the model's step function plus greedy sampling on
-the device, stepped as the generation loop steps it (a step takes its tokens from
-the device and is queued before the host has read them).  ``value`` is decoded
+prompts (context limit 8192): the model's step function with the greedy choice in
+its head's epilogue, stepped as the generation loop steps it (a step takes its
+tokens from the device and is queued before the host has read them).  ``value`` is decoded
 tokens a second, timed with CUDA events around exactly K steps after W warm-up
 steps (default 32: the first 30 or so steps after a burst of prompts run at
 lowered clocks, about 2.1 ms instead of 1.8).  ``e2e`` is the same through
@@ -17,6 +17,13 @@ step's fraction of the HBM roofline, decode at batch 1 and 64, the clocks seen
 during the timed region and the number of this library's kernels launched in it.
 Every decode step reads all weights (5.2 GB), far more than the 126 MB L2, so
 no separate L2 flush is needed between iterations.
+
+``--sizes 9b`` and ``--sizes 27b`` run the workloads named for those sizes: a batch of
+8 prompts of unequal random lengths 512-4,096 and 256 decode steps; a batch of 16
+prompts of 1,024-8,192 tokens and 128 decode steps (a prompt is at most as long as
+leaves room for the decoded tokens in the context of 8192).  Their prefill figure is
+the whole unequal batch in one step.  Bytes and flops of the rooflines are asked of
+the model's parts (``Model.decode_bytes``, ``Model.prefill_flops``).
 """
 from __future__ import annotations
 
@@ -47,6 +54,13 @@ SIZES = {
            "intermediate_size": 14336},
     "27b": {"num_hidden_layers": 46, "hidden_size": 4608, "num_attention_heads": 32, "num_key_value_heads": 16,
             "head_dim": 128, "intermediate_size": 36864, "query_pre_attn_scalar": 144},
+}
+# what is run at each size: the batch, the prompts' lengths (one number: all equal; two: uniform random
+# between them), the decode steps that are timed, and the batches of the extra decode points
+WORKLOADS = {
+    "2b": {"batch": 8, "prompt": (2048,), "steps": 256, "points": (1, 64)},
+    "9b": {"batch": 8, "prompt": (512, 4096), "steps": 256, "points": ()},
+    "27b": {"batch": 16, "prompt": (1024, 8192), "steps": 128, "points": ()},
 }
 PROMPT_LEN = 2048
 CONTEXT = 8192
@@ -112,40 +126,7 @@ class ClockSampler:
                 "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def model_bytes(cfg, n_layers):
-    """Bytes of the weights a decode step reads once (bf16)."""
-    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
-    q = cfg["num_attention_heads"] * cfg["head_dim"]
-    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
-    per_layer = (q + 2 * kv) * h + h * q + 3 * h * i + 4 * h
-    return 2 * (n_layers * per_layer + v * h + h)
-
-
-def cache_bytes(cfg, n_layers, lens):
-    """Bytes of keys and values a decode step reads for sequences of these lengths."""
-    kv_row = 2 * cfg["num_key_value_heads"] * cfg["head_dim"] * 2
-    total = 0
-    for layer in range(n_layers):
-        sliding = layer % 2 == 0
-        for n in lens:
-            total += kv_row * (min(n, cfg["sliding_window"]) if sliding else n)
-    return total
-
-
-def prefill_flops(cfg, n_layers, T, n_logits):
-    h, i, v = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
-    q = cfg["num_attention_heads"] * cfg["head_dim"]
-    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
-    linear = 2 * T * n_layers * ((q + 2 * kv) * h + h * q + 3 * h * i)
-    attn = 0
-    for layer in range(n_layers):
-        w = cfg["sliding_window"] if layer % 2 == 0 else None
-        pairs = sum(min(t + 1, w) if w else t + 1 for t in range(T))
-        attn += 2 * 2 * pairs * q
-    return linear + attn + 2 * n_logits * v * h
-
-
-def prefill_shares(prefill_once, cfg, n_layers, pk) -> dict:
+def prefill_shares(prefill_once, model, lens, pk) -> dict:
     """The layers' products and the attention kernels of one prefill apart: the time charged to them
     (one more prefill under the CUDA profiler of PyTorch) and their flops over the bf16 peak."""
     import torch
@@ -157,60 +138,79 @@ def prefill_shares(prefill_once, cfg, n_layers, pk) -> dict:
     # charged the time from the end of what ran before it to its own end, so that the shares add up to the
     # time the device was busy.
     evs = sorted((e for e in prof.events() if "cuda" in str(e.device_type).lower()), key=lambda e: e.time_range.start)
-    gemm_us = attn_us = 0.0
+    gemm_us = attn_us = other_us = 0.0
     busy_until = None
     for e in evs:
         start, end = e.time_range.start, e.time_range.end
         own = end - start if busy_until is None else max(0.0, end - max(start, busy_until))
         busy_until = end if busy_until is None else max(busy_until, end)
-        if "gemm_tc_kernel<256" in e.name or "gemm_tc_kernel<128" in e.name:     # (the head's one row is not among these)
-            gemm_us += own
+        if "gemm_tc_kernel<256" in e.name or "gemm_tc_kernel<128" in e.name or "gemm_tc_pair_kernel" in e.name:
+            gemm_us += own                                     # (the head's few rows are not among these)
         elif "attn_prefill" in e.name:
             attn_us += own
-    h, i = cfg["hidden_size"], cfg["intermediate_size"]
-    q = cfg["num_attention_heads"] * cfg["head_dim"]
-    kv = cfg["num_key_value_heads"] * cfg["head_dim"]
-    linear = 2 * PROMPT_LEN * n_layers * ((q + 2 * kv) * h + h * q + 3 * h * i)
-    attn = prefill_flops(cfg, n_layers, PROMPT_LEN, 0) - linear
+        else:
+            other_us += own                                    # norms, rotary, embedding, head, copies
+    attn = model.score_flops(lens)
+    linear = model.prefill_flops(lens, 0) - attn
     peak = pk["bf16_tflops"] * 1e12
     out = {}
     if gemm_us > 0:
         out["products"] = {"ms": gemm_us / 1e3, "frac": linear / (gemm_us / 1e6) / peak}
     if attn_us > 0:
         out["attention"] = {"ms": attn_us / 1e3, "frac": attn / (attn_us / 1e6) / peak}
+    out["other"] = {"ms": other_us / 1e3}
     return out
 
 
 def run_ours(args) -> dict:
-    global PROMPT_LEN
-    PROMPT_LEN = args.prompt_len
     import torch
     sys.path.insert(0, str(ROOT))
-    from airframe_b200 import kernels
+    from airframe_b200 import kernels, transfers
     from airframe_b200.config import config_from_dict
     from airframe_b200.engine import GpuRuntime, StepEntry
     from airframe_b200.sampling import Sampler, SamplingParams
 
+    work = dict(WORKLOADS[args.sizes])
+    if args.prompt_len:
+        work["prompt"] = (args.prompt_len,)
+    B = args.batch or work["batch"]
+    K = args.steps or work["steps"]
+    W = max(args.warmup, 3)
+    points = () if args.no_points else work["points"]
     full = dict(GEMMA2_2B, **SIZES[args.sizes])
     full_layers = full["num_hidden_layers"]
     n_layers = args.layers or full_layers
     cfg_dict = dict(full, num_hidden_layers=n_layers)
     cfg = config_from_dict(cfg_dict)
-    B, K, W = args.batch, args.steps, max(args.warmup, 3)
+    V = cfg.vocab_size
     pk = peaks()
     torch.manual_seed(0)
-    max_b = max([B] + ([] if args.no_points else [1, 64]))
-    budget = max_b * ((PROMPT_LEN + K + W + 8 + 63) // 64 * 64)
+    room = CONTEXT - (K + W + 2)                      # a prompt leaves room for the tokens decoded after it
+
+    def lengths(n, seed):
+        spec = work["prompt"]
+        if len(spec) == 1:
+            return [min(spec[0], room)] * n
+        g = torch.Generator().manual_seed(seed)
+        hi = min(spec[1], room)
+        return [int(x) for x in torch.randint(spec[0], hi + 1, (n,), generator=g)]
+
+    def prompts(lens, seed):
+        g = torch.Generator().manual_seed(seed)
+        return [torch.randint(0, V, (n,), generator=g).tolist() for n in lens]
+
+    def pages(n):
+        return (n + K + W + 8 + 63) // 64 * 64
+
+    main_lens = lengths(B, 100 + B)
+    budget = max([sum(pages(n) for n in main_lens)] + [b * pages(min(PROMPT_LEN, room)) for b in points])
+    max_b = max([B] + list(points))
     rt = GpuRuntime.random(cfg, seed=0, dtype="bfloat16", max_tokens=budget, max_context=CONTEXT,
                            max_sequences=max_b, on_device=True)
     eng = rt.engine
+    model = eng.model
     dev = eng.device
-    V = cfg.vocab_size
     greedy = SamplingParams(max_tokens=1, temperature=0.0, repetition_penalty=1.0, ignore_eos=True)
-
-    def prompts(n, seed):
-        g = torch.Generator().manual_seed(seed)
-        return [torch.randint(0, V, (PROMPT_LEN,), generator=g).tolist() for _ in range(n)]
 
     def timed(fn, n):
         start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
@@ -237,14 +237,16 @@ def run_ours(args) -> dict:
         t0 = evs[first].time_range.start
         return [(e.time_range.start - t0, e.time_range.end - e.time_range.start, e.name) for e in evs[first:]]
 
-    def decode_rate(batch, steps, warm, clocks=None, timeline=None):
-        """tokens/s, ms/step and launches of `steps` decode steps at `batch` after 2,048-token prompts."""
+    def decode_rate(lens, steps, warm, clocks=None, timeline=None):
+        """tokens/s, ms/step, launches and final lengths of `steps` decode steps of sequences whose prompts
+        have `lens` tokens."""
+        batch = len(lens)
         sampler = Sampler(V, dev)
         states = [sampler.new_state(greedy, i) for i in range(batch)]
         slots = [eng.take_slot() for _ in range(batch)]
         try:
-            ps = prompts(batch, 100 + batch)
-            first = eng.step([StepEntry(s, p, [PROMPT_LEN - 1]) for s, p in zip(slots, ps)], greedy=True)
+            ps = prompts(lens, 100 + batch)
+            first = eng.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, ps)], greedy=True)
             state = {}
 
             # the product's own way of stepping (GenerationLoop, greedy): a step gives its arg-max tokens (the
@@ -268,32 +270,37 @@ def run_ours(args) -> dict:
             ms = timed(one, steps)
             state["pending"].result()
             launches = kernels.launch_count() + eng.replayed_launches - n0
-            lens = [eng.length(s) for s in slots]
-            return batch * steps / (ms / 1e3), ms / steps, launches, lens
+            after = [eng.length(s) for s in slots]
+            return batch * steps / (ms / 1e3), ms / steps, launches, after
         finally:
             for s in slots:
                 eng.free_slot(s)
 
-    # ---- prefill of 2,048 tokens (one sequence, logits at its last position)
-    def prefill_once():
-        s = eng.take_slot()
-        try:
-            eng.step([StepEntry(s, pf_prompt, [PROMPT_LEN - 1])])
-        finally:
-            eng.free_slot(s)
+    # ---- prefill: one 2,048-token sequence (the default run), or the workload's whole unequal batch in one step;
+    #      logits at the last position of every sequence
+    pf_lens = main_lens if len(work["prompt"]) > 1 else [main_lens[0]]
+    pf_prompts = prompts(pf_lens, 7)
 
-    pf_prompt = prompts(1, 7)[0]
+    def prefill_once():
+        slots = [eng.take_slot() for _ in pf_prompts]
+        try:
+            eng.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, pf_prompts)])
+        finally:
+            for s in slots:
+                eng.free_slot(s)
+
     for _ in range(3):
         prefill_once()
     reps = 5
     pf_ms = timed(prefill_once, reps) / reps
-    pf_flops = prefill_flops(cfg_dict, n_layers, PROMPT_LEN, 1)
-    prefill = {"value": PROMPT_LEN / (pf_ms / 1e3), "tokens": PROMPT_LEN, "ms": pf_ms,
-               "frac": pf_flops / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12)}
+    pf_tokens = sum(pf_lens)
+    pf_flops = model.prefill_flops(pf_lens, len(pf_lens))
+    prefill = {"value": pf_tokens / (pf_ms / 1e3), "tokens": pf_tokens, "ms": pf_ms,
+               "frac": pf_flops / (pf_ms / 1e3) / (pk["bf16_tflops"] * 1e12), "sequences": len(pf_lens)}
 
     if args.timeline:
         tl = []
-        decode_rate(B, 4, W, timeline=tl)
+        decode_rate(main_lens, 4, W, timeline=tl)
         print(f"# one decode step, batch {B}, {n_layers} layers: start us, duration us, kernel")
         for start, dur, name in tl:
             print(f"{start:9.1f} {dur:8.1f}  {name[:100]}")
@@ -301,25 +308,26 @@ def run_ours(args) -> dict:
 
     # ---- the headline: decode at batch B
     clocks = ClockSampler()
-    value, ms_step, launches, lens = decode_rate(B, K, W, clocks)
+    value, ms_step, launches, after = decode_rate(main_lens, K, W, clocks)
     clock_info = clocks.stop()
-    need = model_bytes(cfg_dict, n_layers) + cache_bytes(cfg_dict, n_layers, lens)
+    # the bytes a step has to read: every weight once and the cache of the live sequences, at the lengths they
+    # have in the middle of the timed steps
+    mid = [n - K // 2 for n in after]
+    need = model.decode_bytes(mid)
     achieved = need / (ms_step / 1e3) / 1e9
     roofline = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                "frac": achieved / pk["hbm_gbs"], "peaks": pk["source"]}
+                "frac": achieved / pk["hbm_gbs"], "peaks": pk["source"], "bytes": need}
 
-    points = {}
-    if not args.no_points:
-        for b in (1, 64):
-            points[f"decode_b{b}"] = decode_rate(b, max(4, K // 2), W)[0]
+    point_rates = {}
+    for b in points:
+        point_rates[f"decode_b{b}"] = decode_rate([min(PROMPT_LEN, room)] * b, max(4, K // 2), W)[0]
 
     # ---- end to end through the public entry point
     n_new = K + 1
     stamps = []
     params = SamplingParams(max_tokens=n_new, temperature=0.0, repetition_penalty=1.0, ignore_eos=True)
-    ps = prompts(B, 500)
+    ps = prompts(main_lens, 500)
     rt.generate(ps, SamplingParams(max_tokens=4, temperature=0.0, repetition_penalty=1.0, ignore_eos=True))
-    from airframe_b200 import transfers
     moved = []
 
     def on_token(i, t):
@@ -340,25 +348,30 @@ def run_ours(args) -> dict:
 
     # (last, so that the launches before it come in the same order with and without it)
     try:
-        prefill["profiled"] = dict(prefill_shares(prefill_once, cfg_dict, n_layers, pk),
+        prefill["profiled"] = dict(prefill_shares(prefill_once, model, pf_lens, pk),
                                    note="kernel times of one more prefill under the CUDA profiler of PyTorch, "
                                         "not timed with events like the figures beside it")
     except Exception as why:        # a profiler that cannot attach (another one is attached already) costs only this key
         prefill["profiled"] = {"unavailable": str(why)[:120]}
 
+    equal = len(work["prompt"]) == 1
+    what = f"{main_lens[0]:,}-token prompts" if equal else f"prompts of {work['prompt'][0]:,}-{min(work['prompt'][1], room):,} tokens"
     return {
-        "metric": f"Gemma-2 {args.sizes.upper()} bf16 decode tokens/s at batch {B} ({PROMPT_LEN:,}-token prompts)",
+        "metric": f"Gemma-2 {args.sizes.upper()} bf16 decode tokens/s at batch {B} ({what})",
         "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms_step,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights N(0, 0.02), uniform random token ids",
-        "config": {"model": f"gemma-2-{args.sizes} sizes", "global_batch": B, "seq_len": PROMPT_LEN, "context": CONTEXT,
+        "config": {"model": f"gemma-2-{args.sizes} sizes", "global_batch": B,
+                   "seq_len": main_lens[0] if equal else round(sum(main_lens) / B), "context": CONTEXT,
+                   "prompt_lens": "equal" if equal else f"uniform random, mean {round(sum(main_lens) / B)}, "
+                                                         f"min {min(main_lens)}, max {max(main_lens)}",
                    "parallelism": "single-gpu", "layers": n_layers, "layers_full": full_layers,
                    "hidden": cfg_dict["hidden_size"], "heads": cfg_dict["num_attention_heads"],
                    "kv_heads": cfg_dict["num_key_value_heads"], "head_dim": cfg_dict["head_dim"],
                    "intermediate": cfg_dict["intermediate_size"], "vocab": cfg_dict["vocab_size"],
                    "sliding_window": cfg_dict["sliding_window"], "sampling": "greedy, in the head's epilogue",
-                   "l2": f"inputs larger than L2 (weights {model_bytes(cfg_dict, n_layers) / 1e9:.1f} GB per step)"},
-        "prefill": prefill, "roofline": roofline, "points": points, "e2e": e2e,
+                   "l2": f"inputs larger than L2 (weights {model.decode_bytes([]) / 1e9:.1f} GB per step)"},
+        "prefill": prefill, "roofline": roofline, "points": point_rates, "e2e": e2e,
         "gpu_launches": launches, "clocks": clock_info, "impl": "ours",
     }
 
@@ -366,19 +379,20 @@ def run_ours(args) -> dict:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--steps", type=int, default=0, help="decode steps that are timed (default: the workload's, 256 at 2b)")
     ap.add_argument("--warmup", type=int, default=32,
                     help="untimed decode steps after the prompts (the first 30 or so after a burst of prompts "
                          "run at lowered clocks)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=0, help="sequences of the decode batch (default: the workload's, 8 at 2b)")
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the model has (named in config)")
     ap.add_argument("--no-points", action="store_true", help="skip decode at batch 1 and 64")
     ap.add_argument("--timeline", action="store_true",
                     help="print the kernels of one decode step with their start and duration, then exit")
-    ap.add_argument("--prompt-len", type=int, default=PROMPT_LEN,
-                    help="tokens of every prompt, and of the prefill that is timed (not the default run)")
-    ap.add_argument("--sizes", default="2b", choices=sorted(SIZES), help="layer sizes of this Gemma-2 model")
+    ap.add_argument("--prompt-len", type=int, default=0,
+                    help="equal prompts of this many tokens instead of the workload's (not the default run)")
+    ap.add_argument("--sizes", default="2b", choices=sorted(SIZES),
+                    help="layer sizes of this Gemma-2 model, with the workload named for them")
     args = ap.parse_args()
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":

@@ -660,3 +660,28 @@ def test_attention_prefill_tcgen05_finds_one_far_key_the_window_edge_and_a_growi
     ref = plain.attention(qb.double().reshape(n, nq, hd), kb.double().reshape(n, nkv, hd),
                           v.double().reshape(n, nkv, hd), 1.0, 0.0, None)
     close(out, ref, torch.bfloat16, scale=max(1.0, float(ref.abs().max())))
+
+
+def test_a_wait_that_runs_out_sets_the_error_word_and_the_library_goes_on(K):
+    """The give-up path of the bounded waits for real: a barrier nobody arrives on, a limit of 2 ms.  The
+    kernel returns by itself, the error word is set and is reported once, and the next product is right."""
+    import time
+    K.check_device_errors(DEV)                         # (clean before)
+    t0 = time.perf_counter()
+    waited_ms = K.selftest_wait_runs_out(DEV, limit_ms=2.0)
+    torch.cuda.synchronize()
+    host_ms = (time.perf_counter() - t0) * 1e3
+    assert 2.0 <= waited_ms < 20.0, waited_ms          # it waited for its limit and not much longer
+    assert host_ms < 2000.0
+    assert int(K.error_word(DEV).item()) == 1
+    with pytest.raises(K.KernelError, match="gave up waiting"):
+        K.check_device_errors(DEV)
+    K.check_device_errors(DEV)                         # reported once, then clear
+    x = torch.randn(8, 256).to(torch.bfloat16)
+    w = (torch.randn(384, 256) * 0.05).to(torch.bfloat16)
+    out = torch.empty(8, 384, dtype=torch.float32, device=DEV)
+    K.gemm_tc(out, x.to(DEV), w.to(DEV))
+    K.check_device_errors(DEV)
+    close(out, x.double() @ w.double().T, torch.float32)
+    with pytest.raises(K.KernelError, match="100 ms"):
+        K.selftest_wait_runs_out(DEV, limit_ms=5000.0)
