@@ -63,9 +63,11 @@ class RandomSource:
         return random_tensor(self.decls[name], self.seed, self.store_dtype, self.device)
 
 
-def write_random_model(folder, config, seed: int, store_dtype: str = "bfloat16") -> Path:
+def write_random_model(folder, config, seed: int, store_dtype: str = "bfloat16", device="cpu") -> Path:
     """Write ``config.json`` and ``model.safetensors`` with seeded random
-    weights for ``config`` (a typed configuration of a registered architecture)."""
+    weights for ``config`` (a typed configuration of a registered architecture).
+    ``device``: where the values are drawn (a CUDA device draws billions of
+    values in seconds; its values differ from the CPU's for the same seed)."""
     from ..engine.model import declared_weights  # late: the engine imports this package
 
     folder = Path(folder)
@@ -79,7 +81,7 @@ def write_random_model(folder, config, seed: int, store_dtype: str = "bfloat16")
     def entries():
         for d in decls:
             dt = torch.int32 if d.kind == "int_table" else dtype
-            yield d.name, tuple(d.shape), dt, (lambda d=d: random_tensor(d, seed, dtype))
+            yield d.name, tuple(d.shape), dt, (lambda d=d: random_tensor(d, seed, dtype, device))
 
     write_safetensors(folder / "model.safetensors", entries(), metadata={"format": "pt", "seed": seed})
     return folder

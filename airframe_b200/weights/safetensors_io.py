@@ -113,4 +113,4 @@ def write_safetensors(path, tensors, metadata=None) -> None:
                                        f"declared {list(shape)} {dtype}")
             t = t.contiguous().cpu()
             if t.numel():
-                fh.write(t.view(torch.uint8).numpy().tobytes())
+                fh.write(t.view(torch.uint8).numpy().data)      # (the array's own memory: no copy)

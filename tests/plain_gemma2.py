@@ -33,21 +33,26 @@ _ST_DTYPES = {
 }
 
 
-def read_safetensors(path) -> dict:
-    """name -> torch tensor (CPU, stored dtype) of one .safetensors file."""
-    raw = Path(path).read_bytes()
-    (hlen,) = struct.unpack("<Q", raw[:8])
-    header = json.loads(raw[8:8 + hlen].decode("utf-8"))
+def read_safetensors(path, dtype=None) -> dict:
+    """name -> torch tensor (CPU) of one .safetensors file, in the stored dtype or
+    widened to ``dtype`` (each tensor is converted straight from the file's bytes)."""
+    raw = np.fromfile(str(path), dtype=np.uint8)
+    (hlen,) = struct.unpack("<Q", raw[:8].tobytes())
+    header = json.loads(raw[8:8 + hlen].tobytes().decode("utf-8"))
     base = 8 + hlen
+    whole = torch.from_numpy(raw)
     out = {}
     for name, meta in header.items():
         if name == "__metadata__":
             continue
         a, b = meta["data_offsets"]
         dt = _ST_DTYPES[meta["dtype"]]
-        buf = bytearray(raw[base + a: base + b])
-        t = torch.frombuffer(buf, dtype=dt) if b > a else torch.empty(0, dtype=dt)
-        out[name] = t.reshape(meta["shape"]).clone()
+        chunk = whole[base + a: base + b]
+        if (base + a) % torch.empty(0, dtype=dt).element_size():
+            chunk = chunk.clone()                              # (a view of wider elements must start aligned)
+        t = chunk.view(dt) if b > a else torch.empty(0, dtype=dt)
+        t = t.reshape(meta["shape"])
+        out[name] = t.to(dtype) if dtype is not None and t.is_floating_point() else t.clone()
     return out
 
 
@@ -55,7 +60,7 @@ def read_model_folder(folder, dtype=torch.float64):
     """(config dict, weights dict widened to ``dtype``)."""
     folder = Path(folder)
     cfg = json.loads((folder / "config.json").read_text())
-    w = {k: v.to(dtype) for k, v in read_safetensors(folder / "model.safetensors").items()}
+    w = read_safetensors(folder / "model.safetensors", dtype)
     return cfg, w
 
 

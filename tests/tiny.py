@@ -75,11 +75,11 @@ SMALL_H = dict(WIDE_D, num_hidden_layers=3, hidden_size=192, num_attention_heads
 CONFIGS = {"H": SMALL_H, "A": TINY_A, "B": TINY_B, "C": TINY_C, "D": WIDE_D, "E": WIDE_E, "F": WIDE_F, "G": ODD_G}
 
 
-def make_folder(cfg_dict, seed=0, store_dtype=None, root=None):
+def make_folder(cfg_dict, seed=0, store_dtype=None, root=None, device="cpu"):
     """Write a random model folder for ``cfg_dict`` under a temporary place; returns its path."""
     from airframe_b200.config import config_from_dict
     from airframe_b200.weights import write_random_model
     root = Path(root or tempfile.mkdtemp(prefix="af_model_"))
     cfg = config_from_dict(cfg_dict)
-    write_random_model(root, cfg, seed, store_dtype or cfg_dict.get("torch_dtype", "bfloat16"))
+    write_random_model(root, cfg, seed, store_dtype or cfg_dict.get("torch_dtype", "bfloat16"), device=device)
     return root
