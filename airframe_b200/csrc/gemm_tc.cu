@@ -359,18 +359,17 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
             for (int j = 0; j < CW; ++j) v[j] = a.cap * tanhf(v[j] / a.cap);
           }
           if constexpr (ARGMAX) {
+            // per token: the warp's largest value (one redux on the order-preserving bits), then the lowest
+            // row among the lanes that hold it (a second one)
 #pragma unroll
             for (int j = 0; j < CW; ++j) {
               const bool has = f < a.N && isfinite(v[j]);
-              unsigned long long key =
-                  has ? ((unsigned long long)tc_ordered_bits(v[j]) << 32) | (unsigned long long)(0xffffffffu - (uint32_t)f)
-                      : 0ull;
-#pragma unroll
-              for (int o = 16; o > 0; o >>= 1) {
-                const unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
-                key = other > key ? other : key;
-              }
-              if (lane == 0 && key != 0ull && m0 + c0 + j < a.M) atomicMax(a.keys + (size_t)(m0 + c0 + j) * AF_KEY_STRIDE, key);
+              const uint32_t bits = has ? tc_ordered_bits(v[j]) : 0u;        // (finite values never map to 0)
+              const uint32_t best = __reduce_max_sync(0xffffffffu, bits);
+              const uint32_t row = __reduce_min_sync(0xffffffffu, has && bits == best ? (uint32_t)f : 0xffffffffu);
+              if (lane == 0 && best != 0u && m0 + c0 + j < a.M)
+                atomicMax(a.keys + (size_t)(m0 + c0 + j) * AF_KEY_STRIDE,
+                          ((unsigned long long)best << 32) | (unsigned long long)(0xffffffffu - row));
             }
             continue;
           }

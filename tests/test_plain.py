@@ -133,3 +133,30 @@ def test_xorshift_is_deterministic_and_in_range():
     from airframe_b200.sampling import XorShift64Star
     c = XorShift64Star(42)
     assert [c.next_f32() for _ in range(100)] == [float(x) for x in xs]
+
+
+def test_score_scale_is_query_pre_attn_scalar_not_head_dim(model_a):
+    """Gemma-2's own: scores are scaled by query_pre_attn_scalar^-0.5 (27B: 144 with head_dim 128)."""
+    cfg, w = model_a
+    ids = [5, 17, 3, 200, 9, 41]
+    base = plain.logits(cfg, w, ids)
+    other = plain.logits(dict(cfg, query_pre_attn_scalar=cfg["query_pre_attn_scalar"] * 4), w, ids)
+    assert not torch.allclose(base, other)
+    # one layer by hand: the block's attention equals attention() called with that scale
+    x = plain.embed(ids, w["model.embed_tokens.weight"], cfg["hidden_size"])
+    h = plain.rms_norm(x, w["model.layers.1.input_layernorm.weight"], cfg["rms_norm_eps"])
+    nq, nkv, hd = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
+    pos = list(range(len(ids)))
+    q = plain.rope((h @ w["model.layers.1.self_attn.q_proj.weight"].T).reshape(-1, nq, hd), pos, cfg["rope_theta"])
+    k = plain.rope((h @ w["model.layers.1.self_attn.k_proj.weight"].T).reshape(-1, nkv, hd), pos, cfg["rope_theta"])
+    v = (h @ w["model.layers.1.self_attn.v_proj.weight"].T).reshape(-1, nkv, hd)
+    ctx = plain.attention(q, k, v, cfg["query_pre_attn_scalar"] ** -0.5, cfg["attn_logit_softcapping"], None)
+    a = ctx @ w["model.layers.1.self_attn.o_proj.weight"].T
+    want = x + plain.rms_norm(a, w["model.layers.1.post_attention_layernorm.weight"], cfg["rms_norm_eps"])
+    # layer 1 is a global layer (odd layers see all keys): the block's first half gives the same
+    got = plain.block(x, pos, 1, cfg, w)
+    n2 = plain.rms_norm(want, w["model.layers.1.pre_feedforward_layernorm.weight"], cfg["rms_norm_eps"])
+    f = plain.geglu_mlp(n2, w["model.layers.1.mlp.gate_proj.weight"], w["model.layers.1.mlp.up_proj.weight"],
+                        w["model.layers.1.mlp.down_proj.weight"])
+    want = want + plain.rms_norm(f, w["model.layers.1.post_feedforward_layernorm.weight"], cfg["rms_norm_eps"])
+    assert torch.allclose(got, want, atol=1e-12)
