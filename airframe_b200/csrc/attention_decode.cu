@@ -2,11 +2,18 @@
 // a step of few sequences still fills the GPU (it is bound by the bytes of K
 // and V it reads; every byte is read once).
 //
-// The sequences of a batch may differ much in length: a sequence's keys are cut into as many splits
-// (up to the grid's) as give every block about the same number of pages; blocks beyond a sequence's
-// splits leave at once.
-// Pass 1, grid (sequence, kv head, split): a block of two groups of 4 warps
-// walks its share of the sequence's cache pages, the groups taking alternate
+// How the work is cut.  The grid is one block an SM.  A unit is a (sequence, kv head) pair (a tile of 16
+// heads of it, if the group is larger) with the cache pages its sequence's new token attends to; the pages
+// of all units, divided by the blocks, are a block's share.  Every block works out the cut from the
+// lengths, the same way (da_plan):
+//  * the even cut: every unit into about pages / share splits of equal size, one split a block.  No block
+//    meets the end of a unit; taken when the splits are no more than the blocks and none is more than two
+//    pages above the share (sequences of equal or of mixed lengths, one long one among short ones);
+//  * else the run cut: all units' pages end to end, each block an equal run of them.  A run may end one unit
+//    and begin the next: the block works them as segments, one after the other, and leaves a partial result
+//    for each (many short sequences; more units than blocks).
+// Pass 1: a block of two groups of 4 warps
+// walks its pages, the groups taking alternate
 // pages (one warp per scheduler cannot hide the latency of its own chain of
 // shared-memory loads and mma).  One thread brings the K and V tiles of a page
 // in by TMA (128-byte swizzled boxes, mbarrier-tracked) through a ring of
@@ -93,7 +100,8 @@ __device__ __forceinline__ uint32_t da_pack(float lo, float hi) {
 
 // Pages of the cache that sequence b's new token attends to: [first, last].
 __device__ __forceinline__ int da_pages(const int* slots, const int* lens, int b, int window, int* first_pp, int* last_pp) {
-  const int len = slots[b] >= 0 ? lens[b] : 0;
+  const int slot = slots[b], len_b = lens[b];   // (both loads at once: neither waits for the other)
+  const int len = slot >= 0 ? len_b : 0;
   if (len <= 0) {
     *first_pp = 0;
     *last_pp = -1;
@@ -106,27 +114,6 @@ __device__ __forceinline__ int da_pages(const int* slots, const int* lens, int b
   return *last_pp - *first_pp + 1;
 }
 
-// Into how many splits sequence b's pages are cut (1..max_splits).  The sequences of a batch may differ
-// much in length: every block gets about the same number of pages, total pages / (SMs per row of the
-// grid), so a long sequence among short ones is cut into many splits and the short ones into one,
-// instead of the same number for all.  (The split and the merge kernel compute it alike.)
-__device__ __forceinline__ int da_splits_of(int total, int mine, int rows_of_grid, int n_sms, int max_splits) {
-  const int blocks = max(1, n_sms / max(1, rows_of_grid));       // blocks there are for one kv head of all sequences
-  const int target = max(1, (total + blocks - 1) / blocks);      // pages a block should get
-  return max(1, min(max_splits, (mine + target / 2) / target));
-}
-// The pages of all sequences of the batch, summed by the block's first warp into *total_s (shared memory);
-// the caller synchronises the block before it reads it.
-__device__ __forceinline__ void da_total_pages(const int* slots, const int* lens, int batch, int window, int* total_s) {
-  if (threadIdx.x < 32) {
-    int t = 0, f, l;
-    for (int i = threadIdx.x; i < batch; i += 32) t += da_pages(slots, lens, i, window, &f, &l);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
-    if (threadIdx.x == 0) *total_s = t;
-  }
-}
-
 template <int HD>
 __host__ __device__ constexpr int da_stages() { return HD >= 256 ? 3 : 4; }
 
@@ -136,8 +123,118 @@ __device__ __forceinline__ uint32_t da_piece(uint32_t tile, int r, int c) {
   return tile + (uint32_t)((c >> 3) * 8192 + r * 128 + (((c & 7) ^ (r & 7)) << 4));
 }
 
+
+// ---------------------------------------------------------------- how the work is cut
+
+constexpr int DA_MAX_BATCH = 2048;   // sequences whose page counts a block keeps in shared memory
+
+// The blocks that share the work in the run cut.  A unit of P pages lies in at most P + 1 runs and in at most
+// n_blocks / units_per_seq + 2 (a run is at least total / n_blocks pages, and the unit's sequence alone has
+// units_per_seq * P): if the room for partial results, `room` a unit, is below both, fewer blocks work, so that
+// no unit is cut more often than it has room for.
+__device__ __forceinline__ int da_blocks_used(int n_blocks, int room, int units_per_seq, int most_pages) {
+  if (room >= most_pages + 1 || room >= n_blocks / units_per_seq + 2) return n_blocks;
+  return max(1, min(n_blocks, (room - 2) * units_per_seq));
+}
+
+// Splits of a unit of P pages in the even cut: pages / share, rounded to the nearest (how 1) or down (how 2).
+__device__ __forceinline__ int da_even_splits(int P, int share, int room, int how) {
+  return P > 0 ? max(1, min(room, (P + (how == 1 ? share / 2 : 0)) / share)) : 0;
+}
+
+// What a block loses at the end of a unit inside its run (merging, the next unit's queries, the first page's
+// wait), in pages: the even cut is taken if its largest split is no more than this above the share.
+constexpr int DA_BREAK_PAGES = 2;
+
+struct DaPlan {
+  int share;        // pages a block should get
+  int n_blocks;     // blocks that work in the run cut
+  int even;         // 0: the run cut; else the even cut, and how it rounds (da_even_splits)
+  int pages_before; // pages of the sequences before `b_query` (each counted once, not per unit)
+};
+
+// The plan, by one whole warp (every lane returns the same).  32-bit arithmetic all through: the launcher has
+// checked that batch x pages x units stays below 2^31.  If `pages_s` is given it gets the pages of the sequences
+// before b, and `splits_s` their splits in the even cut (b = 0 .. batch).
+__device__ __forceinline__ DaPlan da_plan(const int* slots, const int* lens, int batch, int window, int units_per_seq,
+                                          int grid_blocks, int room, int b_query, int* pages_s, int* splits_s) {
+  const int lane = threadIdx.x & 31;
+  int carry = 0, most = 0, before = 0, f, l, P_first = 0;
+  if (pages_s && lane == 0) pages_s[0] = 0;
+  for (int base = 0; base < batch; base += 32) {
+    const int i = base + lane;
+    const int P = i < batch ? da_pages(slots, lens, i, window, &f, &l) : 0;
+    if (base == 0) P_first = P;
+    most = max(most, P);
+    if (i < b_query) before += P;
+    int v = P;
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const int up = __shfl_up_sync(0xffffffffu, v, o);
+      if (lane >= o) v += up;
+    }
+    if (pages_s && i < batch) pages_s[i + 1] = carry + v;
+    carry += __shfl_sync(0xffffffffu, v, 31);
+  }
+  most = __reduce_max_sync(0xffffffffu, most);
+  DaPlan pl;
+  pl.pages_before = __reduce_add_sync(0xffffffffu, before);
+  const int total = carry * units_per_seq;
+  pl.n_blocks = da_blocks_used(grid_blocks, room, units_per_seq, most);
+  pl.share = max(1, (total + pl.n_blocks - 1) / pl.n_blocks);
+  // the even cut, rounding either way: how many splits in all, and the most pages of one
+  int items1 = 0, worst1 = 0, items2 = 0, worst2 = 0;
+  for (int base = 0; base < batch; base += 32) {
+    const int i = base + lane;
+    const int P = base == 0 ? P_first : (i < batch ? da_pages(slots, lens, i, window, &f, &l) : 0);
+    const int sp1 = da_even_splits(P, pl.share, room, 1), sp2 = da_even_splits(P, pl.share, room, 2);
+    if (P > 0) {
+      worst1 = max(worst1, (P + sp1 - 1) / sp1);
+      worst2 = max(worst2, (P + sp2 - 1) / sp2);
+    }
+    items1 += sp1;
+    items2 += sp2;
+  }
+  items1 = __reduce_add_sync(0xffffffffu, items1);
+  items2 = __reduce_add_sync(0xffffffffu, items2);
+  worst1 = __reduce_max_sync(0xffffffffu, worst1);
+  worst2 = __reduce_max_sync(0xffffffffu, worst2);
+  const bool fits1 = items1 * units_per_seq <= grid_blocks, fits2 = items2 * units_per_seq <= grid_blocks;
+  int how = 0, worst = 0;
+  if (fits1 && (!fits2 || worst1 <= worst2)) how = 1, worst = worst1;
+  else if (fits2) how = 2, worst = worst2;
+  pl.even = (how != 0 && worst <= pl.share + DA_BREAK_PAGES) ? how : 0;
+  if (splits_s && pl.even) {
+    int items = 0;
+    if (lane == 0) splits_s[0] = 0;
+    for (int base = 0; base < batch; base += 32) {
+      const int i = base + lane;
+      const int P = base == 0 ? P_first : (i < batch ? da_pages(slots, lens, i, window, &f, &l) : 0);
+      int v = da_even_splits(P, pl.share, room, pl.even);
+#pragma unroll
+      for (int o = 1; o < 32; o <<= 1) {
+        const int up = __shfl_up_sync(0xffffffffu, v, o);
+        if (lane >= o) v += up;
+      }
+      if (i < batch) splits_s[i + 1] = items + v;
+      items += __shfl_sync(0xffffffffu, v, 31);
+    }
+  }
+  return pl;
+}
+
+// The largest b in [0, n) with arr[b] * scale <= x (arr ascends, arr[0] = 0).
+__device__ __forceinline__ int da_find(const int* arr, int n, int scale, int x) {
+  int lo = 0, hi = n - 1;
+  while (lo < hi) {
+    const int mid = (lo + hi + 1) >> 1;
+    if (arr[mid] * scale <= x) lo = mid; else hi = mid - 1;
+  }
+  return lo;
+}
+
 // The heads of one kv group are the (up to 16) rows of an m16n8k16 tile; the
-// four warps of a block share each page's 64 keys, 16 keys a warp.
+// four warps of a group share each page's 64 keys, 16 keys a warp.
 template <int HD>
 __global__ void __launch_bounds__(DA_THREADS, 1)
 attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v,
@@ -151,21 +248,19 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
   extern __shared__ unsigned char da_smem_raw[];
   unsigned char* da_smem = (unsigned char*)(((uintptr_t)da_smem_raw + 1023) & ~(uintptr_t)1023);
   __shared__ float m_s[DA_WARPS * 16], l_s[DA_WARPS * 16];
-  // a barrier per page modulo 2 * STAGES: the two groups run ahead of one another, and a page and the
-  // page STAGES later (the other group's, in the same stage) must not share a barrier's phases
+  // a stage's two uses in a row (a page and the page STAGES later, the other group's) must not share a
+  // barrier's phases
   constexpr int NBAR = 2 * STAGES;
   __shared__ uint64_t full[NBAR];
-  __shared__ int give_up_s, total_pages_s;
+  __shared__ int give_up_s;
+  __shared__ int pages_s[DA_MAX_BATCH + 1], splits_s[DA_MAX_BATCH + 1];
+  __shared__ DaPlan plan_s;
   volatile int* give_up = &give_up_s;
 
   pdl_launch_dependents();
-  const int b = blockIdx.x;
   const int group = a.nq / a.nkv;
   const int tiles = (group + 15) / 16;
-  const int kvh = blockIdx.y / tiles;
-  const int row_head0 = kvh * group + (blockIdx.y % tiles) * 16;        // head of tile row 0
-  const int n_rows = min(16, kvh * group + group - row_head0);           // heads in this tile
-  const int z = blockIdx.z;
+  const int units_per_seq = a.nkv * tiles;
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const int grp = warp >> 2, wq = warp & 3;   // warp group; this warp's quarter of a page's keys
   const int g = lane >> 2, t = lane & 3;
@@ -174,39 +269,71 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     give_up_s = 0;
     mbar_fence_init();
   }
-  const int slot = a.slots[b];
-  const int len = slot >= 0 ? a.lens[b] : 0;
-  const int pos = len - 1;
-  const int lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
-
-  int pp_begin = 0, pp_end = 0, first_pp, last_pp;  // last_pp: the page of the new token, which the kernel before wrote
-  const int my_pages = da_pages(a.slots, a.lens, b, a.window, &first_pp, &last_pp);
-  int splits = 1;
-  if (a.n_splits > 1) {
-    da_total_pages(a.slots, a.lens, a.batch, a.window, &total_pages_s);
-    __syncthreads();
-    splits = da_splits_of(total_pages_s, my_pages, gridDim.y, a.n_sms, a.n_splits);
+  // (slots and lengths are inputs of the step, not results of the kernel in front)
+  if (warp == 0) {
+    const DaPlan pl = da_plan(a.slots, a.lens, a.batch, a.window, units_per_seq, (int)gridDim.x, a.n_splits, 0,
+                              pages_s, splits_s);
+    if (lane == 0) plan_s = pl;
   }
-  if (z >= splits) return;                          // (nothing of the block's is in flight yet)
-  if (len > 0) {
-    const int n_pp = last_pp - first_pp + 1;
-    const int per = (n_pp + splits - 1) / splits;
-    pp_begin = first_pp + z * per;
-    pp_end = min(pp_begin + per, last_pp + 1);
-  }
-  const int n_pages = max(pp_end - pp_begin, 0);
-  const int ring_pages = a.ring_rows / AF_PAGE;
-  const int* pt = a.page_table + (size_t)max(slot, 0) * a.max_pages;
   __syncthreads();
+  const int share = plan_s.share;
+  const bool even = plan_s.even != 0;
+  const int total = pages_s[a.batch] * units_per_seq;
+  // the run cut: pages [gpos, gend) of all units' pages end to end
+  int gpos = 0, gend = 0;
+  if (even) {
+    if ((int)blockIdx.x >= splits_s[a.batch] * units_per_seq) return;   // (nothing of the block's is in flight yet)
+  } else {
+    gpos = (int)blockIdx.x * share;
+    gend = min(total, gpos + share);
+    if ((int)blockIdx.x >= plan_s.n_blocks || gpos >= gend) return;
+  }
+  const int ring_pages = a.ring_rows / AF_PAGE;
+  const float cs = a.cap > 0.f ? a.scale / a.cap : a.scale * LOG2E;
+  const float cap2 = a.cap * LOG2E;
 
-  auto issue = [&](int i) {  // page i of this block's share into stage i % STAGES
-    const int pp = pp_begin + i;
+  // A segment: some of the pages of one unit.
+  struct Segment {
+    int b, kvh, row_head0, n_rows, z, n_pages, pp_begin, last_pp, lo, pos;
+    const int* pt;
+  };
+  auto of_unit = [&](Segment& sg, int b, int y, int p_in) {
+    sg.b = b;
+    sg.kvh = y / tiles;
+    sg.row_head0 = sg.kvh * group + (y % tiles) * 16;             // head of tile row 0
+    sg.n_rows = min(16, sg.kvh * group + group - sg.row_head0);    // heads in this tile
+    sg.pos = a.lens[b] - 1;                                        // (length > 0: the sequence has pages)
+    sg.lo = a.window > 0 ? max(0, sg.pos - a.window + 1) : 0;
+    sg.last_pp = sg.pos / AF_PAGE;     // the page of the new token, which the kernel in front wrote
+    sg.pp_begin = sg.lo / AF_PAGE + p_in;
+    sg.pt = a.page_table + (size_t)a.slots[b] * a.max_pages;
+  };
+  // the run cut's segment that begins at page `at` of the run
+  auto locate = [&](int at, bool first) {
+    Segment sg;
+    const int b = da_find(pages_s, a.batch, units_per_seq, at);
+    const int P = pages_s[b + 1] - pages_s[b];
+    const int seq0 = pages_s[b] * units_per_seq;
+    const int y = (at - seq0) / P, p_in = (at - seq0) - y * P;
+    sg.n_pages = min(P - p_in, gend - at);
+    // which of the unit's splits this is: the block's first segment may begin inside a unit, the later ones begin one
+    sg.z = first ? (int)blockIdx.x - (seq0 + y * P) / share : 0;
+    of_unit(sg, b, y, p_in);
+    return sg;
+  };
+  // the cache page that holds page i of segment sg (a load from the page table: asked for ahead of its use)
+  auto page_id = [&](const Segment& sg, int i) {
+    const int pp = sg.pp_begin + i;
     const int entry = ring_pages > 0 ? pp % ring_pages : pp;
-    int page = AF_INDEX_OK(entry < a.max_pages, entry) ? pt[entry] : 0;
-    if (!AF_INDEX_OK(page >= 0, page)) page = 0;     // (the copy must still be made: the stage's barrier expects its bytes)
+    int page = AF_INDEX_OK(entry < a.max_pages, entry) ? sg.pt[entry] : 0;
+    if (!AF_INDEX_OK(page >= 0, page)) page = 0;   // (the copy must still be made: the stage's barrier expects its bytes)
+    return page;
+  };
+  // cache page `page` of kv head kvh, the block's page number ii, into stage ii % STAGES
+  auto issue = [&](int kvh, int page, int ii) {
     const int row = (page * a.nkv + kvh) * AF_PAGE;
-    unsigned char* st = da_smem + (size_t)(i % STAGES) * 2 * TILE_BYTES;
-    uint64_t* bar = &full[i % NBAR];
+    unsigned char* st = da_smem + (size_t)(ii % STAGES) * 2 * TILE_BYTES;
+    uint64_t* bar = &full[ii % NBAR];
     mbar_expect_tx(bar, 2 * TILE_BYTES);
 #pragma unroll
     for (int c = 0; c < HD / 64; ++c) {
@@ -214,217 +341,289 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
       tma_load_2d(st + TILE_BYTES + c * 8192, &map_v, c * 64, row, bar);
     }
   };
-  int issued = 0;
-  if (tid == 0)
-    for (; issued < STAGES && issued < n_pages && pp_begin + issued != last_pp; ++issued) issue(issued);
-  pdl_wait();
-  if (tid == 0)
-    for (; issued < STAGES && issued < n_pages; ++issued) issue(issued);
+  // the first pages of a segment: their page ids are loaded together, then the copies go out
+  auto issue_first = [&](const Segment& sg, int from, int to, int ii0, bool skip_last) {
+    int ids[STAGES];
+#pragma unroll
+    for (int i = 0; i < STAGES; ++i) ids[i] = (i >= from && i < to) ? page_id(sg, i) : 0;
+    int i = from;
+#pragma unroll
+    for (int k = 0; k < STAGES; ++k)
+      if (k == i && k < to && !(skip_last && sg.pp_begin + k == sg.last_pp)) {
+        issue(sg.kvh, ids[k], ii0 + k);
+        ++i;
+      }
+    return i;
+  };
 
-  // the query heads as A fragments: rows g and g + 8 of the tile
-  uint32_t qf[KSTEPS][4];
-  {
-    const __nv_bfloat16* q0 = a.q + (size_t)b * a.q_stride + (size_t)(row_head0 + g) * HD;
-    const __nv_bfloat16* q1 = q0 + (size_t)8 * HD;
-    const bool on0 = len > 0 && g < n_rows, on1 = len > 0 && g + 8 < n_rows;
-#pragma unroll
-    for (int ks = 0; ks < KSTEPS; ++ks) {
-      const int d = ks * 16 + 2 * t;
-      qf[ks][0] = on0 ? *reinterpret_cast<const uint32_t*>(q0 + d) : 0u;
-      qf[ks][1] = on1 ? *reinterpret_cast<const uint32_t*>(q1 + d) : 0u;
-      qf[ks][2] = on0 ? *reinterpret_cast<const uint32_t*>(q0 + d + 8) : 0u;
-      qf[ks][3] = on1 ? *reinterpret_cast<const uint32_t*>(q1 + d + 8) : 0u;
-    }
+  int i_base = 0;          // pages this block has worked before the segment: barriers and stages count on
+  Segment sg;
+  if (even) {
+    // split z of unit y of sequence b, one of da_even_splits(...) equal parts of its pages
+    const int w = (int)blockIdx.x;
+    const int b = da_find(splits_s, a.batch, units_per_seq, w);
+    const int sp = splits_s[b + 1] - splits_s[b], P = pages_s[b + 1] - pages_s[b];
+    const int r = w - splits_s[b] * units_per_seq;
+    const int y = r / sp;
+    const int per = (P + sp - 1) / sp;
+    sg.z = r - y * sp;
+    sg.n_pages = max(0, min(per, P - sg.z * per));     // (0: the unit has fewer pages than splits; an empty partial result)
+    of_unit(sg, b, y, sg.z * per);
+  } else {
+    sg = locate(gpos, true);
   }
-  float o[ONT][4];
+  int issued = 0;          // pages of the segment that are on their way already
+  // the cache rows of earlier tokens do not depend on the kernel in front: the first pages are on their way
+  // before the wait for it; only the page that holds the new token waits
+  if (tid == 0) issued = issue_first(sg, 0, min(STAGES, sg.n_pages), 0, true);
+  pdl_wait();
+  while (true) {
+    const int b = sg.b, n_pages = sg.n_pages, n_rows = sg.n_rows, row_head0 = sg.row_head0, z = sg.z;
+    const int pp_begin = sg.pp_begin, lo = sg.lo, pos = sg.pos;
+    if (tid == 0) issued = issue_first(sg, issued, min(STAGES, n_pages), i_base, false);
+
+    // the query heads as A fragments: rows g and g + 8 of the tile
+    uint32_t qf[KSTEPS][4];
+    {
+      const __nv_bfloat16* q0 = a.q + (size_t)b * a.q_stride + (size_t)(row_head0 + g) * HD;
+      const __nv_bfloat16* q1 = q0 + (size_t)8 * HD;
+      const bool on0 = g < n_rows, on1 = g + 8 < n_rows;
 #pragma unroll
-  for (int n = 0; n < ONT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
-  float mx[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f};
-  const float cs = a.cap > 0.f ? a.scale / a.cap : a.scale * LOG2E;
-  const float cap2 = a.cap * LOG2E;
-  for (int i = grp; i < n_pages; i += DA_GROUPS) {
-    const int s = i % STAGES;
-    const int ok = mbar_wait(&full[i % NBAR], (i / NBAR) & 1, give_up) ? 1 : 0;
-    // the four warps of the group go on or give up together
-    int all_ok;
-    asm volatile(
-        "{\n\t.reg .pred p, q;\n\t"
-        "setp.ne.b32 q, %1, 0;\n\t"
-        "barrier.red.and.pred.aligned p, %2, 128, q;\n\t"
-        "selp.u32 %0, 1, 0, p;\n\t}"
-        : "=r"(all_ok)
-        : "r"(ok), "r"(1 + grp)
-        : "memory");
-    if (!all_ok) break;
-    const uint32_t k_t = smem_u32(da_smem + (size_t)s * 2 * TILE_BYTES);
-    const uint32_t v_t = k_t + TILE_BYTES;
-    // ---- S = Q K^T for this warp's 16 keys
-    // (SCH chains of accumulators: an mma waits for the one before it on the same accumulator)
-    float scp[SCH][2][4];
-#pragma unroll
-    for (int c = 0; c < SCH; ++c)
-#pragma unroll
-      for (int n = 0; n < 2; ++n) scp[c][n][0] = scp[c][n][1] = scp[c][n][2] = scp[c][n][3] = 0.f;
-#pragma unroll
-    for (int ks = 0; ks < KSTEPS; ++ks) {
-      uint32_t b0, b1, b2, b3;
-      da_ldm4(da_piece(k_t, wq * 16 + (lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
-      da_mma(scp[ks % SCH][0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
-      da_mma(scp[ks % SCH][1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
-    }
-    float sc[2][4];
-#pragma unroll
-    for (int n = 0; n < 2; ++n)
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        float v = scp[0][n][e];
-#pragma unroll
-        for (int c = 1; c < SCH; ++c) v += scp[c][n][e];
-        sc[n][e] = v;
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        const int d = ks * 16 + 2 * t;
+        qf[ks][0] = on0 ? *reinterpret_cast<const uint32_t*>(q0 + d) : 0u;
+        qf[ks][1] = on1 ? *reinterpret_cast<const uint32_t*>(q1 + d) : 0u;
+        qf[ks][2] = on0 ? *reinterpret_cast<const uint32_t*>(q0 + d + 8) : 0u;
+        qf[ks][3] = on1 ? *reinterpret_cast<const uint32_t*>(q1 + d + 8) : 0u;
       }
-    // ---- scale, softcap, mask, online softmax (base 2)
-    const int j0 = (pp_begin + i) * AF_PAGE + wq * 16;
-    float new_max[2] = {mx[0], mx[1]};
-    // (the test on the cap stands outside the loops: inside it stays a branch per score)
-    if (a.cap > 0.f) {
+    }
+    float o[ONT][4];
+#pragma unroll
+    for (int n = 0; n < ONT; ++n) o[n][0] = o[n][1] = o[n][2] = o[n][3] = 0.f;
+    float mx[2] = {-INFINITY, -INFINITY}, sum[2] = {0.f, 0.f};
+    // group `grp` takes the pages whose count since the block began is grp modulo 2
+    for (int i = (grp - i_base) & 1; i < n_pages; i += DA_GROUPS) {
+      const int ii = i_base + i;
+      const int s = ii % STAGES;
+      // (the group's first thread refills the stage when the group is done with it: the page's id is asked for now)
+      const bool refill = (tid & 127) == 0 && i + STAGES < n_pages;
+      const int refill_page = refill ? page_id(sg, i + STAGES) : 0;
+      const int ok = mbar_wait(&full[ii % NBAR], (ii / NBAR) & 1, give_up) ? 1 : 0;
+      // the four warps of the group go on or give up together
+      int all_ok;
+      asm volatile(
+          "{\n\t.reg .pred p, q;\n\t"
+          "setp.ne.b32 q, %1, 0;\n\t"
+          "barrier.red.and.pred.aligned p, %2, 128, q;\n\t"
+          "selp.u32 %0, 1, 0, p;\n\t}"
+          : "=r"(all_ok)
+          : "r"(ok), "r"(1 + grp)
+          : "memory");
+      if (!all_ok) break;
+      const uint32_t k_t = smem_u32(da_smem + (size_t)s * 2 * TILE_BYTES);
+      const uint32_t v_t = k_t + TILE_BYTES;
+      // ---- S = Q K^T for this warp's 16 keys
+      float scp[SCH][2][4];
+#pragma unroll
+      for (int c = 0; c < SCH; ++c)
+#pragma unroll
+        for (int n = 0; n < 2; ++n) scp[c][n][0] = scp[c][n][1] = scp[c][n][2] = scp[c][n][3] = 0.f;
+#pragma unroll
+      for (int ks = 0; ks < KSTEPS; ++ks) {
+        uint32_t b0, b1, b2, b3;
+        da_ldm4(da_piece(k_t, wq * 16 + (lane & 7) + (lane >> 4) * 8, ks * 2 + ((lane >> 3) & 1)), b0, b1, b2, b3);
+        da_mma(scp[ks % SCH][0], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b0, b1);
+        da_mma(scp[ks % SCH][1], qf[ks][0], qf[ks][1], qf[ks][2], qf[ks][3], b2, b3);
+      }
+      float sc[2][4];
 #pragma unroll
       for (int n = 0; n < 2; ++n)
 #pragma unroll
-        for (int e = 0; e < 4; ++e) sc[n][e] = cap2 * fast_tanh(sc[n][e] * cs);
-    } else {
+        for (int e = 0; e < 4; ++e) {
+          float v = scp[0][n][e];
 #pragma unroll
-      for (int n = 0; n < 2; ++n)
+          for (int c = 1; c < SCH; ++c) v += scp[c][n][e];
+          sc[n][e] = v;
+        }
+      // ---- scale, softcap, mask, online softmax (base 2)
+      const int j0 = (pp_begin + i) * AF_PAGE + wq * 16;
+      float new_max[2] = {mx[0], mx[1]};
+      if (a.cap > 0.f) {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) sc[n][e] *= cs;
-    }
+        for (int n = 0; n < 2; ++n)
 #pragma unroll
-    for (int n = 0; n < 2; ++n) {
+          for (int e = 0; e < 4; ++e) sc[n][e] = cap2 * fast_tanh(sc[n][e] * cs);
+      } else {
 #pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const int j = j0 + n * 8 + 2 * t + (e & 1);
-        const float v = (j >= lo && j <= pos) ? sc[n][e] : -INFINITY;
-        sc[n][e] = v;
-        new_max[e >> 1] = fmaxf(new_max[e >> 1], v);
+        for (int n = 0; n < 2; ++n)
+#pragma unroll
+          for (int e = 0; e < 4; ++e) sc[n][e] *= cs;
       }
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int j = j0 + n * 8 + 2 * t + (e & 1);
+          const float v = (j >= lo && j <= pos) ? sc[n][e] : -INFINITY;
+          sc[n][e] = v;
+          new_max[e >> 1] = fmaxf(new_max[e >> 1], v);
+        }
+      }
+      float corr[2], ref[2];
+#pragma unroll
+      for (int r = 0; r < 2; ++r) {
+        new_max[r] = fmaxf(new_max[r], __shfl_xor_sync(0xffffffffu, new_max[r], 1));
+        new_max[r] = fmaxf(new_max[r], __shfl_xor_sync(0xffffffffu, new_max[r], 2));
+        ref[r] = new_max[r] == -INFINITY ? 0.f : new_max[r];
+        corr[r] = fast_exp2(mx[r] - ref[r]);
+        mx[r] = new_max[r];
+        sum[r] *= corr[r];
+      }
+#pragma unroll
+      for (int n = 0; n < 2; ++n) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const float p = fast_exp2(sc[n][e] - ref[e >> 1]);
+          sc[n][e] = p;
+          sum[e >> 1] += p;
+        }
+      }
+      if (corr[0] != 1.f || corr[1] != 1.f) {
+#pragma unroll
+        for (int n = 0; n < ONT; ++n) {
+          o[n][0] *= corr[0];
+          o[n][1] *= corr[0];
+          o[n][2] *= corr[1];
+          o[n][3] *= corr[1];
+        }
+      }
+      // ---- O += P V over this warp's 16 keys
+      {
+        const uint32_t a0 = da_pack(sc[0][0], sc[0][1]), a1 = da_pack(sc[0][2], sc[0][3]);
+        const uint32_t a2 = da_pack(sc[1][0], sc[1][1]), a3 = da_pack(sc[1][2], sc[1][3]);
+#pragma unroll
+        for (int np = 0; np < ONT / 2; ++np) {
+          uint32_t b0, b1, b2, b3;
+          da_ldm4t(da_piece(v_t, wq * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, np * 2 + (lane >> 4)), b0, b1, b2, b3);
+          da_mma(o[2 * np], a0, a1, a2, a3, b0, b1);
+          da_mma(o[2 * np + 1], a0, a1, a2, a3, b2, b3);
+        }
+      }
+      // the group is done with the stage (a barrier of its own four warps): its first thread refills it
+      asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory");
+      if (refill && !*give_up) issue(sg.kvh, refill_page, ii + STAGES);
     }
-    float corr[2], ref[2];
+    if (*give_up && tid == 0) grace_period();
+    __syncthreads();
+    const bool gave_up = *give_up != 0;      // (the same for all threads: nobody waits on a barrier any more)
+
+    // ---- merge the eight warps (each saw a part of the keys); a stage is the buffer.  Where the buffer fits one
+    // stage (up to 8 heads in the tile), the next segment's first pages go into the other stages before the
+    // merge, so that the block's stream of pages does not stop at a unit's end.
+    i_base += n_pages;
+    gpos += n_pages;
+    const bool more = gpos < gend && !gave_up;       // (the even cut: one segment; gend is 0)
+    Segment nx = sg;
+    issued = 0;
+    if (more) {
+      nx = locate(gpos, false);
+      if (tid == 0 && n_rows <= 8) issued = issue_first(nx, 0, min(STAGES - 1, nx.n_pages), i_base, false);
+    }
+    // [warp][rows of real heads][HD], in the stage that the next pages reach last (thread 0 alone issues on)
+    float* o_s = reinterpret_cast<float*>(da_smem + (n_rows <= 8 ? (size_t)((i_base + STAGES - 1) % STAGES) * 2 * TILE_BYTES : 0));
 #pragma unroll
     for (int r = 0; r < 2; ++r) {
-      new_max[r] = fmaxf(new_max[r], __shfl_xor_sync(0xffffffffu, new_max[r], 1));
-      new_max[r] = fmaxf(new_max[r], __shfl_xor_sync(0xffffffffu, new_max[r], 2));
-      ref[r] = new_max[r] == -INFINITY ? 0.f : new_max[r];
-      corr[r] = fast_exp2(mx[r] - ref[r]);
-      mx[r] = new_max[r];
-      sum[r] *= corr[r];
-    }
+      sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
+      sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
+      const int row = g + 8 * r;
+      if (t == 0) {
+        m_s[warp * 16 + row] = mx[r];
+        l_s[warp * 16 + row] = sum[r];
+      }
+      if (row < n_rows) {
 #pragma unroll
-    for (int n = 0; n < 2; ++n) {
-#pragma unroll
-      for (int e = 0; e < 4; ++e) {
-        const float p = fast_exp2(sc[n][e] - ref[e >> 1]);
-        sc[n][e] = p;
-        sum[e >> 1] += p;
+        for (int n = 0; n < ONT; ++n) {
+          float* dst = o_s + ((size_t)(warp * n_rows + row)) * HD + n * 8 + 2 * t;
+          dst[0] = o[n][2 * r];
+          dst[1] = o[n][2 * r + 1];
+        }
       }
     }
-    if (corr[0] != 1.f || corr[1] != 1.f) {
+    __syncthreads();
+    for (int i = tid; i < n_rows * HD; i += DA_THREADS) {
+      const int row = i / HD, d = i - row * HD;
+      float M = -INFINITY;
 #pragma unroll
-      for (int n = 0; n < ONT; ++n) {
-        o[n][0] *= corr[0];
-        o[n][1] *= corr[0];
-        o[n][2] *= corr[1];
-        o[n][3] *= corr[1];
+      for (int w = 0; w < DA_WARPS; ++w) M = fmaxf(M, m_s[w * 16 + row]);
+      const float ref = M == -INFINITY ? 0.f : M;
+      float L = 0.f, O = 0.f;
+#pragma unroll
+      for (int w = 0; w < DA_WARPS; ++w) {
+        const float f = fast_exp2(m_s[w * 16 + row] - ref);
+        L += l_s[w * 16 + row] * f;
+        O += o_s[((size_t)(w * n_rows + row)) * HD + d] * f;
+      }
+      const size_t pidx = ((size_t)b * a.nq + row_head0 + row) * a.n_splits + z;
+      a.part_o[pidx * HD + d] = O;
+      if (d == 0) {
+        a.part_ml[pidx * 2] = M;
+        a.part_ml[pidx * 2 + 1] = L;
       }
     }
-    // ---- O += P V over this warp's 16 keys
-    {
-      const uint32_t a0 = da_pack(sc[0][0], sc[0][1]), a1 = da_pack(sc[0][2], sc[0][3]);
-      const uint32_t a2 = da_pack(sc[1][0], sc[1][1]), a3 = da_pack(sc[1][2], sc[1][3]);
-#pragma unroll
-      for (int np = 0; np < ONT / 2; ++np) {
-        uint32_t b0, b1, b2, b3;
-        da_ldm4t(da_piece(v_t, wq * 16 + (lane & 7) + ((lane >> 3) & 1) * 8, np * 2 + (lane >> 4)), b0, b1, b2, b3);
-        da_mma(o[2 * np], a0, a1, a2, a3, b0, b1);
-        da_mma(o[2 * np + 1], a0, a1, a2, a3, b2, b3);
-      }
-    }
-    // the group is done with stage s (a barrier of its own four warps): its first thread refills it
-    asm volatile("bar.sync %0, 128;" ::"r"(1 + grp) : "memory");
-    if ((tid & 127) == 0 && i + STAGES < n_pages && !*give_up) issue(i + STAGES);
-  }
-  if (*give_up && tid == 0) grace_period();
-  __syncthreads();
-
-  // ---- merge the four warps (each saw a quarter of the keys); the stage memory is the buffer
-  float* o_s = reinterpret_cast<float*>(da_smem);  // [warp][rows of real heads][HD]
-#pragma unroll
-  for (int r = 0; r < 2; ++r) {
-    sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 1);
-    sum[r] += __shfl_xor_sync(0xffffffffu, sum[r], 2);
-    const int row = g + 8 * r;
-    if (t == 0) {
-      m_s[warp * 16 + row] = mx[r];
-      l_s[warp * 16 + row] = sum[r];
-    }
-    if (row < n_rows) {
-#pragma unroll
-      for (int n = 0; n < ONT; ++n) {
-        float* dst = o_s + ((size_t)(warp * n_rows + row)) * HD + n * 8 + 2 * t;
-        dst[0] = o[n][2 * r];
-        dst[1] = o[n][2 * r + 1];
-      }
-    }
-  }
-  __syncthreads();
-  for (int i = tid; i < n_rows * HD; i += DA_THREADS) {
-    const int row = i / HD, d = i - row * HD;
-    float M = -INFINITY;
-#pragma unroll
-    for (int w = 0; w < DA_WARPS; ++w) M = fmaxf(M, m_s[w * 16 + row]);
-    const float ref = M == -INFINITY ? 0.f : M;
-    float L = 0.f, O = 0.f;
-#pragma unroll
-    for (int w = 0; w < DA_WARPS; ++w) {
-      const float f = fast_exp2(m_s[w * 16 + row] - ref);
-      L += l_s[w * 16 + row] * f;
-      O += o_s[((size_t)(w * n_rows + row)) * HD + d] * f;
-    }
-    const size_t pidx = ((size_t)b * a.nq + row_head0 + row) * a.n_splits + z;
-    a.part_o[pidx * HD + d] = O;
-    if (d == 0) {
-      a.part_ml[pidx * 2] = M;
-      a.part_ml[pidx * 2 + 1] = L;
-    }
+    if (!more) break;
+    __syncthreads();       // (the buffer is one of the next segment's stages)
+    sg = nx;
   }
   if (tid == 0 && give_up_s && a.err) atomicExch(a.err, 1);
 }
 
+// ---------------------------------------------------------------- pass 2
+
+constexpr int DA_MERGE_FEW = 8;        // up to this many splits: 128 threads, every load at once
+constexpr int DA_MERGE_THREADS = 512;  // more, and few (sequence, head) pairs: groups of threads take the splits in turn
+constexpr int DA_MERGE_MOST = 512;     // splits whose (max, sum) the block keeps in shared memory
+
+// Merges the splits of (sequence, head), cut as the split kernel cut them (da_plan with that kernel's grid).
 template <int HD>
 __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long long out_stride,
                                          const float* __restrict__ part_o, const float* __restrict__ part_ml,
-                                         int nq, int max_splits, const int* __restrict__ slots,
-                                         const int* __restrict__ lens, int window, int rows_of_grid, int n_sms) {
+                                         int nq, int nkv, int max_splits, const int* __restrict__ slots,
+                                         const int* __restrict__ lens, int window, int grid_blocks) {
   pdl_launch_dependents();
-  const int b = blockIdx.x, h = blockIdx.y;
+  const int b = blockIdx.x, h = blockIdx.y, batch = gridDim.x;
   const size_t p0 = ((size_t)b * nq + h) * max_splits;
-  // (slots and lengths are inputs of the step: the number of splits is worked out before the wait)
-  __shared__ int total_pages_s;
-  int first_pp, last_pp, n_splits = 1;
-  if (max_splits > 1) {
-    const int my_pages = da_pages(slots, lens, b, window, &first_pp, &last_pp);
-    da_total_pages(slots, lens, gridDim.x, window, &total_pages_s);
-    __syncthreads();
-    n_splits = da_splits_of(total_pages_s, my_pages, rows_of_grid, n_sms, max_splits);
+  __shared__ DaPlan plan_s;
+  __shared__ float m_sh[DA_MERGE_MOST], l_sh[DA_MERGE_MOST];
+  __shared__ float red_s[DA_MERGE_THREADS * 2];
+  const int group = nq / nkv, tiles = (group + 15) / 16, units_per_seq = nkv * tiles;
+  // (slots and lengths are inputs of the step: the cut is worked out before the wait)
+  if (threadIdx.x < 32) {
+    const DaPlan pl = da_plan(slots, lens, batch, window, units_per_seq, grid_blocks, max_splits, b, nullptr, nullptr);
+    if (threadIdx.x == 0) plan_s = pl;
+  }
+  __syncthreads();
+  int first_pp, last_pp;
+  const int P = da_pages(slots, lens, b, window, &first_pp, &last_pp);
+  int n_splits;
+  if (plan_s.even) {
+    n_splits = da_even_splits(P, plan_s.share, max_splits, plan_s.even);
+  } else {
+    const int y = (h / group) * tiles + (h % group) / 16;
+    const int unit0 = plan_s.pages_before * units_per_seq + y * P;
+    n_splits = P > 0 ? (unit0 + P - 1) / plan_s.share - unit0 / plan_s.share + 1 : 0;
   }
   pdl_wait();
   // (the number of splits is known before the wait and the loads below depend on nothing else: without
   // this the compiler may move them, through the const __restrict__ pointers, above the wait)
   part_o = pdl_fresh(part_o);
   part_ml = pdl_fresh(part_ml);
-  constexpr int FEW = 8;
-  const int d = threadIdx.x;   // HD >= 128: threads 0..127 take d and d + 128 (HD 256)
-  if (n_splits <= FEW) {
+  __nv_bfloat16* dst = out + (size_t)b * out_stride + (size_t)h * HD;
+  if (n_splits <= DA_MERGE_FEW) {
     // few splits: every load (outputs, maxima, sums) is issued before the first use, one round trip
+    constexpr int FEW = DA_MERGE_FEW;
     constexpr int PER = HD > 128 ? HD / 128 : 1;
+    const int d = threadIdx.x;   // HD >= 128: threads 0..127 take d and d + 128 (HD 256)
+    if (d >= 128 || d >= HD) return;
     float o[FEW][PER], m[FEW], l[FEW];
 #pragma unroll
     for (int s = 0; s < FEW; ++s) {
@@ -432,7 +631,7 @@ __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long l
       m[s] = on ? part_ml[(p0 + s) * 2] : -INFINITY;
       l[s] = on ? part_ml[(p0 + s) * 2 + 1] : 0.f;
 #pragma unroll
-      for (int e = 0; e < PER; ++e) o[s][e] = on && d + e * 128 < HD ? part_o[(p0 + s) * HD + d + e * 128] : 0.f;
+      for (int e = 0; e < PER; ++e) o[s][e] = on ? part_o[(p0 + s) * HD + d + e * 128] : 0.f;
     }
     float M = -INFINITY;
 #pragma unroll
@@ -450,10 +649,72 @@ __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long l
     }
     const float inv = L > 0.f ? 1.f / L : 0.f;
 #pragma unroll
-    for (int e = 0; e < PER; ++e)
-      if (d + e * 128 < HD) out[(size_t)b * out_stride + (size_t)h * HD + d + e * 128] = __float2bfloat16_rn(O[e] * inv);
+    for (int e = 0; e < PER; ++e) dst[d + e * 128] = __float2bfloat16_rn(O[e] * inv);
     return;
   }
+  if (n_splits <= DA_MERGE_MOST && blockDim.x % (HD / 2) == 0) {
+    // many splits, three round trips: (max, sum) of every split at once; the outputs, the splits dealt to
+    // groups of HD / 2 threads (two dims a thread), eight loads in flight each; the groups' sums through shared memory
+    const int tid = threadIdx.x;
+    for (int s = tid; s < n_splits; s += (int)blockDim.x) {
+      const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (p0 + s) * 2));
+      m_sh[s] = ml.x;
+      l_sh[s] = ml.y;
+    }
+    __syncthreads();
+    float M = -INFINITY;
+    for (int s = tid & 31; s < n_splits; s += 32) M = fmaxf(M, m_sh[s]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    const float ref = M == -INFINITY ? 0.f : M;
+    float L = 0.f;
+    for (int s = tid & 31; s < n_splits; s += 32) L += l_sh[s] * fast_exp2(m_sh[s] - ref);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) L += __shfl_xor_sync(0xffffffffu, L, o);
+    constexpr int ROW = HD / 2;                       // threads of a group
+    const int GROUPS = (int)blockDim.x / ROW;         // (1 .. 16)
+    const int grp = tid / ROW, dp = tid - grp * ROW;
+    float2 acc = make_float2(0.f, 0.f);
+    int s = grp;
+    for (; s + 7 * GROUPS < n_splits; s += 8 * GROUPS) {
+      float2 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u) v[u] = __ldcg(reinterpret_cast<const float2*>(part_o + (p0 + s + u * GROUPS) * HD) + dp);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float f = fast_exp2(m_sh[s + u * GROUPS] - ref);
+        acc.x += v[u].x * f;
+        acc.y += v[u].y * f;
+      }
+    }
+    {
+      float2 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        v[u] = s + u * GROUPS < n_splits ? __ldcg(reinterpret_cast<const float2*>(part_o + (p0 + s + u * GROUPS) * HD) + dp)
+                                         : make_float2(0.f, 0.f);
+#pragma unroll
+      for (int u = 0; u < 8; ++u) {
+        const float f = s + u * GROUPS < n_splits ? fast_exp2(m_sh[s + u * GROUPS] - ref) : 0.f;
+        acc.x += v[u].x * f;
+        acc.y += v[u].y * f;
+      }
+    }
+    red_s[tid * 2] = acc.x;
+    red_s[tid * 2 + 1] = acc.y;
+    __syncthreads();
+    if (tid < ROW) {
+      float2 O = make_float2(0.f, 0.f);
+      for (int gq = 0; gq < GROUPS; ++gq) {
+        O.x += red_s[(gq * ROW + tid) * 2];
+        O.y += red_s[(gq * ROW + tid) * 2 + 1];
+      }
+      const float inv = L > 0.f ? 1.f / L : 0.f;
+      *reinterpret_cast<__nv_bfloat162*>(dst + 2 * tid) = __floats2bfloat162_rn(O.x * inv, O.y * inv);
+    }
+    return;
+  }
+  // (more splits than the block keeps: one after the other)
   float M = -INFINITY;
   for (int s = 0; s < n_splits; ++s) M = fmaxf(M, part_ml[(p0 + s) * 2]);
   const float ref = M == -INFINITY ? 0.f : M;
@@ -463,7 +724,7 @@ __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long l
   for (int dd = threadIdx.x; dd < HD; dd += blockDim.x) {
     float O = 0.f;
     for (int s = 0; s < n_splits; ++s) O += part_o[(p0 + s) * HD + dd] * fast_exp2(part_ml[(p0 + s) * 2] - ref);
-    out[(size_t)b * out_stride + (size_t)h * HD + dd] = __float2bfloat16_rn(O * inv);
+    dst[dd] = __float2bfloat16_rn(O * inv);
   }
 }
 
@@ -489,12 +750,21 @@ int launch_decode(DecodeArgs a, int batch, long long n_pages, cudaStream_t strea
   rc = af_make_map_bf16(&mv, a.vcache, n_pages * a.nkv * AF_PAGE, HD, HD, AF_PAGE);
   if (rc) return rc;
   const int group = a.nq / a.nkv;
-  dim3 grid(batch, a.nkv * ((group + 15) / 16), a.n_splits);
-  af_launch(attn_decode_split_kernel<HD>, grid, dim3(DA_THREADS), smem, stream, mk, mv, a);
+  const int units_per_seq = a.nkv * ((group + 15) / 16);
+  // (a sequence attends to at most max_pages + 1 pages: a window's first and last page may be the same of the ring)
+  AF_REQUIRE(batch <= DA_MAX_BATCH && (long long)batch * (a.max_pages + 1) * units_per_seq < (1ll << 31),
+             "af_attn_decode: %d sequences of up to %d pages (takes %d sequences)", batch, a.max_pages, DA_MAX_BATCH);
+  const int n_blocks = a.n_sms;   // one block an SM; the blocks work out among themselves which of them work
+  af_launch(attn_decode_split_kernel<HD>, dim3(n_blocks), dim3(DA_THREADS), smem, stream, mk, mv, a);
   AF_COUNT_LAUNCH("af_attn_decode (split)");
-  af_launch(attn_decode_merge_kernel<HD>, dim3(batch, a.nq), dim3(HD < 128 ? HD : 128), 0, stream, a.out,
-            a.out_stride, (const float*)a.part_o, (const float*)a.part_ml, a.nq, a.n_splits, a.slots, a.lens, a.window,
-            (int)grid.y, a.n_sms);
+  // The large block only where the merge's blocks are few: the split kernel's blocks fill their SMs' registers, so
+  // the merge's blocks wait (their part before the wait done) on the SMs that the split kernel left idle, and
+  // those hold few large blocks.  Many (sequence, head) pairs have few splits each, unless one long sequence stands
+  // among short ones: then one group of threads takes its splits eight at a time.
+  const int merge_threads = a.n_splits > DA_MERGE_FEW && batch * a.nq <= 32 ? DA_MERGE_THREADS : (HD < 128 ? HD : 128);
+  af_launch(attn_decode_merge_kernel<HD>, dim3(batch, a.nq), dim3(merge_threads), 0, stream, a.out, a.out_stride,
+            (const float*)a.part_o, (const float*)a.part_ml, a.nq, a.nkv, a.n_splits, a.slots, a.lens, a.window,
+            n_blocks);
   AF_CHECK_LAUNCH("af_attn_decode (merge)");
 }
 

@@ -586,35 +586,26 @@ def attn_prefill(out, q, k, v, batch, nq, nkv, hd, scale, cap, window, slopes=No
     attn_prefill_plain(out, q, k, v, batch.positions, nq, nkv, hd, scale, cap, window)
 
 
-def attn_decode_splits(batch: int, nkv: int, max_len: int, window: int, blocks: int = 0) -> int:
-    """How many ways the keys of a sequence are split so that the step fills
-    the GPU (``blocks``: its multiprocessors, asked of the device when 0)."""
+def attn_decode_max_splits(batch: int, nkv: int, max_len: int, window: int, blocks: int = 0, nq: int = 0) -> int:
+    """The most splits the decode kernel may give one (sequence, kv head) unit:
+    the room its partial results need.  The kernel's blocks (one an SM) each
+    take an equal share of all units' cache pages, so a unit lies in at most
+    ``blocks // units of a sequence + 2`` blocks (one long sequence among empty
+    ones, whatever the batch) and in at most its pages + 1."""
     blocks = blocks or sm_count()
     rows = min(max_len, window) if window else max_len
     pages = max(1, (rows + PAGE - 1) // PAGE + (1 if window else 0))
-    want = max(1, blocks // max(1, batch * nkv))   # one wave of blocks, each with a long run of pages
-    return max(1, min(want, pages, 64))
-
-
-def attn_decode_max_splits(batch: int, nkv: int, max_len: int, window: int, blocks: int = 0) -> int:
-    """The most splits the split kernel may give one sequence (the third extent
-    of its grid).  With sequences of equal lengths it uses
-    :func:`attn_decode_splits` of them; the room above that is for a long
-    sequence among short ones, up to three blocks an SM in all (a block without
-    a split of its own leaves at once, but the SMs start them one by one)."""
-    blocks = blocks or sm_count()
-    rows = min(max_len, window) if window else max_len
-    pages = max(1, (rows + PAGE - 1) // PAGE + (1 if window else 0))
-    units = max(1, batch * nkv)
-    return max(1, min(max(blocks // units, min(16, 3 * blocks // units)), pages, 64))
+    tiles = ((nq // nkv) + 15) // 16 if nq else 1
+    return max(1, min(blocks // max(1, nkv * tiles) + 2, pages + 1))
 
 
 def attn_decode_split(out, q, kcache, vcache, page_table, slots, lens, nq, nkv, hd, scale, cap, window, ring_rows,
                       n_splits: int, scratch=None) -> None:
     """bfloat16 decode attention, split over the keys (two kernels: partial
     results into ``scratch``, then their merge).  ``n_splits`` is the most
-    splits a sequence gets: the kernel cuts every sequence so that all blocks
-    get about the same number of cache pages."""
+    splits a (sequence, kv head) unit gets: the kernel cuts the units' pages so
+    that all blocks get about the same number of them (with less room than
+    :func:`attn_decode_max_splits` fewer blocks work)."""
     B = q.shape[0]
     lib = _lib()
     lib.af_attn_decode_scratch.restype = ctypes.c_longlong
@@ -639,7 +630,7 @@ def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window, slopes=None)
     bfloat16 and head sizes it takes, else the plain kernel (which also serves
     scores with a per-head slope)."""
     if slopes is None and q.dtype == torch.bfloat16 and _lib().af_attn_decode_supported(c_int(hd)):
-        n = attn_decode_max_splits(batch.n_seqs, nkv, batch.max_len_after, window)
+        n = attn_decode_max_splits(batch.n_seqs, nkv, batch.max_len_after, window, nq=nq)
         attn_decode_split(out, q, kv.k, kv.v, kv.page_table, batch.slots, batch.len_after, nq, nkv, hd, scale, cap,
                           window, kv.ring_rows, n)
         return

@@ -357,8 +357,9 @@ def test_attention_prefill_plain(K, dtype, hd, nq, nkv, window, cap):
         o += n
 
 
-def _decode_case(K, dtype, hd, nq, nkv, window, cap, lens, q, ks, vs, scale):
-    """Sequences with their own lengths in permuted pages; returns kernel output [B, nq*hd]."""
+def _decode_case(K, dtype, hd, nq, nkv, window, cap, lens, q, ks, vs, scale, n_splits=None, padding=()):
+    """Sequences with their own lengths in permuted pages; returns kernel output [B, nq*hd].  ``n_splits``: the
+    split kernel with that much room for partial results; ``padding``: rows of the batch without a slot."""
     B = len(lens)
     ring = ((window + PAGE - 1) // PAGE) * PAGE if window else 0
     per_seq = max(((min(n, ring) if ring else n) + PAGE - 1) // PAGE for n in lens)
@@ -378,11 +379,15 @@ def _decode_case(K, dtype, hd, nq, nkv, window, cap, lens, q, ks, vs, scale):
             p = int(table[slots[b], r // PAGE])
             kc[p, :, r % PAGE] = ks[b][r_pos]
             vc[p, :, r % PAGE] = vs[b][r_pos]
-    out = torch.empty(B, nq * hd, dtype=dtype, device=DEV)
+    out = torch.full((B, nq * hd), float("nan"), dtype=dtype, device=DEV)
+    slots_t = torch.tensor([-1 if b in padding else sl for b, sl in enumerate(slots)], dtype=torch.int32, device=DEV)
+    lens_t = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    if n_splits is not None:
+        K.attn_decode_split(out, q.to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV), slots_t, lens_t, nq, nkv, hd,
+                            scale, cap, window, ring, n_splits)
+        return out
     K.attn_decode(out, q.to(DEV), _View(kc.to(DEV), vc.to(DEV), table.to(DEV), ring),
-                  _Batch(torch.tensor(slots, dtype=torch.int32, device=DEV),
-                         torch.tensor(lens, dtype=torch.int32, device=DEV), max(lens)),
-                  nq, nkv, hd, scale, cap, window)
+                  _Batch(slots_t, lens_t, max(lens)), nq, nkv, hd, scale, cap, window)
     return out
 
 
@@ -437,8 +442,70 @@ def test_attention_decode_one_long_sequence_among_short_ones(K, hd, nq, nkv, win
         close(out[b], ref, dtype, scale=1.0)
     near = (out[1].double().cpu().reshape(nq, hd)[0] - vs[1][far, 0].double()).abs().max()
     assert near < 0.1, float(near)
-    assert K.attn_decode_max_splits(7, nkv, 2500, window) >= K.attn_decode_splits(7, nkv, 2500, window)
-    assert K.attn_decode_max_splits(8, 4, 8192, 0) > K.attn_decode_splits(8, 4, 8192, 0)
+
+
+def _check_decode(K, out, lens, q, ks, vs, nq, hd, scale, cap, window, padding=()):
+    for b, n in enumerate(lens):
+        if b in padding:
+            assert float(out[b].float().abs().max()) == 0.0, b          # a row without a slot gives zeros
+            continue
+        qq = torch.zeros(n, nq, hd, dtype=torch.float64)
+        qq[-1] = q[b].double().reshape(nq, hd)
+        ref = plain.attention(qq, ks[b].double(), vs[b].double(), scale, cap, window or None)[-1]
+        close(out[b], ref, torch.bfloat16, scale=1.0)
+
+
+@pytest.mark.parametrize("hd,nq,nkv,window", [(256, 8, 4, 0), (128, 8, 4, 200), (64, 40, 2, 0), (128, 12, 2, 0)])
+def test_attention_decode_many_short_sequences_share_blocks(K, hd, nq, nkv, window):
+    """More (sequence, kv head) units than blocks: the blocks take equal runs of the units' pages end to end, so a
+    block ends one unit and begins the next (other sequence, other kv head, other tile of heads) and leaves a
+    partial result for each.  Rows without a slot lie between them.  (40 heads in 2 groups: tiles of 16 and 4.)"""
+    dtype = torch.bfloat16
+    g = torch.Generator().manual_seed(hd + nq)
+    n_seq = 90 if nkv == 2 else 50
+    lens = [int(x) for x in torch.randint(1, 330, (n_seq,), generator=g)]
+    lens[3], lens[17] = 1, 64
+    padding = (0, 5, 6, n_seq - 1)
+    scale = 1.0 / math.sqrt(hd)
+    q = torch.randn(n_seq, nq * hd, generator=g).to(dtype)
+    ks = [(torch.randn(n, nkv, hd, generator=g) * 0.5).to(dtype) for n in lens]
+    vs = [torch.randn(n, nkv, hd, generator=g).to(dtype) for n in lens]
+    out = _decode_case(K, dtype, hd, nq, nkv, window, 30.0, lens, q, ks, vs, scale, padding=padding)
+    _check_decode(K, out, lens, q, ks, vs, nq, hd, scale, 30.0, window, padding)
+
+
+@pytest.mark.parametrize("n_splits", [1, 2, 3, 5, 9, 64])
+def test_attention_decode_with_any_room_for_partial_results(K, n_splits):
+    """The caller says how many partial results a unit may leave; with little room fewer blocks work, and the
+    result is the same."""
+    dtype, hd, nq, nkv = torch.bfloat16, 128, 6, 2
+    torch.manual_seed(n_splits)
+    lens = [700, 3, 1500, 64, 200, 129, 2000, 90, 1, 333, 65, 1000]
+    scale = 1.0 / math.sqrt(hd)
+    q = torch.randn(len(lens), nq * hd).to(dtype)
+    ks = [(torch.randn(n, nkv, hd) * 0.5).to(dtype) for n in lens]
+    vs = [torch.randn(n, nkv, hd).to(dtype) for n in lens]
+    out = _decode_case(K, dtype, hd, nq, nkv, 0, 0.0, lens, q, ks, vs, scale, n_splits=n_splits)
+    _check_decode(K, out, lens, q, ks, vs, nq, hd, scale, 0.0, 0)
+
+
+def test_attention_decode_one_sequence_in_many_splits(K):
+    """One sequence alone is cut into a split a page (more than the merge's short path takes): a key in the
+    first page and one in the last both count."""
+    dtype, hd, nq, nkv, n = torch.bfloat16, 256, 8, 4, 4000
+    torch.manual_seed(11)
+    q = torch.randn(1, nq * hd).to(dtype)
+    k = (torch.randn(n, nkv, hd) * 0.05).to(dtype)
+    v = torch.randn(n, nkv, hd).to(dtype)
+    qv = q.float().reshape(nq, hd)
+    k[7, 0] = (qv[0] * 4.0).to(dtype)
+    k[n - 2, 0] = (qv[0] * 4.0).to(dtype)
+    scale = 1.0 / math.sqrt(hd)
+    out = _decode_case(K, dtype, hd, nq, nkv, 0, 0.0, [n], q, [k], [v], scale)
+    _check_decode(K, out, [n], q, [k], [v], nq, hd, scale, 0.0, 0)
+    both = 0.5 * (v[7, 0].double() + v[n - 2, 0].double())
+    assert float((out[0].double().cpu().reshape(nq, hd)[0] - both).abs().max()) < 0.1
+    assert K.attn_decode_max_splits(1, nkv, n, 0, nq=nq) > 8
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
