@@ -16,11 +16,21 @@ long long af_attn_decode_scratch(int batch, int nq, int hd, int n_splits);
 
 // Decode attention over the paged bfloat16 cache (see attention_decode.cu).
 // `scratch` is the caller's: af_attn_decode_scratch(...) floats of device memory.  n_splits is the most
-// splits a sequence's keys are cut into (the kernel cuts each sequence by its length).
+// splits a sequence's keys are cut into (the kernel cuts each sequence by its length).  `plan`: the step's plan
+// from af_attn_decode_plan for the same slots, lengths, page table, heads, window, ring and n_splits, or null
+// (every block then works the cut out itself, which costs it a few loads, one after the other, before its
+// first copy).
 int af_attn_decode(void* out, long long out_stride, const void* q, long long q_stride, const void* kcache,
                    const void* vcache, long long n_pages, const int* page_table, int max_pages, const int* slots,
                    const int* lens, int batch, int nq, int nkv, int hd, float scale, float cap, int window,
-                   int ring_rows, int n_splits, float* scratch, int* err, cudaStream_t stream);
+                   int ring_rows, int n_splits, float* scratch, const int* plan, int* err, cudaStream_t stream);
+
+// The plan of a step: how af_attn_decode cuts its work, made once for all layers that read the same caches the
+// same way.  `plan`: af_attn_decode_plan_ints(...) 32-bit integers of device memory, 16-byte aligned.
+long long af_attn_decode_plan_ints(int batch, int nq, int nkv);
+int af_attn_decode_plan(int* plan, long long plan_ints, const int* page_table, int max_pages, const int* slots,
+                        const int* lens, int batch, int nq, int nkv, int window, int ring_rows, int n_splits,
+                        cudaStream_t stream);
 
 // ---------------------------------------------------------------------------
 // af_attn_decode_static: the same attention for callers that cannot allocate.

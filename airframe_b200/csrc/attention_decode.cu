@@ -71,6 +71,7 @@ struct DecodeArgs {
   float* part_o;   // [batch, nq, splits, HD]
   float* part_ml;  // [batch, nq, splits, 2]
   int* err;        // set to 1 when a bounded wait ran out
+  const int* plan; // the step's plan (attn_decode_plan_kernel), or null: every block works the cut out itself
   __nv_bfloat16* out;  // [batch, nq * HD], rows out_stride apart
   long long out_stride;
 };
@@ -233,6 +234,130 @@ __device__ __forceinline__ int da_find(const int* arr, int n, int scale, int x) 
   return lo;
 }
 
+// What block w begins with: pages [p_in, p_in + n_pages) of unit y of sequence b, the unit's split z; run_pages is
+// all the block works (in the run cut it goes on with the units that follow).  n_pages < 0: the block has no work.
+struct DaFirst {
+  int n_pages, b, y, z, p_in, run_pages;
+};
+
+__device__ __forceinline__ DaFirst da_first_segment(const DaPlan& pl, const int* pages_s, const int* splits_s, int batch,
+                                                    int units_per_seq, int w) {
+  DaFirst fs;
+  fs.n_pages = -1;
+  fs.b = fs.y = fs.z = fs.p_in = fs.run_pages = 0;
+  if (pl.even) {
+    // split z of unit y of sequence b, one of da_even_splits(...) equal parts of its pages
+    if (w >= splits_s[batch] * units_per_seq) return fs;
+    const int b = da_find(splits_s, batch, units_per_seq, w);
+    const int sp = splits_s[b + 1] - splits_s[b], P = pages_s[b + 1] - pages_s[b];
+    const int r = w - splits_s[b] * units_per_seq;
+    const int per = (P + sp - 1) / sp;
+    fs.b = b;
+    fs.y = r / sp;
+    fs.z = r - fs.y * sp;
+    fs.p_in = fs.z * per;
+    fs.n_pages = max(0, min(per, P - fs.p_in));   // (0: the unit has fewer pages than splits; an empty partial result)
+    fs.run_pages = fs.n_pages;
+    return fs;
+  }
+  // the run cut: pages [gpos, gend) of all units' pages end to end
+  const int total = pages_s[batch] * units_per_seq;
+  const int gpos = w * pl.share, gend = min(total, gpos + pl.share);
+  if (w >= pl.n_blocks || gpos >= gend) return fs;
+  const int b = da_find(pages_s, batch, units_per_seq, gpos);
+  const int P = pages_s[b + 1] - pages_s[b];
+  const int seq0 = pages_s[b] * units_per_seq;
+  fs.b = b;
+  fs.y = (gpos - seq0) / P;
+  fs.p_in = (gpos - seq0) - fs.y * P;
+  fs.run_pages = gend - gpos;
+  fs.n_pages = min(P - fs.p_in, fs.run_pages);
+  fs.z = w - (seq0 + fs.y * P) / pl.share;   // (the run may begin inside a unit: then it is not the unit's first split)
+  return fs;
+}
+
+// ---------------------------------------------------------------- the plan of a step
+//
+// The cut depends on the step's lengths alone, so the layers that read the same caches the same way (one group of
+// layers) can share it: a small kernel works it out once, and each layer's blocks read their first segment from
+// it with one load, where otherwise each block loads slots and lengths, works out the cut and loads page ids,
+// one after the other, before its first copy can start.  The plan, 32-bit integers:
+//   [0, 8)                    room (splits a unit may have), grid blocks, sequences, units a sequence, how cut
+//   [8, 8 + sequences*units)  the splits of every unit, for the merge
+//   then 16 a block           n_pages (< 0: no work), b, y, z, p_in, run_pages, position of the new token, slot,
+//                             the cache pages of the segment's first four pages
+constexpr int DA_PLAN_HEAD = 8;
+constexpr int DA_PLAN_REC = 16;
+
+__host__ __device__ inline long long da_plan_records_at(int batch, int units_per_seq) {
+  return DA_PLAN_HEAD + (((long long)batch * units_per_seq + 3) / 4) * 4;
+}
+
+// One block.  It does not release its dependents early: the kernel behind it starts when the plan is complete, and
+// so does every kernel after that one, so all of them may read the plan before they wait for anything.
+__global__ void __launch_bounds__(256)
+attn_decode_plan_kernel(int* __restrict__ plan, const int* __restrict__ slots, const int* __restrict__ lens,
+                        const int* __restrict__ page_table, int max_pages, int batch, int nq, int nkv, int window,
+                        int ring_rows, int room, int grid_blocks) {
+  extern __shared__ int dp_smem[];
+  int* pages_s = dp_smem;                 // [batch + 1]
+  int* splits_s = dp_smem + batch + 1;    // [batch + 1]
+  __shared__ DaPlan plan_s;
+  pdl_wait();
+  const int group = nq / nkv, tiles = (group + 15) / 16, units_per_seq = nkv * tiles;
+  if (threadIdx.x < 32) {
+    const DaPlan pl = da_plan(slots, lens, batch, window, units_per_seq, grid_blocks, room, 0, pages_s, splits_s);
+    if (threadIdx.x == 0) plan_s = pl;
+  }
+  __syncthreads();
+  const DaPlan pl = plan_s;
+  if (threadIdx.x == 0) {
+    plan[0] = room;
+    plan[1] = grid_blocks;
+    plan[2] = batch;
+    plan[3] = units_per_seq;
+    plan[4] = pl.even;
+    plan[5] = pl.share;
+    plan[6] = pl.n_blocks;
+    plan[7] = 0;
+  }
+  for (int u = threadIdx.x; u < batch * units_per_seq; u += blockDim.x) {
+    const int b = u / units_per_seq, y = u - b * units_per_seq;
+    const int P = pages_s[b + 1] - pages_s[b];
+    int n = 0;
+    if (pl.even) {
+      n = da_even_splits(P, pl.share, room, pl.even);
+    } else if (P > 0) {
+      const int unit0 = pages_s[b] * units_per_seq + y * P;
+      n = (unit0 + P - 1) / pl.share - unit0 / pl.share + 1;
+    }
+    plan[DA_PLAN_HEAD + u] = n;
+  }
+  int* recs = plan + da_plan_records_at(batch, units_per_seq);
+  const int ring_pages = ring_rows / AF_PAGE;
+  for (int w = threadIdx.x; w < grid_blocks; w += blockDim.x) {
+    const DaFirst fs = da_first_segment(pl, pages_s, splits_s, batch, units_per_seq, w);
+    int* r = recs + (size_t)w * DA_PLAN_REC;
+    int pos = 0, slot = 0, ids[4] = {0, 0, 0, 0};
+    if (fs.n_pages >= 0) {
+      pos = lens[fs.b] - 1;
+      slot = slots[fs.b];
+      const int lo = window > 0 ? max(0, pos - window + 1) : 0;
+      for (int i = 0; i < 4 && i < fs.n_pages; ++i) {
+        const int pp = lo / AF_PAGE + fs.p_in + i;
+        const int entry = ring_pages > 0 ? pp % ring_pages : pp;
+        int page = AF_INDEX_OK(entry < max_pages, entry) ? page_table[(size_t)slot * max_pages + entry] : 0;
+        if (!AF_INDEX_OK(page >= 0, page)) page = 0;
+        ids[i] = page;
+      }
+    }
+    reinterpret_cast<int4*>(r)[0] = make_int4(fs.n_pages, fs.b, fs.y, fs.z);
+    reinterpret_cast<int4*>(r)[1] = make_int4(fs.p_in, fs.run_pages, pos, slot);
+    reinterpret_cast<int4*>(r)[2] = make_int4(ids[0], ids[1], ids[2], ids[3]);
+    reinterpret_cast<int4*>(r)[3] = make_int4(0, 0, 0, 0);
+  }
+}
+
 // The heads of one kv group are the (up to 16) rows of an m16n8k16 tile; the
 // four warps of a group share each page's 64 keys, 16 keys a warp.
 template <int HD>
@@ -269,57 +394,77 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     give_up_s = 0;
     mbar_fence_init();
   }
-  // (slots and lengths are inputs of the step, not results of the kernel in front)
-  if (warp == 0) {
-    const DaPlan pl = da_plan(a.slots, a.lens, a.batch, a.window, units_per_seq, (int)gridDim.x, a.n_splits, 0,
-                              pages_s, splits_s);
-    if (lane == 0) plan_s = pl;
-  }
-  __syncthreads();
-  const int share = plan_s.share;
-  const bool even = plan_s.even != 0;
-  const int total = pages_s[a.batch] * units_per_seq;
-  // the run cut: pages [gpos, gend) of all units' pages end to end
-  int gpos = 0, gend = 0;
-  if (even) {
-    if ((int)blockIdx.x >= splits_s[a.batch] * units_per_seq) return;   // (nothing of the block's is in flight yet)
+  // What the block begins with: from the step's plan with one load, or worked out here (slots and lengths are
+  // inputs of the step, not results of the kernel in front).
+  DaFirst fs;
+  int pos0 = 0, slot0 = 0, ids0[4] = {0, 0, 0, 0};
+  if (a.plan != nullptr) {
+    const int4* rec = reinterpret_cast<const int4*>(a.plan + da_plan_records_at(a.batch, units_per_seq)) +
+                      (size_t)blockIdx.x * (DA_PLAN_REC / 4);
+    const uint64_t keep = l2_policy_keep();   // (every layer of the group reads the plan: it should stay in L2)
+    const int4 head = ld_keep_int4(reinterpret_cast<const int4*>(a.plan), keep);
+    const int4 r0 = ld_keep_int4(rec, keep), r1 = ld_keep_int4(rec + 1, keep), r2 = ld_keep_int4(rec + 2, keep);
+    fs.n_pages = r0.x, fs.b = r0.y, fs.y = r0.z, fs.z = r0.w;
+    fs.p_in = r1.x, fs.run_pages = r1.y, pos0 = r1.z, slot0 = r1.w;
+    ids0[0] = r2.x, ids0[1] = r2.y, ids0[2] = r2.z, ids0[3] = r2.w;
+    if (head.x != a.n_splits || head.y != (int)gridDim.x || head.z != a.batch || head.w != units_per_seq) {
+      // (a plan made for another launch: nothing is read or written by it)
+      if (tid == 0 && a.err) atomicExch(a.err, 1);
+      return;
+    }
+    __syncthreads();     // (the barriers are set up)
   } else {
-    gpos = (int)blockIdx.x * share;
-    gend = min(total, gpos + share);
-    if ((int)blockIdx.x >= plan_s.n_blocks || gpos >= gend) return;
+    if (warp == 0) {
+      const DaPlan pl = da_plan(a.slots, a.lens, a.batch, a.window, units_per_seq, (int)gridDim.x, a.n_splits, 0,
+                                pages_s, splits_s);
+      if (lane == 0) plan_s = pl;
+    }
+    __syncthreads();
+    fs = da_first_segment(plan_s, pages_s, splits_s, a.batch, units_per_seq, (int)blockIdx.x);
+    if (fs.n_pages >= 0) {
+      pos0 = a.lens[fs.b] - 1;
+      slot0 = a.slots[fs.b];
+    }
   }
+  if (fs.n_pages < 0) return;                          // (nothing of the block's is in flight yet)
+  int left = fs.run_pages;                             // pages the block has still to work
   const int ring_pages = a.ring_rows / AF_PAGE;
   const float cs = a.cap > 0.f ? a.scale / a.cap : a.scale * LOG2E;
   const float cap2 = a.cap * LOG2E;
 
   // A segment: some of the pages of one unit.
   struct Segment {
-    int b, kvh, row_head0, n_rows, z, n_pages, pp_begin, last_pp, lo, pos;
+    int b, y, kvh, row_head0, n_rows, z, n_pages, pp_begin, last_pp, lo, pos;
     const int* pt;
   };
-  auto of_unit = [&](Segment& sg, int b, int y, int p_in) {
+  auto of_unit = [&](Segment& sg, int b, int y, int p_in, int pos, int slot) {
     sg.b = b;
+    sg.y = y;
     sg.kvh = y / tiles;
     sg.row_head0 = sg.kvh * group + (y % tiles) * 16;             // head of tile row 0
     sg.n_rows = min(16, sg.kvh * group + group - sg.row_head0);    // heads in this tile
-    sg.pos = a.lens[b] - 1;                                        // (length > 0: the sequence has pages)
-    sg.lo = a.window > 0 ? max(0, sg.pos - a.window + 1) : 0;
-    sg.last_pp = sg.pos / AF_PAGE;     // the page of the new token, which the kernel in front wrote
+    sg.pos = pos;
+    sg.lo = a.window > 0 ? max(0, pos - a.window + 1) : 0;
+    sg.last_pp = pos / AF_PAGE;        // the page of the new token, which the kernel in front wrote
     sg.pp_begin = sg.lo / AF_PAGE + p_in;
-    sg.pt = a.page_table + (size_t)a.slots[b] * a.max_pages;
+    sg.pt = a.page_table + (size_t)slot * a.max_pages;
   };
-  // the run cut's segment that begins at page `at` of the run
-  auto locate = [&](int at, bool first) {
-    Segment sg;
-    const int b = da_find(pages_s, a.batch, units_per_seq, at);
-    const int P = pages_s[b + 1] - pages_s[b];
-    const int seq0 = pages_s[b] * units_per_seq;
-    const int y = (at - seq0) / P, p_in = (at - seq0) - y * P;
-    sg.n_pages = min(P - p_in, gend - at);
-    // which of the unit's splits this is: the block's first segment may begin inside a unit, the later ones begin one
-    sg.z = first ? (int)blockIdx.x - (seq0 + y * P) / share : 0;
-    of_unit(sg, b, y, p_in);
-    return sg;
+  // the run cut goes on with the unit behind sg's: the same sequence's next, or the first of the next sequence
+  // that has pages (one there is: pages are left)
+  auto next_unit = [&](const Segment& sg) {
+    Segment nx;
+    int b = sg.b, y = sg.y + 1;
+    if (y >= units_per_seq) {
+      y = 0;
+      int f, l;
+      do ++b; while (b < a.batch - 1 && da_pages(a.slots, a.lens, b, a.window, &f, &l) == 0);
+    }
+    int f, l;
+    const int P = da_pages(a.slots, a.lens, b, a.window, &f, &l);
+    nx.z = 0;
+    nx.n_pages = min(P, left);
+    of_unit(nx, b, y, 0, a.lens[b] - 1, a.slots[b]);
+    return nx;
   };
   // the cache page that holds page i of segment sg (a load from the page table: asked for ahead of its use)
   auto page_id = [&](const Segment& sg, int i) {
@@ -329,6 +474,7 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     if (!AF_INDEX_OK(page >= 0, page)) page = 0;   // (the copy must still be made: the stage's barrier expects its bytes)
     return page;
   };
+  const uint64_t read_once = l2_policy_read_once();   // (a step reads every cache page once)
   // cache page `page` of kv head kvh, the block's page number ii, into stage ii % STAGES
   auto issue = [&](int kvh, int page, int ii) {
     const int row = (page * a.nkv + kvh) * AF_PAGE;
@@ -337,8 +483,8 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     mbar_expect_tx(bar, 2 * TILE_BYTES);
 #pragma unroll
     for (int c = 0; c < HD / 64; ++c) {
-      tma_load_2d(st + c * 8192, &map_k, c * 64, row, bar);
-      tma_load_2d(st + TILE_BYTES + c * 8192, &map_v, c * 64, row, bar);
+      tma_load_2d_once(st + c * 8192, &map_k, c * 64, row, bar, read_once);
+      tma_load_2d_once(st + TILE_BYTES + c * 8192, &map_v, c * 64, row, bar, read_once);
     }
   };
   // the first pages of a segment: their page ids are loaded together, then the copies go out
@@ -358,24 +504,25 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
 
   int i_base = 0;          // pages this block has worked before the segment: barriers and stages count on
   Segment sg;
-  if (even) {
-    // split z of unit y of sequence b, one of da_even_splits(...) equal parts of its pages
-    const int w = (int)blockIdx.x;
-    const int b = da_find(splits_s, a.batch, units_per_seq, w);
-    const int sp = splits_s[b + 1] - splits_s[b], P = pages_s[b + 1] - pages_s[b];
-    const int r = w - splits_s[b] * units_per_seq;
-    const int y = r / sp;
-    const int per = (P + sp - 1) / sp;
-    sg.z = r - y * sp;
-    sg.n_pages = max(0, min(per, P - sg.z * per));     // (0: the unit has fewer pages than splits; an empty partial result)
-    of_unit(sg, b, y, sg.z * per);
-  } else {
-    sg = locate(gpos, true);
-  }
+  sg.z = fs.z;
+  sg.n_pages = fs.n_pages;
+  of_unit(sg, fs.b, fs.y, fs.p_in, pos0, slot0);
   int issued = 0;          // pages of the segment that are on their way already
   // the cache rows of earlier tokens do not depend on the kernel in front: the first pages are on their way
   // before the wait for it; only the page that holds the new token waits
-  if (tid == 0) issued = issue_first(sg, 0, min(STAGES, sg.n_pages), 0, true);
+  if (tid == 0) {
+    if (a.plan != nullptr) {
+      // (the plan holds the first pages' ids: no load from the page table stands before the copies)
+#pragma unroll
+      for (int k = 0; k < STAGES; ++k)
+        if (k == issued && k < sg.n_pages && sg.pp_begin + k != sg.last_pp) {
+          issue(sg.kvh, ids0[k], k);
+          ++issued;
+        }
+    } else {
+      issued = issue_first(sg, 0, min(STAGES, sg.n_pages), 0, true);
+    }
+  }
   pdl_wait();
   while (true) {
     const int b = sg.b, n_pages = sg.n_pages, n_rows = sg.n_rows, row_head0 = sg.row_head0, z = sg.z;
@@ -521,12 +668,12 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     // stage (up to 8 heads in the tile), the next segment's first pages go into the other stages before the
     // merge, so that the block's stream of pages does not stop at a unit's end.
     i_base += n_pages;
-    gpos += n_pages;
-    const bool more = gpos < gend && !gave_up;       // (the even cut: one segment; gend is 0)
+    left -= n_pages;
+    const bool more = left > 0 && !gave_up;          // (the even cut: one segment)
     Segment nx = sg;
     issued = 0;
     if (more) {
-      nx = locate(gpos, false);
+      nx = next_unit(sg);
       if (tid == 0 && n_rows <= 8) issued = issue_first(nx, 0, min(STAGES - 1, nx.n_pages), i_base, false);
     }
     // [warp][rows of real heads][HD], in the stage that the next pages reach last (thread 0 alone issues on)
@@ -588,7 +735,8 @@ template <int HD>
 __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long long out_stride,
                                          const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          int nq, int nkv, int max_splits, const int* __restrict__ slots,
-                                         const int* __restrict__ lens, int window, int grid_blocks) {
+                                         const int* __restrict__ lens, int window, int grid_blocks,
+                                         const int* __restrict__ plan) {
   pdl_launch_dependents();
   const int b = blockIdx.x, h = blockIdx.y, batch = gridDim.x;
   const size_t p0 = ((size_t)b * nq + h) * max_splits;
@@ -596,21 +744,25 @@ __global__ void attn_decode_merge_kernel(__nv_bfloat16* __restrict__ out, long l
   __shared__ float m_sh[DA_MERGE_MOST], l_sh[DA_MERGE_MOST];
   __shared__ float red_s[DA_MERGE_THREADS * 2];
   const int group = nq / nkv, tiles = (group + 15) / 16, units_per_seq = nkv * tiles;
-  // (slots and lengths are inputs of the step: the cut is worked out before the wait)
-  if (threadIdx.x < 32) {
-    const DaPlan pl = da_plan(slots, lens, batch, window, units_per_seq, grid_blocks, max_splits, b, nullptr, nullptr);
-    if (threadIdx.x == 0) plan_s = pl;
-  }
-  __syncthreads();
-  int first_pp, last_pp;
-  const int P = da_pages(slots, lens, b, window, &first_pp, &last_pp);
+  // (the plan, or slots and lengths, are inputs of the step: the cut is known before the wait)
   int n_splits;
-  if (plan_s.even) {
-    n_splits = da_even_splits(P, plan_s.share, max_splits, plan_s.even);
+  if (plan != nullptr) {
+    n_splits = ld_keep_int(plan + DA_PLAN_HEAD + b * units_per_seq + (h / group) * tiles + (h % group) / 16, l2_policy_keep());
   } else {
-    const int y = (h / group) * tiles + (h % group) / 16;
-    const int unit0 = plan_s.pages_before * units_per_seq + y * P;
-    n_splits = P > 0 ? (unit0 + P - 1) / plan_s.share - unit0 / plan_s.share + 1 : 0;
+    if (threadIdx.x < 32) {
+      const DaPlan pl = da_plan(slots, lens, batch, window, units_per_seq, grid_blocks, max_splits, b, nullptr, nullptr);
+      if (threadIdx.x == 0) plan_s = pl;
+    }
+    __syncthreads();
+    int first_pp, last_pp;
+    const int P = da_pages(slots, lens, b, window, &first_pp, &last_pp);
+    if (plan_s.even) {
+      n_splits = da_even_splits(P, plan_s.share, max_splits, plan_s.even);
+    } else {
+      const int y = (h / group) * tiles + (h % group) / 16;
+      const int unit0 = plan_s.pages_before * units_per_seq + y * P;
+      n_splits = P > 0 ? (unit0 + P - 1) / plan_s.share - unit0 / plan_s.share + 1 : 0;
+    }
   }
   pdl_wait();
   // (the number of splits is known before the wait and the loads below depend on nothing else: without
@@ -764,7 +916,7 @@ int launch_decode(DecodeArgs a, int batch, long long n_pages, cudaStream_t strea
   const int merge_threads = a.n_splits > DA_MERGE_FEW && batch * a.nq <= 32 ? DA_MERGE_THREADS : (HD < 128 ? HD : 128);
   af_launch(attn_decode_merge_kernel<HD>, dim3(batch, a.nq), dim3(merge_threads), 0, stream, a.out, a.out_stride,
             (const float*)a.part_o, (const float*)a.part_ml, a.nq, a.nkv, a.n_splits, a.slots, a.lens, a.window,
-            n_blocks);
+            n_blocks, a.plan);
   AF_CHECK_LAUNCH("af_attn_decode (merge)");
 }
 
@@ -787,14 +939,15 @@ AF_EXPORT int af_attn_decode(void* out, long long out_stride, const void* q, lon
                              const void* kcache, const void* vcache, long long n_pages, const int* page_table,
                              int max_pages, const int* slots, const int* lens, int batch, int nq, int nkv, int hd,
                              float scale, float cap, int window, int ring_rows, int n_splits, float* scratch,
-                             int* err, cudaStream_t stream) {
+                             const int* plan, int* err, cudaStream_t stream) {
   if (batch == 0) return 0;
   AF_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "af_attn_decode: heads %d, groups %d", nq, nkv);
   AF_REQUIRE(af_attn_decode_supported(hd), "af_attn_decode: head_dim %d (takes 64, 128, 256)", hd);
   AF_REQUIRE(ring_rows % AF_PAGE == 0 && (ring_rows == 0 || (window > 0 && window <= ring_rows)),
              "af_attn_decode: window %d, ring rows %d", window, ring_rows);
   AF_REQUIRE(n_splits >= 1 && n_splits <= 65535 && scratch != nullptr, "af_attn_decode: splits %d", n_splits);
-  AF_REQUIRE(((uintptr_t)kcache & 15) == 0 && ((uintptr_t)vcache & 15) == 0, "af_attn_decode: cache alignment");
+  AF_REQUIRE(((uintptr_t)kcache & 15) == 0 && ((uintptr_t)vcache & 15) == 0 && ((uintptr_t)plan & 15) == 0,
+             "af_attn_decode: cache and plan alignment");
   DecodeArgs a;
   a.q = (const __nv_bfloat16*)q;
   a.q_stride = q_stride;
@@ -817,12 +970,45 @@ AF_EXPORT int af_attn_decode(void* out, long long out_stride, const void* q, lon
   a.part_o = scratch;
   a.part_ml = scratch + (size_t)batch * nq * n_splits * hd;
   a.err = err;
+  a.plan = plan;
   a.out = (__nv_bfloat16*)out;
   a.out_stride = out_stride;
   AF_REQUIRE(n_pages > 0 && n_pages * nkv * AF_PAGE < (1ll << 31), "af_attn_decode: %lld cache pages", n_pages);
   if (hd == 64) return launch_decode<64>(a, batch, n_pages, stream);
   if (hd == 128) return launch_decode<128>(a, batch, n_pages, stream);
   return launch_decode<256>(a, batch, n_pages, stream);
+}
+
+// ---------------------------------------------------------------- the plan of a step
+
+// 32-bit integers of a plan for af_attn_decode.
+AF_EXPORT long long af_attn_decode_plan_ints(int batch, int nq, int nkv) {
+  if (batch <= 0 || nq <= 0 || nkv <= 0 || nq % nkv) return 0;
+  const int units_per_seq = nkv * ((nq / nkv + 15) / 16);
+  int sms = af_sm_count();
+  if (sms <= 0) return 0;
+  return da_plan_records_at(batch, units_per_seq) + (long long)sms * DA_PLAN_REC;
+}
+
+// Works out, once for a step, how af_attn_decode cuts the work of the layers that read the same caches the same
+// way (the same slots, lengths, page table, heads, window, ring and n_splits): pass `plan` to each of their calls.
+// It holds for these lengths alone: a step later it is made again.
+AF_EXPORT int af_attn_decode_plan(int* plan, long long plan_ints, const int* page_table, int max_pages,
+                                  const int* slots, const int* lens, int batch, int nq, int nkv, int window,
+                                  int ring_rows, int n_splits, cudaStream_t stream) {
+  if (batch == 0) return 0;
+  AF_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "af_attn_decode_plan: heads %d, groups %d", nq, nkv);
+  AF_REQUIRE(plan != nullptr && ((uintptr_t)plan & 15) == 0 && plan_ints >= af_attn_decode_plan_ints(batch, nq, nkv),
+             "af_attn_decode_plan: a plan of %lld integers, 16-byte aligned, wanted", af_attn_decode_plan_ints(batch, nq, nkv));
+  AF_REQUIRE(n_splits >= 1 && ring_rows % AF_PAGE == 0, "af_attn_decode_plan: splits %d, ring rows %d", n_splits, ring_rows);
+  const int units_per_seq = nkv * ((nq / nkv + 15) / 16);
+  AF_REQUIRE(batch <= DA_MAX_BATCH && (long long)batch * (max_pages + 1) * units_per_seq < (1ll << 31),
+             "af_attn_decode_plan: %d sequences of up to %d pages (takes %d sequences)", batch, max_pages, DA_MAX_BATCH);
+  const int sms = af_sm_count();
+  if (sms <= 0) return -1;
+  af_launch(attn_decode_plan_kernel, dim3(1), dim3(256), (size_t)2 * (batch + 1) * sizeof(int), stream, plan, slots,
+            lens, page_table, max_pages, batch, nq, nkv, window, ring_rows, n_splits, sms);
+  AF_CHECK_LAUNCH("af_attn_decode_plan");
 }
 
 // ---------------------------------------------------------------- no allocation
@@ -877,5 +1063,5 @@ AF_EXPORT int af_attn_decode_static(void* out, long long out_stride, const void*
   const int rc = decode_scratch_address(&scratch);
   if (rc) return rc;
   return af_attn_decode(out, out_stride, q, q_stride, kcache, vcache, n_pages, page_table, max_pages, slots, lens,
-                        batch, nq, nkv, hd, scale, cap, window, ring_rows, n_splits, scratch, err, stream);
+                        batch, nq, nkv, hd, scale, cap, window, ring_rows, n_splits, scratch, nullptr, err, stream);
 }

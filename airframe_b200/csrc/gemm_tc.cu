@@ -129,6 +129,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
   const int kb0 = blockIdx.z * a.kb_per_split;
   const int kb_count = min(a.kb_per_split, total_kb - kb0);
   const int n_tiles = a.tiles_w * a.tiles_m;
+  // with one tile of tokens every weight is read once: it is marked first to leave L2 (many tiles of tokens
+  // come back to the same weights, which should stay)
+  const bool w_once = a.tiles_m == 1;
+  const uint64_t read_once = l2_policy_read_once();
 
   // The producer thread sets the barriers up and sends the first stages' weight tiles on their way at once,
   // before the block meets at its first barrier and before the wait for the kernel in front: the weights
@@ -151,7 +155,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       mbar_expect_tx(&full[kb], STAGE_BYTES);
       const int k = (kb0 + kb) * TC_BK;
 #pragma unroll
-      for (int acc = 0; acc < NACC; ++acc) tma_load_2d(st + acc * A_BYTES, &map_w, k, n0 + acc * TC_BM, &full[kb]);
+      for (int acc = 0; acc < NACC; ++acc) {
+        if (w_once) tma_load_2d_once(st + acc * A_BYTES, &map_w, k, n0 + acc * TC_BM, &full[kb], read_once);
+        else tma_load_2d(st + acc * A_BYTES, &map_w, k, n0 + acc * TC_BM, &full[kb]);
+      }
     }
   }
   if (warp == 1) {
@@ -192,7 +199,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
           mbar_expect_tx(&full[s], STAGE_BYTES);
           const int k = (kb0 + kb) * TC_BK;
 #pragma unroll
-          for (int acc = 0; acc < NACC; ++acc) tma_load_2d(st + acc * A_BYTES, &map_w, k, n0 + acc * TC_BM, &full[s]);
+          for (int acc = 0; acc < NACC; ++acc) {
+            if (w_once) tma_load_2d_once(st + acc * A_BYTES, &map_w, k, n0 + acc * TC_BM, &full[s], read_once);
+            else tma_load_2d(st + acc * A_BYTES, &map_w, k, n0 + acc * TC_BM, &full[s]);
+          }
           tma_load_2d(st + NACC * A_BYTES, &map_x, k, m0, &full[s]);
         }
       }

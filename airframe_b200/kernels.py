@@ -599,8 +599,27 @@ def attn_decode_max_splits(batch: int, nkv: int, max_len: int, window: int, bloc
     return max(1, min(blocks // max(1, nkv * tiles) + 2, pages + 1))
 
 
+def attn_decode_plan(page_table, slots, lens, nq: int, nkv: int, window: int, ring_rows: int, n_splits: int):
+    """The plan of a decode step for :func:`attn_decode_split`: how the work is
+    cut among the blocks, worked out by one small kernel for all layers that
+    read the same caches the same way (these slots, lengths, page table, heads,
+    window, ring and ``n_splits``).  It holds for these lengths alone."""
+    lib = _lib()
+    lib.af_attn_decode_plan_ints.restype = ctypes.c_longlong
+    B = slots.shape[0]
+    n = lib.af_attn_decode_plan_ints(c_int(B), c_int(nq), c_int(nkv))
+    if n <= 0:
+        raise KernelError(f"attn_decode_plan: {B} sequences, {nq} heads in {nkv} groups")
+    plan = torch.empty(n, dtype=torch.int32, device=slots.device)
+    _check(lib.af_attn_decode_plan(
+        _ptr(plan, "plan", torch.int32), c_longlong(n), _ptr(page_table, "page_table", torch.int32),
+        c_int(page_table.shape[1]), _ptr(slots, "slots", torch.int32), _ptr(lens, "lens", torch.int32), c_int(B),
+        c_int(nq), c_int(nkv), c_int(window), c_int(ring_rows), c_int(n_splits), _stream()))
+    return plan
+
+
 def attn_decode_split(out, q, kcache, vcache, page_table, slots, lens, nq, nkv, hd, scale, cap, window, ring_rows,
-                      n_splits: int, scratch=None) -> None:
+                      n_splits: int, scratch=None, plan=None) -> None:
     """bfloat16 decode attention, split over the keys (two kernels: partial
     results into ``scratch``, then their merge).  ``n_splits`` is the most
     splits a (sequence, kv head) unit gets: the kernel cuts the units' pages so
@@ -622,6 +641,7 @@ def attn_decode_split(out, q, kcache, vcache, page_table, slots, lens, nq, nkv, 
         _ptr(slots, "slots", torch.int32),
         _ptr(lens, "lens", torch.int32), c_int(B), c_int(nq), c_int(nkv), c_int(hd), c_float(scale), c_float(cap),
         c_int(window), c_int(ring_rows), c_int(n_splits), _ptr(scratch, "scratch", torch.float32),
+        _ptr(plan, "plan", torch.int32) if plan is not None else ctypes.c_void_p(0),
         _ptr(error_word(q.device), "err", torch.int32), _stream()))
 
 
@@ -631,8 +651,17 @@ def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window, slopes=None)
     scores with a per-head slope)."""
     if slopes is None and q.dtype == torch.bfloat16 and _lib().af_attn_decode_supported(c_int(hd)):
         n = attn_decode_max_splits(batch.n_seqs, nkv, batch.max_len_after, window, nq=nq)
+        # the plan of the step, shared by the layers that read this group of caches alike (a batch without a
+        # place for the step's tables gets none: every block then works the cut out itself)
+        plan, aux = None, getattr(batch, "aux", None)
+        if aux is not None:
+            key = ("attn_decode_plan", kv.page_table.data_ptr(), kv.ring_rows, nq, nkv, window, n)
+            if key not in aux:
+                aux[key] = attn_decode_plan(kv.page_table, batch.slots, batch.len_after, nq, nkv, window,
+                                            kv.ring_rows, n)
+            plan = aux[key]
         attn_decode_split(out, q, kv.k, kv.v, kv.page_table, batch.slots, batch.len_after, nq, nkv, hd, scale, cap,
-                          window, kv.ring_rows, n)
+                          window, kv.ring_rows, n, plan=plan)
         return
     attn_decode_plain(out, q, kv.k, kv.v, kv.page_table, batch.slots, batch.len_after, nq, nkv, hd,
                       scale, cap, window, kv.ring_rows, slopes)

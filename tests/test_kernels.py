@@ -357,9 +357,10 @@ def test_attention_prefill_plain(K, dtype, hd, nq, nkv, window, cap):
         o += n
 
 
-def _decode_case(K, dtype, hd, nq, nkv, window, cap, lens, q, ks, vs, scale, n_splits=None, padding=()):
+def _decode_case(K, dtype, hd, nq, nkv, window, cap, lens, q, ks, vs, scale, n_splits=None, padding=(), plan=False):
     """Sequences with their own lengths in permuted pages; returns kernel output [B, nq*hd].  ``n_splits``: the
-    split kernel with that much room for partial results; ``padding``: rows of the batch without a slot."""
+    split kernel with that much room for partial results; ``padding``: rows of the batch without a slot;
+    ``plan``: the cut comes from the step's plan (else every block works it out itself)."""
     B = len(lens)
     ring = ((window + PAGE - 1) // PAGE) * PAGE if window else 0
     per_seq = max(((min(n, ring) if ring else n) + PAGE - 1) // PAGE for n in lens)
@@ -383,11 +384,18 @@ def _decode_case(K, dtype, hd, nq, nkv, window, cap, lens, q, ks, vs, scale, n_s
     slots_t = torch.tensor([-1 if b in padding else sl for b, sl in enumerate(slots)], dtype=torch.int32, device=DEV)
     lens_t = torch.tensor(lens, dtype=torch.int32, device=DEV)
     if n_splits is not None:
-        K.attn_decode_split(out, q.to(DEV), kc.to(DEV), vc.to(DEV), table.to(DEV), slots_t, lens_t, nq, nkv, hd,
-                            scale, cap, window, ring, n_splits)
+        table_d = table.to(DEV)
+        the_plan = K.attn_decode_plan(table_d, slots_t, lens_t, nq, nkv, window, ring, n_splits) if plan else None
+        K.attn_decode_split(out, q.to(DEV), kc.to(DEV), vc.to(DEV), table_d, slots_t, lens_t, nq, nkv, hd,
+                            scale, cap, window, ring, n_splits, plan=the_plan)
         return out
-    K.attn_decode(out, q.to(DEV), _View(kc.to(DEV), vc.to(DEV), table.to(DEV), ring),
-                  _Batch(slots_t, lens_t, max(lens)), nq, nkv, hd, scale, cap, window)
+    batch = _Batch(slots_t, lens_t, max(lens))
+    if plan:
+        batch.aux = {}
+    K.attn_decode(out, q.to(DEV), _View(kc.to(DEV), vc.to(DEV), table.to(DEV), ring), batch, nq, nkv, hd, scale, cap,
+                  window)
+    if plan and dtype == torch.bfloat16 and hd in (64, 128, 256):
+        assert any(k[0] == "attn_decode_plan" for k in batch.aux)
     return out
 
 
@@ -421,8 +429,9 @@ def test_attention_decode_over_pages(K, dtype, hd, nq, nkv, window, cap):
         close(out[b], ref, dtype, scale=1.0)
 
 
+@pytest.mark.parametrize("plan", [False, True])
 @pytest.mark.parametrize("hd,nq,nkv,window", [(256, 8, 4, 0), (128, 6, 2, 0), (256, 4, 2, 300), (128, 16, 2, 1000)])
-def test_attention_decode_one_long_sequence_among_short_ones(K, hd, nq, nkv, window):
+def test_attention_decode_one_long_sequence_among_short_ones(K, hd, nq, nkv, window, plan):
     """The split kernel cuts every sequence by its own length: the long one into many splits, the short
     ones into one; a key far back in the long one has to be found."""
     dtype = torch.bfloat16
@@ -434,7 +443,7 @@ def test_attention_decode_one_long_sequence_among_short_ones(K, hd, nq, nkv, win
     vs = [torch.randn(n, nkv, hd).to(dtype) for n in lens]
     far = 2500 - 1 - (150 if window else 2100)
     ks[1][far] = (q[1].float().reshape(nq, hd)[: nq // nkv].sum(0) * 6.0).to(dtype)     # the first kv group's heads score it high
-    out = _decode_case(K, dtype, hd, nq, nkv, window, 30.0, lens, q, ks, vs, scale)
+    out = _decode_case(K, dtype, hd, nq, nkv, window, 30.0, lens, q, ks, vs, scale, plan=plan)
     for b, n in enumerate(lens):
         qq = torch.zeros(n, nq, hd, dtype=torch.float64)
         qq[-1] = q[b].double().reshape(nq, hd)
@@ -455,8 +464,9 @@ def _check_decode(K, out, lens, q, ks, vs, nq, hd, scale, cap, window, padding=(
         close(out[b], ref, torch.bfloat16, scale=1.0)
 
 
+@pytest.mark.parametrize("plan", [False, True])
 @pytest.mark.parametrize("hd,nq,nkv,window", [(256, 8, 4, 0), (128, 8, 4, 200), (64, 40, 2, 0), (128, 12, 2, 0)])
-def test_attention_decode_many_short_sequences_share_blocks(K, hd, nq, nkv, window):
+def test_attention_decode_many_short_sequences_share_blocks(K, hd, nq, nkv, window, plan):
     """More (sequence, kv head) units than blocks: the blocks take equal runs of the units' pages end to end, so a
     block ends one unit and begins the next (other sequence, other kv head, other tile of heads) and leaves a
     partial result for each.  Rows without a slot lie between them.  (40 heads in 2 groups: tiles of 16 and 4.)"""
@@ -470,12 +480,13 @@ def test_attention_decode_many_short_sequences_share_blocks(K, hd, nq, nkv, wind
     q = torch.randn(n_seq, nq * hd, generator=g).to(dtype)
     ks = [(torch.randn(n, nkv, hd, generator=g) * 0.5).to(dtype) for n in lens]
     vs = [torch.randn(n, nkv, hd, generator=g).to(dtype) for n in lens]
-    out = _decode_case(K, dtype, hd, nq, nkv, window, 30.0, lens, q, ks, vs, scale, padding=padding)
+    out = _decode_case(K, dtype, hd, nq, nkv, window, 30.0, lens, q, ks, vs, scale, padding=padding, plan=plan)
     _check_decode(K, out, lens, q, ks, vs, nq, hd, scale, 30.0, window, padding)
 
 
+@pytest.mark.parametrize("plan", [False, True])
 @pytest.mark.parametrize("n_splits", [1, 2, 3, 5, 9, 64])
-def test_attention_decode_with_any_room_for_partial_results(K, n_splits):
+def test_attention_decode_with_any_room_for_partial_results(K, n_splits, plan):
     """The caller says how many partial results a unit may leave; with little room fewer blocks work, and the
     result is the same."""
     dtype, hd, nq, nkv = torch.bfloat16, 128, 6, 2
@@ -485,7 +496,7 @@ def test_attention_decode_with_any_room_for_partial_results(K, n_splits):
     q = torch.randn(len(lens), nq * hd).to(dtype)
     ks = [(torch.randn(n, nkv, hd) * 0.5).to(dtype) for n in lens]
     vs = [torch.randn(n, nkv, hd).to(dtype) for n in lens]
-    out = _decode_case(K, dtype, hd, nq, nkv, 0, 0.0, lens, q, ks, vs, scale, n_splits=n_splits)
+    out = _decode_case(K, dtype, hd, nq, nkv, 0, 0.0, lens, q, ks, vs, scale, n_splits=n_splits, plan=plan)
     _check_decode(K, out, lens, q, ks, vs, nq, hd, scale, 0.0, 0)
 
 
@@ -752,3 +763,22 @@ def test_a_wait_that_runs_out_sets_the_error_word_and_the_library_goes_on(K):
     close(out, x.double() @ w.double().T, torch.float32)
     with pytest.raises(K.KernelError, match="100 ms"):
         K.selftest_wait_runs_out(DEV, limit_ms=5000.0)
+
+
+def test_attention_decode_refuses_a_plan_of_another_launch(K):
+    """A plan made for other room than the call's is not followed: the error word is raised, nothing is read
+    through it."""
+    dtype, hd, nq, nkv = torch.bfloat16, 128, 4, 2
+    lens = [100, 300]
+    table = torch.arange(10, dtype=torch.int32).reshape(2, 5).to(DEV)
+    kc = torch.zeros(10, nkv, PAGE, hd, dtype=dtype, device=DEV)
+    slots = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    lens_t = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    q = torch.zeros(2, nq * hd, dtype=dtype, device=DEV)
+    out = torch.zeros_like(q)
+    plan = K.attn_decode_plan(table, slots, lens_t, nq, nkv, 0, 0, 7)
+    K.attn_decode_split(out, q, kc, kc, table, slots, lens_t, nq, nkv, hd, 1.0, 0.0, 0, 0, 9, plan=plan)
+    torch.cuda.synchronize()
+    with pytest.raises(K.KernelError):
+        K.check_device_errors(DEV)
+    K.check_device_errors(DEV)   # (the word is cleared by the check)

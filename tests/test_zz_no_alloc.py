@@ -57,7 +57,7 @@ def _call(lib, fn, p, batch, nq, nkv, hd, splits, scratch=None):
             c_void_p(p["lens"].data_ptr()), c_int(batch), c_int(nq), c_int(nkv), c_int(hd),
             c_float(1.0 / math.sqrt(hd)), c_float(30.0), c_int(p["window"]), c_int(ring), c_int(splits)]
     if scratch is not None:
-        args.append(c_void_p(scratch.data_ptr()))
+        args += [c_void_p(scratch.data_ptr()), c_void_p(0)]      # scratch of the caller's, no plan of the step
     args += [c_void_p(err.data_ptr()), c_void_p(torch.cuda.current_stream().cuda_stream)]
     rc = fn(*args)
     torch.cuda.synchronize()
