@@ -108,7 +108,8 @@ __global__ void rope_cache_kernel(T* __restrict__ qkv, int row_stride, const flo
 __global__ void __launch_bounds__(256)
 rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, long long row_stride, const int* __restrict__ positions,
                       const int* __restrict__ seq_of_token, const int* __restrict__ slots,
-                      const int* __restrict__ len_after, const float* __restrict__ inv_freq, int nq, int nkv, int hd,
+                      const int* __restrict__ len_after, const float* __restrict__ inv_freq,
+                      const float2* __restrict__ table, int nq, int nkv, int hd,
                       __nv_bfloat16* __restrict__ kcache, __nv_bfloat16* __restrict__ vcache,
                       const int* __restrict__ page_table, int max_pages, int ring_rows) {
   pdl_launch_dependents();
@@ -139,13 +140,23 @@ rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, long long row_stride, con
   // the pieces of a head (it is for head sizes up to 512 that divide so): its 8 pairs' angles are fixed
   const bool fixed_c = blockDim.x % per_head == 0;
   float sn0[8], cs0[8];
-  if (fixed_c) {
+  if (fixed_c && table == nullptr) {
     const int c = threadIdx.x % per_head;
 #pragma unroll
     for (int e = 0; e < 8; ++e) sincosf((float)pos * inv_freq[c * 8 + e], &sn0[e], &cs0[e]);
   }
   pdl_wait();
   row = pdl_fresh(row);
+  if (fixed_c && table != nullptr) {
+    // the step's table of (cos, sin), made once for all layers by the same arithmetic (a kernel of this step
+    // wrote it: read after the wait)
+    const float4* tp = reinterpret_cast<const float4*>(pdl_fresh(table) + (size_t)t * half + (threadIdx.x % per_head) * 8);
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float4 v = tp[e];
+      cs0[2 * e] = v.x, sn0[2 * e] = v.y, cs0[2 * e + 1] = v.z, sn0[2 * e + 1] = v.w;
+    }
+  }
   for (int i = threadIdx.x; i < n_heads * per_head; i += blockDim.x) {
     const int head = i / per_head, c = i - head * per_head;
     __nv_bfloat16* x = row + (size_t)head * hd + c * 8;
@@ -188,7 +199,7 @@ rope_cache_vec_kernel(__nv_bfloat16* __restrict__ qkv, long long row_stride, con
 AF_EXPORT int af_rope_cache_write(void* qkv, int dtype, int row_stride, const float* parts, int n_parts,
                                   long long part_stride, const int* positions,
                                   const int* seq_of_token, const int* slots, const int* len_after,
-                                  const float* inv_freq, int n_tokens, int nq, int nkv, int hd,
+                                  const float* inv_freq, const float* table, int n_tokens, int nq, int nkv, int hd,
                                   int rot_dim, int pairing, void* kcache, void* vcache,
                                   const int* page_table, int max_pages, int ring_rows,
                                   cudaStream_t stream) {
@@ -203,7 +214,8 @@ AF_EXPORT int af_rope_cache_write(void* qkv, int dtype, int row_stride, const fl
       row_stride % 8 == 0 && ((uintptr_t)qkv & 15) == 0 && ((uintptr_t)kcache & 15) == 0 &&
       ((uintptr_t)vcache & 15) == 0 && n_tokens >= 64) {
     af_launch(rope_cache_vec_kernel, dim3(n_tokens), dim3(256), 0, stream, (__nv_bfloat16*)qkv, (long long)row_stride,
-              positions, seq_of_token, slots, len_after, inv_freq, nq, nkv, hd, (__nv_bfloat16*)kcache,
+              positions, seq_of_token, slots, len_after, inv_freq,
+              ((uintptr_t)table & 15) == 0 ? reinterpret_cast<const float2*>(table) : nullptr, nq, nkv, hd, (__nv_bfloat16*)kcache,
               (__nv_bfloat16*)vcache, page_table, max_pages, ring_rows);
     AF_CHECK_LAUNCH("af_rope_cache_write");
   }

@@ -186,12 +186,18 @@ def gemm_plain(out, x, w, cap: float = 0.0) -> None:
 
 # ---------------------------------------------------------------- attention
 
+ROPE_TABLE_ROWS = 64     # from this many rows on, the rotary kernel for bfloat16 rows takes the step's table
+
+
 def rope_cache_write(qkv, positions, inv_freq, nq: int, nkv: int, hd: int, rot_dim: int, pairing: str,
                      seq_of_token=None, slots=None, len_after=None, kcache=None, vcache=None,
-                     page_table=None, ring_rows: int = 0, parts=None) -> None:
+                     page_table=None, ring_rows: int = 0, parts=None, table=None) -> None:
     """Rotate the q and k heads of the packed rows [q | k | v] in place and,
     when a cache is given, store k and v at each token's row of its page.
-    ``parts`` (float32 [S, T, width] split-K partial sums) are added into qkv first."""
+    ``parts`` (float32 [S, T, width] split-K partial sums) are added into qkv first.
+    ``table``: the step's cosines and sines (:func:`rope_table` of these positions and
+    frequencies); the kernel for many bfloat16 rows reads them instead of working them
+    out for every layer again (the same 32-bit values)."""
     T = qkv.shape[0]
     if qkv.shape[1] != (nq + 2 * nkv) * hd:
         raise KernelError(f"rope_cache_write: row width {qkv.shape[1]} is not (nq + 2 nkv) * head_dim")
@@ -199,6 +205,8 @@ def rope_cache_write(qkv, positions, inv_freq, nq: int, nkv: int, hd: int, rot_d
         raise KernelError(f"rope_cache_write: unknown pairing '{pairing}'")
     if inv_freq.numel() != rot_dim // 2:
         raise KernelError("rope_cache_write: inv_freq must hold rot_dim / 2 values")
+    if table is not None and (tuple(table.shape) != (T, rot_dim // 2, 2) or not table.is_contiguous()):
+        raise KernelError(f"rope_cache_write: the table must be [{T}, {rot_dim // 2}, 2]")
     max_pages = 0
     if kcache is not None:
         if kcache.dtype != qkv.dtype or vcache.dtype != qkv.dtype:
@@ -213,7 +221,8 @@ def rope_cache_write(qkv, positions, inv_freq, nq: int, nkv: int, hd: int, rot_d
         _ptr(seq_of_token, "seq_of_token", torch.int32, allow_none=True),
         _ptr(slots, "slots", torch.int32, allow_none=True),
         _ptr(len_after, "len_after", torch.int32, allow_none=True),
-        _ptr(inv_freq, "inv_freq", torch.float32), c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(rot_dim),
+        _ptr(inv_freq, "inv_freq", torch.float32), _ptr(table, "table", torch.float32, allow_none=True),
+        c_int(T), c_int(nq), c_int(nkv), c_int(hd), c_int(rot_dim),
         c_int(PAIRINGS[pairing]), _ptr(kcache, allow_none=True), _ptr(vcache, allow_none=True),
         _ptr(page_table, "page_table", torch.int32, allow_none=True), c_int(max_pages), c_int(ring_rows),
         _stream()))

@@ -61,10 +61,15 @@ class Rope(PositionEncoding):
         k rows are what the cache keeps)."""
         if self.rotary_dim > hd:
             raise ConfigError(f"rope: rotary_dim {self.rotary_dim} exceeds head_dim {hd}")
+        # many rows (a prompt): the cosines and sines come from the step's table, made once for all layers
+        table = None
+        if (qkv.shape[0] >= kernels.ROPE_TABLE_ROWS and parts is None and qkv.dtype == torch.bfloat16
+                and self.rotates_half_pairs(hd)):
+            table = self.rotary_table(batch, hd)
         kernels.rope_cache_write(qkv, batch.positions, self.inv_freq, nq, nkv, hd, self.rotary_dim,
                                  self.pairing, seq_of_token=batch.seq_of_token, slots=batch.slots,
                                  len_after=batch.len_after, kcache=kv.k, vcache=kv.v,
-                                 page_table=kv.page_table, ring_rows=kv.ring_rows, parts=parts)
+                                 page_table=kv.page_table, ring_rows=kv.ring_rows, parts=parts, table=table)
         return True
 
 

@@ -782,3 +782,37 @@ def test_attention_decode_refuses_a_plan_of_another_launch(K):
     with pytest.raises(K.KernelError):
         K.check_device_errors(DEV)
     K.check_device_errors(DEV)   # (the word is cleared by the check)
+
+
+@pytest.mark.parametrize("hd", [256, 80, 128])
+def test_rope_with_the_table_of_the_step_gives_the_same_bits(K, hd):
+    """Many bfloat16 rows: the kernel takes cosines and sines from the step's table, which holds the same 32-bit
+    values that it works out itself without one; the rows and the cache come out bit for bit the same, and right."""
+    dtype, nq, nkv, theta = torch.bfloat16, 4, 2, 10000.0
+    lens = [150, 40]
+    T = sum(lens)
+    torch.manual_seed(hd)
+    qkv = torch.randn(T, (nq + 2 * nkv) * hd).to(dtype)
+    pos = torch.tensor(list(range(150)) + list(range(40)), dtype=torch.int32, device=DEV)
+    seq = torch.tensor([0] * 150 + [1] * 40, dtype=torch.int32, device=DEV)
+    inv = (torch.tensor(theta, dtype=torch.float64) ** (-2.0 * torch.arange(hd // 2, dtype=torch.float64) / hd)).float().to(DEV)
+    table = torch.tensor([[4, 2, 0], [1, -1, -1]], dtype=torch.int32, device=DEV)
+    slots = torch.tensor([0, 1], dtype=torch.int32, device=DEV)
+    lens_t = torch.tensor(lens, dtype=torch.int32, device=DEV)
+    outs = []
+    for with_table in (False, True):
+        d = qkv.to(DEV)
+        kc = torch.zeros(5, nkv, PAGE, hd, dtype=dtype, device=DEV)
+        vc = torch.zeros_like(kc)
+        tb = K.rope_table(pos, inv) if with_table else None
+        K.rope_cache_write(d, pos, inv, nq, nkv, hd, hd, "half", seq_of_token=seq, slots=slots, len_after=lens_t,
+                           kcache=kc, vcache=vc, page_table=table, ring_rows=0, table=tb)
+        outs.append((d, kc, vc))
+    for a, b in zip(outs[0], outs[1]):
+        assert torch.equal(a, b)
+    x = qkv.double().reshape(T, nq + 2 * nkv, hd)
+    want = torch.cat([plain.rope(x[:, : nq + nkv], pos.tolist(), theta), x[:, nq + nkv:]], 1)
+    close(outs[1][0].reshape(T, -1, hd), want, dtype)
+    assert torch.equal(outs[1][1][4, 0, 5].cpu(), outs[1][0].cpu().reshape(T, -1, hd)[5, nq])     # k of token 5, kv head 0
+    with pytest.raises(K.KernelError, match="table"):
+        K.rope_cache_write(qkv.to(DEV), pos, inv, nq, nkv, hd, hd, "half", table=K.rope_table(pos[:10], inv))
