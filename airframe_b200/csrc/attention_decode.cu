@@ -675,6 +675,10 @@ attn_decode_split_kernel(const __grid_constant__ CUtensorMap map_k, const __grid
     if (more) {
       nx = next_unit(sg);
       if (tid == 0 && n_rows <= 8) issued = issue_first(nx, 0, min(STAGES - 1, nx.n_pages), i_base, false);
+      // the next unit's queries: asked into L1 now, read when the merge is done
+      if (tid < nx.n_rows * (HD / 64))
+        asm volatile("prefetch.global.L1 [%0];" ::"l"(a.q + (size_t)nx.b * a.q_stride +
+                                                       (size_t)(nx.row_head0 + tid / (HD / 64)) * HD + (tid % (HD / 64)) * 64));
     }
     // [warp][rows of real heads][HD], in the stage that the next pages reach last (thread 0 alone issues on)
     float* o_s = reinterpret_cast<float*>(da_smem + (n_rows <= 8 ? (size_t)((i_base + STAGES - 1) % STAGES) * 2 * TILE_BYTES : 0));

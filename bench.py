@@ -376,6 +376,62 @@ def run_ours(args) -> dict:
     }
 
 
+def attention_points() -> None:
+    """The decode attention kernels alone (split + merge, the cut from a step's plan) at the shapes of the three
+    sizes' workloads: a CUDA graph of 12 launches back to back over caches larger than L2, taken in turn; CUDA events."""
+    import torch
+    from airframe_b200 import kernels as K
+    dev, page = torch.device("cuda:0"), 64
+
+    def case(tag, nq, nkv, hd, lens, n_caches):
+        B = len(lens)
+        per = max((n + page - 1) // page for n in lens)
+        n_pages = B * per
+        caches = [(torch.randn(n_pages, nkv, page, hd, device=dev).bfloat16(),
+                   torch.randn(n_pages, nkv, page, hd, device=dev).bfloat16()) for _ in range(n_caches)]
+        table = torch.randperm(n_pages, device=dev).int().reshape(B, per).contiguous()
+        slots = torch.arange(B, device=dev, dtype=torch.int32)
+        lens_t = torch.tensor(lens, device=dev, dtype=torch.int32)
+        q = torch.randn(B, nq * hd, device=dev).bfloat16()
+        out = torch.empty_like(q)
+        nbytes = sum((n + page - 1) // page for n in lens) * page * nkv * hd * 2 * 2
+        n = K.attn_decode_max_splits(B, nkv, max(lens), 0, nq=nq)
+        scratch = torch.empty(B * nq * n * (hd + 2), device=dev)
+        plan = K.attn_decode_plan(table, slots, lens_t, nq, nkv, 0, 0, n)
+
+        def run(i):
+            kc, vc = caches[i % n_caches]
+            K.attn_decode_split(out, q, kc, vc, table, slots, lens_t, nq, nkv, hd, hd ** -0.5, 50.0, 0, 0, n,
+                                scratch, plan=plan)
+        for i in range(3):
+            run(i)
+        torch.cuda.synchronize()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for i in range(12):
+                run(i)
+        graph.replay()
+        torch.cuda.synchronize()
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        for _ in range(10):
+            graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        us = a.elapsed_time(b) / 120 * 1000
+        print(f"{tag:44s} {us:8.2f} us a launch  {nbytes / us / 1e6:6.2f} TB/s  ({nbytes / 1e6:.0f} MB of cache pages)",
+              flush=True)
+
+    case("2b sizes, 8 x 2,049 tokens", 8, 4, 256, [2049] * 8, 6)
+    case("2b sizes, 1 x 2,049", 8, 4, 256, [2049], 16)
+    case("2b sizes, 64 x 2,049", 8, 4, 256, [2049] * 64, 2)
+    case("2b sizes, 32 short ones of 100 ... 410", 8, 4, 256, [100 + 10 * i for i in range(32)], 8)
+    case("2b sizes, one of 8,000 among 15 of 300", 8, 4, 256, [300] * 15 + [8000], 4)
+    case("9b sizes, 8 of 512 ... 4,096", 16, 8, 256, [512 * (i + 1) for i in range(8)], 3)
+    case("9b sizes, 8 x 2,304 (the same bytes)", 16, 8, 256, [2304] * 8, 3)
+    case("27b sizes, 16 of 1,024 ... 8,194", 32, 16, 128, [1024 + i * 478 for i in range(16)], 2)
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -391,6 +447,8 @@ def main() -> int:
                     help="print the kernels of one decode step with their start and duration, then exit")
     ap.add_argument("--prompt-len", type=int, default=0,
                     help="equal prompts of this many tokens instead of the workload's (not the default run)")
+    ap.add_argument("--attention", action="store_true",
+                    help="time the decode attention kernels alone at the workloads' shapes, then exit")
     ap.add_argument("--sizes", default="2b", choices=sorted(SIZES),
                     help="layer sizes of this Gemma-2 model, with the workload named for them")
     args = ap.parse_args()
@@ -402,6 +460,9 @@ def main() -> int:
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not supported")
         return 2
+    if args.attention:
+        attention_points()
+        return 0
     line = run_ours(args)
     if line is not None:
         print(json.dumps(line))
