@@ -25,6 +25,34 @@ enum AfPairing { AF_PAIR_HALF = 0, AF_PAIR_ADJACENT = 1 };
 // Tokens per cache page.  A sequence holds whole pages.
 #define AF_PAGE 64
 
+// The order in which the blocks of a tensor-core product walk its tiles (weight tiles x token tiles).
+// group == 0: a weight tile's token tiles one after the other (a prompt of few token tiles: the blocks that work at
+// the same time hold all of them).  Else the weight tiles in groups of `group`, within a group the weight tile
+// fastest: the blocks at work share `group` weight tiles and about SMs / group token tiles, so that both
+// operands come out of L2 (with thousands of token tiles the other order streams all activations from memory
+// once for every weight tile).
+#ifdef __CUDACC__
+__host__ __device__ __forceinline__ void af_tile_of(int t, int tiles_w, int tiles_m, int group, int* wt, int* mt) {
+  if (group <= 0) {
+    *wt = t / tiles_m;
+    *mt = t % tiles_m;
+    return;
+  }
+  const int per_group = group * tiles_m;
+  const int g = t / per_group, r = t - g * per_group;
+  const int width = min(group, tiles_w - g * group);      // (the last group may hold fewer weight tiles)
+  *wt = g * group + r % width;
+  *mt = r / width;
+}
+// The group for these many token tiles on `sms` blocks.
+__host__ __device__ __forceinline__ int af_tile_group(int tiles_m, int sms) {
+  if (tiles_m <= 16) return 0;
+  int g = 1;
+  while ((g + 1) * (g + 1) <= sms) ++g;
+  return g;
+}
+#endif
+
 // Records a message that af_last_error() returns and yields the error code.
 int af_fail(int code, const char* fmt, ...);
 

@@ -94,6 +94,7 @@ struct TcArgs {
   int* tickets;              // split-K: a counter per tile, zero between launches
   // ARGMAX only
   unsigned long long* keys;  // [M * AF_KEY_STRIDE] best (value, row) per token, zero before the launch
+  int group;                 // the order in which the blocks walk the tiles (af_tile_of)
 };
 
 // Float bits whose unsigned order is the floats' order.
@@ -149,7 +150,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     mbar_init(&acc_empty, 4);   // one arrival an epilogue warp
     give_up_s = 0;
     mbar_fence_init();
-    const int n0 = (blockIdx.x / a.tiles_m) * (TC_BM * NACC);
+    int wt_first, mt_first;
+    af_tile_of((int)blockIdx.x, a.tiles_w, a.tiles_m, a.group, &wt_first, &mt_first);
+    const int n0 = wt_first * (TC_BM * NACC);
     for (int kb = 0; kb < early; ++kb) {
       unsigned char* st = tiles + (size_t)kb * STAGE_BYTES;
       mbar_expect_tx(&full[kb], STAGE_BYTES);
@@ -179,7 +182,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
       int it = 0;
       bool first = true;
       for (int tile = blockIdx.x; tile < n_tiles && !*give_up; tile += gridDim.x) {
-        const int n0 = (tile / a.tiles_m) * (TC_BM * NACC), m0 = (tile % a.tiles_m) * BN;
+        int wt, mt;
+        af_tile_of(tile, a.tiles_w, a.tiles_m, a.group, &wt, &mt);
+        const int n0 = wt * (TC_BM * NACC), m0 = mt * BN;
         int kb = 0;
         if (first) {
           // (the weight tiles of these stages are on their way since the kernel began) the activations follow
@@ -248,8 +253,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     pdl_wait();
     int round = 0;
     for (int tile = blockIdx.x; tile < n_tiles; tile += gridDim.x, ++round) {
-      const int tile_w = tile / a.tiles_m;
-      const int m0 = (tile % a.tiles_m) * BN;
+      int tile_w, mt;
+      af_tile_of(tile, a.tiles_w, a.tiles_m, a.group, &tile_w, &mt);
+      const int m0 = mt * BN;
       if (!mbar_wait(&acc_full, round & 1, give_up)) break;
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       TO* out = reinterpret_cast<TO*>(a.out) + (size_t)blockIdx.z * a.part_stride;
@@ -448,6 +454,7 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcArgs a, long long n_w
   const long long tiles = (long long)a.tiles_w * a.tiles_m;
   const int sms = af_sm_count();
   if (sms <= 0) return -1;
+  a.group = af_tile_group(a.tiles_m, sms);
   if constexpr (BN <= 64 && NACC == 1) {
     // bound by the weight stream: a block per tile; many waves of them run two to an SM
     dim3 grid((unsigned)tiles, 1, splits);

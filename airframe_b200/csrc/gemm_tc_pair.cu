@@ -42,6 +42,7 @@ struct TpArgs {
   int tiles_w, tiles_m;   // tiles of 256 weight rows and of 256 tokens; pair p walks p, p + pairs, ... (token tile fastest)
   float cap;
   int* err;
+  int group;              // the order in which the pairs walk the tiles (af_tile_of)
 };
 
 __device__ __forceinline__ uint32_t cluster_rank() {
@@ -149,13 +150,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       const int total = my_tiles * kb_count;
       auto load_w = [&](int it) {
         const int tile = pair + (it / kb_count) * n_pairs;
-        const int n0 = (tile / a.tiles_m) * (2 * TP_BM) + (int)rank * TP_BM;
+        int wt, mt;
+        af_tile_of(tile, a.tiles_w, a.tiles_m, a.group, &wt, &mt);
+        const int n0 = wt * (2 * TP_BM) + (int)rank * TP_BM;
         tma_load_2d_pair(tiles + (size_t)(it % TP_STAGES) * TP_STAGE_BYTES, &map_w, (it % kb_count) * TP_BK, n0,
                          map_to_rank(smem_u32(&full[it % TP_STAGES]), 0));
       };
       auto load_x = [&](int it) {
         const int tile = pair + (it / kb_count) * n_pairs;
-        const int m0 = (tile % a.tiles_m) * TP_BN + (int)rank * (TP_BN / 2);
+        int wt, mt;
+        af_tile_of(tile, a.tiles_w, a.tiles_m, a.group, &wt, &mt);
+        const int m0 = mt * TP_BN + (int)rank * (TP_BN / 2);
         tma_load_2d_pair(tiles + (size_t)(it % TP_STAGES) * TP_STAGE_BYTES + TP_A_BYTES, &map_x, (it % kb_count) * TP_BK,
                          m0, map_to_rank(smem_u32(&full[it % TP_STAGES]), 0));
       };
@@ -215,8 +220,10 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     int round = 0;
     for (int tile = pair; tile < n_tiles; tile += n_pairs, ++round) {
       const int buf = round & 1;
-      const int wt = (tile / a.tiles_m) * 2 + (int)rank;       // this block's tile of 128 weight rows
-      const int m0 = (tile % a.tiles_m) * TP_BN;
+      int wt2, mt;
+      af_tile_of(tile, a.tiles_w, a.tiles_m, a.group, &wt2, &mt);
+      const int wt = wt2 * 2 + (int)rank;                      // this block's tile of 128 weight rows
+      const int m0 = mt * TP_BN;
       if (!mbar_wait(&acc_full[buf], (round >> 1) & 1, give_up)) break;
       tc_fence_after();
       TO* out = reinterpret_cast<TO*>(a.out);
@@ -297,6 +304,7 @@ int launch_pair(const CUtensorMap& mw, const CUtensorMap& mx, TpArgs a, long lon
   const int sms = af_sm_count();
   if (sms <= 0) return -1;
   const long long pairs = tiles < sms / 2 ? tiles : sms / 2;
+  a.group = af_tile_group(a.tiles_m, sms / 2);
   af_launch(gemm_tc_pair_kernel<ACT, TO>, dim3((unsigned)(2 * pairs)), dim3(TP_THREADS), TP_SMEM, stream, mw, mx, a);
   AF_CHECK_LAUNCH("af_gemm_tc_pair");
 }
