@@ -148,21 +148,39 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
       // the K blocks of all tiles of this pair form one sequence `it` through the ring of stages
       const int my_tiles = pair < n_tiles ? (n_tiles - pair + n_pairs - 1) / n_pairs : 0;
       const int total = my_tiles * kb_count;
+      // The two streams of copies (weights, activations) each walk the tiles' K blocks in order; where a stream
+      // is in its walk is counted on, not divided out stage by stage (this thread has a stage's copies to send
+      // in the time its products take).
+      struct Walk {
+        int kb, tile, wt, mt;
+      };
+      auto begin = [&](Walk& w) {
+        w.kb = 0;
+        w.tile = pair;
+        w.wt = w.mt = 0;
+        if (w.tile < n_tiles) af_tile_of(w.tile, a.tiles_w, a.tiles_m, a.group, &w.wt, &w.mt);
+      };
+      auto step = [&](Walk& w) {
+        if (++w.kb == kb_count) {
+          w.kb = 0;
+          w.tile += n_pairs;
+          if (w.tile < n_tiles) af_tile_of(w.tile, a.tiles_w, a.tiles_m, a.group, &w.wt, &w.mt);
+        }
+      };
+      Walk ww, wx;
+      begin(ww);
+      begin(wx);
       auto load_w = [&](int it) {
-        const int tile = pair + (it / kb_count) * n_pairs;
-        int wt, mt;
-        af_tile_of(tile, a.tiles_w, a.tiles_m, a.group, &wt, &mt);
-        const int n0 = wt * (2 * TP_BM) + (int)rank * TP_BM;
-        tma_load_2d_pair(tiles + (size_t)(it % TP_STAGES) * TP_STAGE_BYTES, &map_w, (it % kb_count) * TP_BK, n0,
+        const int n0 = ww.wt * (2 * TP_BM) + (int)rank * TP_BM;
+        tma_load_2d_pair(tiles + (size_t)(it % TP_STAGES) * TP_STAGE_BYTES, &map_w, ww.kb * TP_BK, n0,
                          map_to_rank(smem_u32(&full[it % TP_STAGES]), 0));
+        step(ww);
       };
       auto load_x = [&](int it) {
-        const int tile = pair + (it / kb_count) * n_pairs;
-        int wt, mt;
-        af_tile_of(tile, a.tiles_w, a.tiles_m, a.group, &wt, &mt);
-        const int m0 = mt * TP_BN + (int)rank * (TP_BN / 2);
-        tma_load_2d_pair(tiles + (size_t)(it % TP_STAGES) * TP_STAGE_BYTES + TP_A_BYTES, &map_x, (it % kb_count) * TP_BK,
+        const int m0 = wx.mt * TP_BN + (int)rank * (TP_BN / 2);
+        tma_load_2d_pair(tiles + (size_t)(it % TP_STAGES) * TP_STAGE_BYTES + TP_A_BYTES, &map_x, wx.kb * TP_BK,
                          m0, map_to_rank(smem_u32(&full[it % TP_STAGES]), 0));
+        step(wx);
       };
       // The weights do not depend on the kernel in front: the first stages' weight tiles go out before the
       // wait for it, the activations after it.
