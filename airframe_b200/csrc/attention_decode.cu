@@ -4,8 +4,9 @@
 //
 // How the work is cut.  The grid is one block an SM.  A unit is a (sequence, kv head) pair (a tile of 16
 // heads of it, if the group is larger) with the cache pages its sequence's new token attends to; the pages
-// of all units, divided by the blocks, are a block's share.  Every block works out the cut from the
-// lengths, the same way (da_plan):
+// of all units, divided by the blocks, are a block's share.  The cut follows from the lengths alone
+// (da_plan); a small kernel works it out once a step for all layers that read their caches alike and leaves
+// every block what it begins with (af_attn_decode_plan), or, without such a plan, every block works it out:
 //  * the even cut: every unit into about pages / share splits of equal size, one split a block.  No block
 //    meets the end of a unit; taken when the splits are no more than the blocks and none is more than two
 //    pages above the share (sequences of equal or of mixed lengths, one long one among short ones);
