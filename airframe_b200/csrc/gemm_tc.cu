@@ -458,10 +458,12 @@ int launch(const CUtensorMap& mw, const CUtensorMap& mx, TcArgs a, long long n_w
   if constexpr (BN <= 64 && NACC == 1) {
     // bound by the weight stream: a block per tile; many waves of them run two to an SM
     dim3 grid((unsigned)tiles, 1, splits);
-    // Half an SM's shared memory a block for grids of more than two waves: one block's fill and drain hide
-    // behind the other's stream.  (For the short streams of a decode step, whose next kernel's blocks would
-    // then fit beside these, it measured the same or worse inside the step: 1.68 ms against 1.66 at batch 1.)
-    if (per_sm == 2 || (per_sm == 0 && tiles * splits > 2 * sms))
+    // Half an SM's shared memory a block for grids of more than one wave: one block's fill and drain hide
+    // behind the other's stream, and a grid of one and a half waves (the gated product of 9B sizes: 224 tiles)
+    // streams all its tiles at once instead of 148 and then 76 (the decode step of 9B sizes, batch 8: 4.72 ms
+    // against 5.08).  (For grids that fit one wave, whose next kernel's blocks would then fit beside these, it
+    // measured the same or worse inside the step: 1.68 ms against 1.66 at batch 1 of 2B sizes.)
+    if (per_sm == 2 || (per_sm == 0 && tiles * splits > sms))
       return launch_on<BN, NACC, ACT, TO, 2>(grid, mw, mx, a, stream);
     return launch_on<BN, NACC, ACT, TO, 1>(grid, mw, mx, a, stream);
   }
@@ -530,7 +532,7 @@ AF_EXPORT int af_gemm_tc_token_tile(int M) {
 // N] partial sums (part_stride elements apart) and out_dtype must be AF_F32.
 // per_sm (weight-bound products of up to 64 tokens only): 2 gives a block half an SM's shared memory, so that the
 // blocks of the next product in the stream fit beside it and fetch their first weight tiles while this one still
-// runs; 1 gives it the whole SM; 0 chooses (2 for grids of more than two waves).
+// runs; 1 gives it the whole SM; 0 chooses (2 for grids of more than one wave).
 // err: device word set to 1 when a wait inside the kernel ran out of time.
 AF_EXPORT int af_gemm_tc(void* out, int out_dtype, long long ldo, long long part_stride, const void* x,
                          long long ldx, const void* w, long long ldw, long long n_w_rows, int M, int K, int gated,
