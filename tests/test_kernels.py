@@ -765,6 +765,61 @@ def test_a_wait_that_runs_out_sets_the_error_word_and_the_library_goes_on(K):
         K.selftest_wait_runs_out(DEV, limit_ms=5000.0)
 
 
+def test_attention_decode_random_shapes_agree_with_the_plain_kernel(K):
+    """Fifty random steps (head sizes, groups of up to 20 heads, 1 to 200 sequences of every mix of lengths, windows,
+    rows without a slot, any room for partial results, with and without the step's plan): the split kernel's cut
+    must cover every page of every sequence once, whatever the shapes; the plain kernel walks the keys one by one."""
+    import random
+    rng = random.Random(20)
+    ran = 0
+    while ran < 50:
+        hd = rng.choice([64, 128, 256])
+        nkv = rng.choice([1, 2, 4, 8])
+        nq = nkv * rng.choice([1, 2, 3, 8, 17, 20])
+        if nq * hd > 8192:
+            continue
+        B = rng.choice([1, 2, 3, 7, 8, 31, 32, 33, 64, 65, 100, 150, 200])
+        kind = rng.choice(["short", "mixed", "long1", "equal", "tiny"])
+        if kind == "short":
+            lens = [rng.randint(1, 200) for _ in range(B)]
+        elif kind == "mixed":
+            lens = [rng.randint(1, 1500) for _ in range(B)]
+        elif kind == "long1":
+            lens = [rng.randint(1, 100) for _ in range(B)]
+            lens[rng.randrange(B)] = rng.randint(2000, 5000)
+        elif kind == "equal":
+            lens = [rng.choice([64, 65, 128, 700, 1024])] * B
+        else:
+            lens = [rng.randint(1, 3) for _ in range(B)]
+        window = rng.choice([0, 0, 64, 100, 257, 1024])
+        ring = ((window + PAGE - 1) // PAGE) * PAGE if window else 0
+        per_seq = max(((min(n, ring) if ring else n) + PAGE - 1) // PAGE for n in lens)
+        n_pages = B * per_seq + 1
+        if n_pages * nkv * PAGE * hd * 4 > 2e9:
+            continue
+        ran += 1
+        g = torch.Generator().manual_seed(ran)
+        table = (torch.randperm(n_pages - 1, generator=g)[: B * per_seq].reshape(B, per_seq) + 1).to(torch.int32).to(DEV)
+        kc = (torch.randn(n_pages, nkv, PAGE, hd, device=DEV) * 0.3).bfloat16()
+        vc = torch.randn(n_pages, nkv, PAGE, hd, device=DEV).bfloat16()
+        slots = torch.tensor([-1 if rng.random() < 0.15 else b for b in range(B)], dtype=torch.int32, device=DEV)
+        lens_t = torch.tensor(lens, dtype=torch.int32, device=DEV)
+        q = torch.randn(B, nq * hd, device=DEV).bfloat16()
+        scale, cap = 1.0 / math.sqrt(hd), rng.choice([0.0, 30.0])
+        ref = torch.empty(B, nq * hd, dtype=torch.bfloat16, device=DEV)
+        K.attn_decode_plain(ref, q, kc, vc, table, slots, lens_t, nq, nkv, hd, scale, cap, window, ring)
+        for room in (K.attn_decode_max_splits(B, nkv, max(lens), window, nq=nq), rng.choice([1, 2, 3, 4, 7])):
+            for use_plan in (False, True):
+                out = torch.full((B, nq * hd), float("nan"), dtype=torch.bfloat16, device=DEV)
+                plan = K.attn_decode_plan(table, slots, lens_t, nq, nkv, window, ring, room) if use_plan else None
+                K.attn_decode_split(out, q, kc, vc, table, slots, lens_t, nq, nkv, hd, scale, cap, window, ring, room,
+                                    plan=plan)
+                K.check_device_errors(DEV)
+                off = float((out.float() - ref.float()).abs().max())
+                assert off <= 1.2e-2 * max(1.0, float(ref.float().abs().max())), \
+                    dict(hd=hd, nq=nq, nkv=nkv, B=B, kind=kind, window=window, room=room, plan=use_plan, off=off)
+
+
 def test_attention_decode_refuses_a_plan_of_another_launch(K):
     """A plan made for other room than the call's is not followed: the error word is raised, nothing is read
     through it."""
