@@ -360,14 +360,19 @@ def gemm_tc_supported(x, w, out) -> bool:
 
 
 def gemm_tc_splits(M: int, N: int, K: int) -> int:
-    """How many K splits fill the GPU when a product has few output tiles."""
+    """How many K splits fill the GPU when a product has few output tiles: up to
+    two blocks an SM (a grid beyond one wave runs two blocks an SM, which stream
+    at once: measured faster inside the decode step than one wave of blocks
+    with a whole SM each; for up to 16 rows), at least 4 K blocks a split, at
+    most 16 splits."""
     lib = _lib()
     bn = lib.af_gemm_tc_token_tile(c_int(M))
     tiles = ((N + 127) // 128) * ((M + bn - 1) // bn)
     kb = (K + 63) // 64
     if tiles >= 96 or kb < 8:
         return 1
-    want = max(1, min(sm_count() // tiles, kb // 4, 16))
+    waves = 2 if M <= 16 else 1       # (more rows: the partial sums' own bytes weigh more than the fuller GPU)
+    want = max(1, min((waves * sm_count()) // tiles, kb // 4, 16))
     per = (kb + want - 1) // want
     return (kb + per - 1) // per
 
