@@ -157,6 +157,17 @@ class Engine:
         self.cache.commit(growth)
         return logits if borrow else logits.clone()
 
+    def repeat_last_decode(self, n: int) -> None:
+        """Runs the captured decode step of the last call ``n`` more times on
+        the inputs it had: the same rows go into the cache again and the same
+        results come out, nothing else changes.  For measurements (the device's
+        clocks settle under the load of the step itself before it is timed)."""
+        g = getattr(self, "_last_graph", None)
+        if g is None:
+            raise StepError("no captured decode step has run yet")
+        for _ in range(n):
+            g["graph"].replay()
+
     def _decode_graphed(self, slots, lens, tokens=None, tokens_dev=None, greedy: bool = False):
         """One decode step, every row wanting its token's logits, through a CUDA
         graph.  Rows with slot -1 are padding.  The tokens come from the host
@@ -191,6 +202,7 @@ class Engine:
             g["dynamic"][:B].copy_(tokens_dev[:B], non_blocking=True)
         g["graph"].replay()
         self.replayed_launches += g["launches"]
+        self._last_graph = g
         return g["logits"][:B]
 
     def _capture(self, Bp: int, greedy: bool = False) -> dict:
