@@ -138,6 +138,9 @@ def test_decode_steps_fed_from_the_device(case, dtype):
                     dev = torch.tensor(toks, dtype=torch.int32, device=eng.device)
                     lg = eng.decode_rows([slots[i] if i in live else None for i in range(3)], dev)
                     got.append(lg[live].clone())
+                    # the same step again on its own inputs changes nothing: not these logits, not the steps after
+                    eng.repeat_last_decode(2)
+                    assert torch.equal(lg[live], got[-1])
             outs[way] = got
         finally:
             for s in slots:
