@@ -20,13 +20,14 @@ template <typename T>
 __device__ __forceinline__ float rope_src(const T* row, const float* parts, int n_parts, size_t part_stride,
                                           int i) {
   if (parts == nullptr) return to_f32(row[i]);
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  // (16 loads in flight: a product of up to 16 splits costs one round trip; the sums go on in index order)
+  float acc[16];
   float v = 0.f;
-  for (int p0 = 0; p0 < n_parts; p0 += 4) {
+  for (int p0 = 0; p0 < n_parts; p0 += 16) {
 #pragma unroll
-    for (int u = 0; u < 4; ++u) acc[u] = p0 + u < n_parts ? parts[(size_t)(p0 + u) * part_stride + i] : 0.f;
+    for (int u = 0; u < 16; ++u) acc[u] = p0 + u < n_parts ? parts[(size_t)(p0 + u) * part_stride + i] : 0.f;
 #pragma unroll
-    for (int u = 0; u < 4; ++u) v += acc[u];
+    for (int u = 0; u < 16; ++u) v += acc[u];
   }
   return v;
 }

