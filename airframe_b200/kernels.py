@@ -659,11 +659,15 @@ def attn_decode_split(out, q, kcache, vcache, page_table, slots, lens, nq, nkv, 
         _ptr(error_word(q.device), "err", torch.int32), _stream()))
 
 
+ATTN_DECODE_MAX_SEQS = 2048     # sequences of a step that the split kernel plans for (more: the plain kernel)
+
+
 def attn_decode(out, q, kv, batch, nq, nkv, hd, scale, cap, window, slopes=None) -> None:
     """Attention of a decode step over the cache: the split kernel for
     bfloat16 and head sizes it takes, else the plain kernel (which also serves
     scores with a per-head slope)."""
-    if slopes is None and q.dtype == torch.bfloat16 and _lib().af_attn_decode_supported(c_int(hd)):
+    if (slopes is None and q.dtype == torch.bfloat16 and _lib().af_attn_decode_supported(c_int(hd))
+            and batch.n_seqs <= ATTN_DECODE_MAX_SEQS):
         n = attn_decode_max_splits(batch.n_seqs, nkv, batch.max_len_after, window, nq=nq)
         # the plan of the step, shared by the layers that read this group of caches alike (a batch without a
         # place for the step's tables gets none: every block then works the cut out itself)
